@@ -1,0 +1,518 @@
+#!/usr/bin/env python
+"""Benchmark of the FFT spatial-convolution path (one JSON line on stdout).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--layer C2] [--impl ours|reference]
+
+A step is the three nn passes (updateOutput, updateGradInput, accGradParameters) of one
+layer over one seeded synthetic batch; `value` is direct-convolution-equivalent TFLOP/s
+(3 * 2*B*P*F*kH*kW*oH*oW flops per step) with the operands resident in HBM.  With N > 1
+ranks the global batch of 128 is split across ranks (strong scaling) and the weight
+gradient's spectrum is all-reduced inside accGradParameters.  `e2e` is the same step
+through the host-buffer entry points of the C ABI (pinned host memory, copies timed).
+`--impl reference` times the reference's own CPU convolution (compiled from its source
+under oracle/_ref) on a bounded batch slice with every host thread.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# name: (B, P, F, iH, iW, kH, kW, padH, padW, bias?)   -- the reference's benchmark list
+LAYERS = {
+    "C1": (16, 16, 16, 32, 32, 5, 5, 0, 0, False),
+    "C2": (128, 3, 96, 128, 128, 11, 11, 0, 0, True),
+    "C3": (128, 64, 128, 64, 64, 9, 9, 0, 0, False),
+    "C4a": (128, 128, 128, 32, 32, 9, 9, 0, 0, False),
+    "C4b": (128, 128, 128, 16, 16, 7, 7, 0, 0, False),
+    "C5": (128, 384, 384, 13, 13, 3, 3, 1, 1, False),
+}
+PASSES = ("updateOutput", "updateGradInput", "accGradParameters")
+STAGES = ("fft_a", "fft_b", "contract", "allreduce", "ifft", "bias")
+METRIC = "direct-conv-equivalent TFLOP/s over updateOutput+updateGradInput+accGradParameters (ms per pass in `layers`)"
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def conv_flops(L, batch=None):
+    B, P, F, iH, iW, kH, kW, pH, pW, _ = L
+    B = batch if batch is not None else B
+    oH, oW = iH + 2 * pH - kH + 1, iW + 2 * pW - kW + 1
+    return 2.0 * B * P * F * kH * kW * oH * oW
+
+
+def fft_size(L):
+    _, _, _, iH, iW, kH, kW, pH, pW, _ = L
+    n, need = 8, max(iH + 2 * pH, iW + 2 * pW, kH, kW)
+    while n < need:
+        n *= 2
+    return n
+
+
+def stage_algorithmic(L, B, pass_idx, stage):
+    """(bytes, flops) one launch of a stage moves / performs, by the definitions in DESIGN.md:
+    a transform of D planes of h x w reads or writes 4*D*h*w real bytes and 8*D*bins
+    spectrum bytes; the contraction reads two spectra, writes one and does 8*M*N*K*bins flops."""
+    _, P, F, iH, iW, kH, kW, pH, pW, _ = L
+    oH, oW = iH + 2 * pH - kH + 1, iW + 2 * pW - kW + 1
+    n = fft_size(L)
+    bins = (n // 2 + 1) * n
+    real = {"in": (B * P, iH * iW), "out": (B * F, oH * oW), "w": (F * P, kH * kW)}
+    plan = {  # pass -> (fft_a, fft_b, ifft) operands
+        0: ("in", "w", "out"), 1: ("out", "w", "in"), 2: ("out", "in", "w")}[pass_idx]
+    def tr(which):
+        d, hw = real[which]
+        return 4.0 * d * hw + 8.0 * d * bins
+    if stage == "fft_a":
+        return tr(plan[0]), 0.0
+    if stage == "fft_b":
+        return tr(plan[1]), 0.0
+    if stage == "ifft":
+        return tr(plan[2]), 0.0
+    if stage == "contract":
+        spectra = 8.0 * bins * (B * P + B * F + F * P)
+        return spectra, 8.0 * B * P * F * bins
+    if stage == "allreduce":
+        return 8.0 * bins * F * P, 0.0
+    if stage == "bias":
+        return 8.0 * B * F, 0.0
+    raise KeyError(stage)
+
+
+# ---------------------------------------------------------------------------
+# reference arm / CPU baseline
+# ---------------------------------------------------------------------------
+def host_threads():
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def cpu_reference_step(L, threads, items, filters, seed=0):
+    """One bounded sample: the three reference CPU functions on `items` batch elements and
+    the first `filters` output planes of the layer, batch slices spread over `threads`
+    threads.  Work is linear in both, so throughput carries over to the full layer.
+    Returns (seconds, kind)."""
+    import numpy as np
+    import oracle
+    _, P, _, iH, iW, kH, kW, pH, pW, _ = L
+    s = oracle.Shape(items, P, filters, iH, iW, kH, kW, pH, pW)
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((items, P, iH, iW)).astype(np.float32)
+    w = rng.uniform(-1, 1, (filters, P, kH, kW)).astype(np.float32) / np.float32(np.sqrt(kH * kW * P))
+    go = rng.standard_normal((items, filters, s.oH, s.oW)).astype(np.float32)
+    use_ref = oracle.reference_available()
+    t0 = time.perf_counter()
+    if use_ref:
+        oracle.reference_update_output(s, x, w, threads=threads)
+        oracle.reference_update_grad_input(s, go, w, threads=threads)
+        oracle.reference_acc_grad_weight(s, x, go, 1.0, threads=threads)
+    else:  # the fp64 restatement (OpenMP over planes)
+        oracle.update_output(s, x, w)
+        oracle.update_grad_input(s, go, w)
+        oracle.acc_grad_weight(s, x, go, 1.0)
+    return time.perf_counter() - t0, ("reference" if use_ref else "port")
+
+
+def sample_flops(L, items, filters):
+    return 3.0 * conv_flops(L, items) * filters / L[2]
+
+
+def cpu_sample(L, threads, target_s):
+    """Sizes a sample (batch items, filters) that takes about target_s seconds: one batch
+    element per thread, then as many filters as fit, calibrated by a small probe."""
+    items = int(min(L[0], threads))
+    probe_f = max(1, L[2] // 32)
+    dt, _ = cpu_reference_step(L, threads, items, probe_f)
+    rate = sample_flops(L, items, probe_f) / max(dt, 1e-6)
+    filters = int(max(1, min(L[2], round(rate * target_s / sample_flops(L, items, 1)))))
+    return items, filters
+
+
+def sample_text(name, L, items, filters, threads):
+    return (f"{items} of {L[0]} batch elements x {filters} of {L[2]} filters of layer {name}, all three passes, "
+            f"{threads} threads (one batch slice each); throughput is linear in both")
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    L = LAYERS[args.layer]
+    threads = host_threads()
+    target = max(0.5, min(8.0, 120.0 / max(1, args.steps + args.warmup)))
+    items, filters = cpu_sample(L, threads, target)
+    kind = "reference"
+    for _ in range(args.warmup):
+        _, kind = cpu_reference_step(L, threads, items, filters)
+    times = []
+    for i in range(args.steps):
+        dt, kind = cpu_reference_step(L, threads, items, filters, seed=i + 1)
+        times.append(dt)
+    total = sum(times)
+    value = sample_flops(L, items, filters) * args.steps / total / 1e12
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": workload_config(args.layer, L, args.gpus),
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": min(threads, items), "kind": kind,
+                         "sample": sample_text(args.layer, L, items, filters, threads)},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+def workload_config(name, L, gpus):
+    B, P, F, iH, iW, kH, kW, pH, pW, _ = L
+    return {
+        "workload": f"{name}: batch {B} x {P} planes x {iH}x{iW}, {F} filters {kH}x{kW}, pad {pH}, stride 1, "
+                    f"FFT size {fft_size(L)}; one step = updateOutput + updateGradInput + accGradParameters",
+        "global_batch": B, "parallelism": f"batch sharded over {gpus} rank(s), gradWeight spectrum all-reduced (NCCL)"
+        if gpus > 1 else "single GPU",
+        "l2": "per-step working set exceeds the 126 MB L2; per-pass rows in `layers` are timed after an L2 flush",
+    }
+
+
+# ---------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        try:
+            with open(self.path) as f:
+                for line in f:
+                    c = [x.strip() for x in line.split(",")]
+                    if len(c) < 9:
+                        continue
+                    try:
+                        sm.append(float(c[1]))
+                        mx.append(float(c[2]))
+                    except ValueError:
+                        continue
+                    for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), c[5:9]):
+                        if v.lower().startswith("active"):
+                            reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            busy = [v for v in sm if v >= 0.5 * max(sm)] or sm
+            out.update(sm_mhz=statistics.median(busy), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+def gen(torch, shape, seed, kind="normal", bound=1.0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    t = torch.empty(shape, device="cuda", dtype=torch.float32)
+    return t.normal_(generator=g) if kind == "normal" else t.uniform_(-bound, bound, generator=g)
+
+
+class LayerRun:
+    """Device tensors and a native handle for one layer at a local batch."""
+
+    def __init__(self, torch, name, L, local_batch, rank, comm=None):
+        from fbcunn_b200 import SpatialConvolutionFBFFT
+        self.torch, self.name, self.L, self.B = torch, name, L, local_batch
+        _, P, F, iH, iW, kH, kW, pH, pW, has_bias = L
+        cfg = list(LAYERS).index(name) + 1
+        oH, oW = iH + 2 * pH - kH + 1, iW + 2 * pW - kW + 1
+        bound = 1.0 / (kH * kW * P) ** 0.5
+        self.x = gen(torch, (local_batch, P, iH, iW), 1000 * cfg + 10 * rank)
+        self.go = gen(torch, (local_batch, F, oH, oW), 1000 * cfg + 10 * rank + 1)
+        self.m = SpatialConvolutionFBFFT(P, F, kW, kH, 1, 1, pW, pH)
+        self.m.weight.copy_(gen(torch, (F, P, kH, kW), 1000 * cfg + 2, "uniform", bound))
+        if has_bias:
+            self.m.bias.copy_(gen(torch, (F,), 1000 * cfg + 3, "uniform", 0.01))
+        else:
+            self.m.bias.zero_()
+        if comm is not None:
+            self.m.attachCommunicator(*comm)
+
+    def step(self):
+        self.m.updateOutput(self.x)
+        self.m.updateGradInput(self.x, self.go)
+        self.m.accGradParameters(self.x, self.go, 1.0)
+
+    def run_pass(self, i):
+        if i == 0:
+            self.m.updateOutput(self.x)
+        elif i == 1:
+            self.m.updateGradInput(self.x, self.go)
+        else:
+            self.m.accGradParameters(self.x, self.go, 1.0)
+
+    def handle(self):
+        return self.m._handle
+
+
+def read_profile(handle):
+    from fbcunn_b200 import capi
+    out = {}
+    for pi, pname in enumerate(PASSES):
+        for si, sname in enumerate(STAGES):
+            ms, n = ctypes.c_double(), ctypes.c_int()
+            capi.check(capi.lib().fbfftconv_profile_read(handle, pi, si, ctypes.byref(ms), ctypes.byref(n)))
+            if n.value:
+                out[(pi, sname)] = (ms.value, n.value)
+    return out
+
+
+def kernel_table(L, B, prof, pk):
+    rows = []
+    for (pi, sname), (ms, n) in sorted(prof.items()):
+        by, fl = stage_algorithmic(L, B, pi, sname)
+        avg_s = ms / n / 1e3
+        row = {"pass": PASSES[pi], "kernel": sname, "launches": n, "avg_us": 1e6 * avg_s, "total_ms": ms,
+               "gbs": by / avg_s / 1e9 if avg_s > 0 else None}
+        if fl:
+            row["tflops"] = fl / avg_s / 1e12 if avg_s > 0 else None
+        rows.append(row)
+    return rows
+
+
+def run_gpu_arm(args):
+    import torch
+    import torch.distributed as dist
+    from fbcunn_b200 import build as fb_build
+    from fbcunn_b200 import capi
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    fb_build.build()
+    capi.lib()
+    comm = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        from fbcunn_b200 import SpatialConvolutionFBFFT
+        uid = torch.zeros(128, dtype=torch.uint8, device="cuda")
+        if rank == 0:
+            uid.copy_(torch.frombuffer(bytearray(SpatialConvolutionFBFFT.makeUniqueId()), dtype=torch.uint8))
+        dist.broadcast(uid, 0)
+        comm = (bytes(uid.cpu().numpy().tobytes()), rank, world)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(v):
+        if world == 1:
+            return v
+        t = torch.tensor([v], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    pk = peaks()
+    name, L = args.layer, LAYERS[args.layer]
+    assert L[0] % world == 0, "global batch must divide over the ranks"
+    local_b = L[0] // world
+    run = LayerRun(torch, name, L, local_b, rank, comm)
+    for _ in range(max(args.warmup, 3)):
+        run.step()
+    barrier()
+
+    # ---- timed region: K steps, device time, max over ranks --------------------
+    lib = capi.lib()
+    capi.check(lib.fbfftconv_profile_enable(run.handle(), 1))
+    capi.check(lib.fbfftconv_profile_reset(run.handle()))
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = capi.kernel_launches()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record()
+    for _ in range(args.steps):
+        run.step()
+    ev1.record()
+    barrier()
+    elapsed_ms = max_over_ranks(ev0.elapsed_time(ev1))
+    launches = capi.kernel_launches() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    prof = read_profile(run.handle())
+    capi.check(lib.fbfftconv_profile_enable(run.handle(), 0))
+    ms_per_step = elapsed_ms / args.steps
+    value = 3.0 * conv_flops(L) / (ms_per_step / 1e3) / 1e12
+
+    kernels = kernel_table(L, local_b, prof, pk)
+    top = max((k for k in kernels if k["kernel"] != "allreduce"), key=lambda k: k["total_ms"])
+    tensor_bound = False  # the fp32 CUDA-core contraction is compared with HBM like the transforms
+    by, fl = stage_algorithmic(L, local_b, PASSES.index(top["pass"]), top["kernel"])
+    achieved = by / (top["avg_us"] / 1e6) / 1e9
+    roofline = {"bound": "hbm", "kernel": f'{top["kernel"]} of {top["pass"]}', "achieved": achieved,
+                "peak": pk["hbm_gbs"], "peak_source": pk["source"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"],
+                "traffic": None, "algorithmic_bytes_per_launch": by, "avg_launch_us": top["avg_us"],
+                "share_of_step": top["total_ms"] / elapsed_ms}
+    del tensor_bound
+
+    # ---- e2e: host buffers through the *_host entry points ----------------------
+    e2e = measure_e2e(torch, lib, run, L, local_b, world, barrier, max_over_ranks,
+                      steps=max(1, min(args.steps, 5)))
+
+    # ---- per layer, per pass (cold L2) ------------------------------------------
+    layers = {}
+    if not args.no_layers:
+        del run
+        torch.cuda.empty_cache()
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+        for lname, LL in LAYERS.items():
+            if LL[0] % world:
+                continue
+            lb = LL[0] // world
+            r = LayerRun(torch, lname, LL, lb, rank, comm)
+            for _ in range(3):
+                r.step()
+            capi.check(lib.fbfftconv_profile_enable(r.handle(), 1))
+            capi.check(lib.fbfftconv_profile_reset(r.handle()))
+            per_pass = []
+            for pi in range(3):
+                ts = []
+                for _ in range(args.layer_iters):
+                    flush.zero_()
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    barrier()
+                    a.record()
+                    r.run_pass(pi)
+                    b.record()
+                    barrier()
+                    ts.append(max_over_ranks(a.elapsed_time(b)))
+                ms = statistics.median(ts)
+                per_pass.append({"pass": PASSES[pi], "ms": ms, "tflops": conv_flops(LL) / (ms / 1e3) / 1e12})
+            prof_l = read_profile(r.handle())
+            layers[lname] = {"fft_size": fft_size(LL), "local_batch": lb, "passes": per_pass,
+                             "kernels": kernel_table(LL, lb, prof_l, pk)}
+            del r
+            torch.cuda.empty_cache()
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        threads = host_threads()
+        items, filters = cpu_sample(L, threads, 6.0)
+        dt, kind = cpu_reference_step(L, threads, items, filters)
+        dt2, kind = cpu_reference_step(L, threads, items, filters, seed=1)
+        dt = min(dt, dt2)
+        cpu = {"value": sample_flops(L, items, filters) / dt / 1e12, "unit": "TFLOP/s",
+               "cores": min(threads, items), "kind": kind,
+               "sample": sample_text(name, L, items, filters, threads) + f"; {dt:.1f} s per sample"}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": workload_config(name, L, world), "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
+            "gpu_launches": int(launches), "clocks": clocks, "kernels": kernels, "layers": layers,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+def measure_e2e(torch, lib, run, L, local_b, world, barrier, max_over_ranks, steps):
+    from fbcunn_b200 import capi
+    m = run.m
+    _, P, F, iH, iW, kH, kW, pH, pW, has_bias = L
+    oH, oW = iH + 2 * pH - kH + 1, iW + 2 * pW - kW + 1
+    pin = lambda t: t.detach().cpu().pin_memory()
+    hx, hgo, hw, hb = pin(run.x), pin(run.go), pin(m.weight), pin(m.bias)
+    hout = torch.empty((local_b, F, oH, oW)).pin_memory()
+    hgi = torch.empty((local_b, P, iH, iW)).pin_memory()
+    hgw = torch.empty((F, P, kH, kW)).pin_memory()
+    hgb = torch.empty((F,)).pin_memory()
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    h = run.handle()
+
+    def step():
+        capi.check(lib.fbfftconv_update_output_host(h, p(hx), p(hw), p(hb) if has_bias else None, p(hout), st))
+        capi.check(lib.fbfftconv_update_grad_input_host(h, p(hgo), p(hw), p(hgi), st))
+        capi.check(lib.fbfftconv_acc_grad_parameters_host(h, p(hx), p(hgo), p(hgw), p(hgb), ctypes.c_float(1.0), st))
+
+    step()
+    barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        step()
+    b.record()
+    barrier()
+    ms = max_over_ranks(a.elapsed_time(b)) / steps
+    h2d = 4 * (2 * hx.numel() + 2 * hgo.numel() + 2 * hw.numel() + (hb.numel() if has_bias else 0))
+    d2h = 4 * (hout.numel() + hgi.numel() + hgw.numel() + hgb.numel())
+    return {"value": 3.0 * conv_flops(L) / (ms / 1e3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms,
+            "h2d_bytes_per_step": int(h2d) * world, "d2h_bytes_per_step": int(d2h) * world,
+            "api": "fbfftconv_update_output_host / _update_grad_input_host / _acc_grad_parameters_host, pinned host buffers"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--layer", default="C2", choices=list(LAYERS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layer-iters", type=int, default=5)
+    ap.add_argument("--no-layers", action="store_true", help="skip the per-layer / per-pass table")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference_arm(args)
+    return run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

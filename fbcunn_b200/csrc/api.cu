@@ -1,0 +1,755 @@
+// C ABI of the library (declared in include/fbfftconv.h): handle, scratch
+// management, the three passes, their host-buffer variants, the sub-steps and the
+// NCCL hook.  Plays the part of the reference's pass driver
+// (fbcunn/SpatialConvolutionFBFFT.lua:102-354) and buffer cache
+// (fbcunn/SpatialConvolutionFFT.lua:652-870) on the native side of the boundary.
+#include <dlfcn.h>
+#include <nccl.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "../../include/fbfftconv.h"
+#include "kernels.h"
+
+using namespace fbfft;
+
+namespace {
+
+thread_local std::string t_error;
+
+int fail(int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  t_error = buf;
+  return code;
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+  return fail(FBFFTCONV_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+#define FBF_CUDA(expr)                                   \
+  do {                                                   \
+    cudaError_t e_ = (expr);                             \
+    if (e_ != cudaSuccess) return cuda_fail(e_, #expr);  \
+  } while (0)
+#define FBF_TRY(expr)                    \
+  do {                                   \
+    int rc_ = (expr);                    \
+    if (rc_ != FBFFTCONV_OK) return rc_; \
+  } while (0)
+
+int pad4(int v) { return (v + 3) & ~3; }
+
+int next_pow2(int v) {
+  int p = 1;
+  while (p < v) p <<= 1;
+  return p;
+}
+
+// ---- NCCL, resolved at run time so that single-GPU users need no libnccl -----
+struct NcclApi {
+  void* lib = nullptr;
+  ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
+  ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+  ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t,
+                            cudaStream_t) = nullptr;
+  ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+  const char* (*GetErrorString)(ncclResult_t) = nullptr;
+};
+
+NcclApi* nccl_api() {
+  static NcclApi api;
+  static bool tried = false;
+  if (tried) return api.lib ? &api : nullptr;
+  tried = true;
+  const char* env = getenv("FBFFTCONV_NCCL_LIB");
+  void* lib = nullptr;
+  if (env && *env) lib = dlopen(env, RTLD_NOW | RTLD_GLOBAL);
+  if (!lib) lib = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD | RTLD_GLOBAL);
+  if (!lib) lib = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+  if (!lib) lib = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+  if (!lib) return nullptr;
+  api.GetUniqueId = reinterpret_cast<decltype(api.GetUniqueId)>(dlsym(lib, "ncclGetUniqueId"));
+  api.CommInitRank = reinterpret_cast<decltype(api.CommInitRank)>(dlsym(lib, "ncclCommInitRank"));
+  api.AllReduce = reinterpret_cast<decltype(api.AllReduce)>(dlsym(lib, "ncclAllReduce"));
+  api.CommDestroy = reinterpret_cast<decltype(api.CommDestroy)>(dlsym(lib, "ncclCommDestroy"));
+  api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(dlsym(lib, "ncclGetErrorString"));
+  if (!api.GetUniqueId || !api.CommInitRank || !api.AllReduce || !api.CommDestroy) return nullptr;
+  api.lib = lib;
+  return &api;
+}
+
+int nccl_fail(NcclApi* api, ncclResult_t r, const char* what) {
+  return fail(FBFFTCONV_ERR_COMM, "%s: %s", what,
+              api && api->GetErrorString ? api->GetErrorString(r) : "nccl error");
+}
+
+}  // namespace
+
+struct EventPair {
+  cudaEvent_t start, stop;
+};
+
+struct fbfftconv_handle {
+  fbfftconv_desc d;
+  // per-kernel timing: event pairs per (pass, stage), reused after a reset
+  bool profiling = false;
+  std::vector<EventPair> events[3][FBFFTCONV_STAGE_COUNT];
+  int events_used[3][FBFFTCONV_STAGE_COUNT] = {};
+  int device;
+  int N, bins;
+  int oH, oW;
+  // frequency buffers, each sized for the largest use among the three passes
+  size_t bytes_in, bytes_out, bytes_w, bytes_small, bytes_total;
+  char* ws = nullptr;
+  bool ws_owned = false;
+  // device copies for the host-buffer entry points
+  char* stage = nullptr;
+  size_t stage_bytes = 0;
+  // communicator
+  ncclComm_t comm = nullptr;
+  int rank = 0, nranks = 1;
+
+  float2* buf_in() const { return reinterpret_cast<float2*>(ws); }
+  float2* buf_out() const { return reinterpret_cast<float2*>(ws + bytes_in); }
+  float2* buf_w() const { return reinterpret_cast<float2*>(ws + bytes_in + bytes_out); }
+  float* small() const { return reinterpret_cast<float*>(ws + bytes_in + bytes_out + bytes_w); }
+};
+
+namespace {
+
+size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
+
+int ensure_workspace(fbfftconv_handle* h) {
+  if (h->ws) return FBFFTCONV_OK;
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, h->bytes_total);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(e == cudaErrorMemoryAllocation ? FBFFTCONV_ERR_NOMEM : FBFFTCONV_ERR_CUDA,
+                "workspace of %zu bytes: %s", h->bytes_total, cudaGetErrorString(e));
+  }
+  h->ws = static_cast<char*>(p);
+  h->ws_owned = true;
+  return FBFFTCONV_OK;
+}
+
+// Brackets the work enqueued during its lifetime with an event pair of (pass, stage).
+struct StageTimer {
+  fbfftconv_handle* h;
+  cudaStream_t s;
+  EventPair* ev = nullptr;
+  StageTimer(fbfftconv_handle* h_, int pass, int stage, cudaStream_t s_) : h(h_), s(s_) {
+    if (!h->profiling) return;
+    auto& pool = h->events[pass][stage];
+    int& used = h->events_used[pass][stage];
+    if (used == (int)pool.size()) {
+      EventPair p;
+      if (cudaEventCreate(&p.start) != cudaSuccess || cudaEventCreate(&p.stop) != cudaSuccess) return;
+      pool.push_back(p);
+    }
+    ev = &pool[used++];
+    cudaEventRecord(ev->start, s);
+  }
+  ~StageTimer() {
+    if (ev) cudaEventRecord(ev->stop, s);
+  }
+};
+
+struct DeviceGuard {
+  int prev = -1;
+  bool switched = false;
+  cudaError_t enter(int dev) {
+    cudaError_t e = cudaGetDevice(&prev);
+    if (e != cudaSuccess) return e;
+    if (prev != dev) {
+      e = cudaSetDevice(dev);
+      switched = (e == cudaSuccess);
+    }
+    return e;
+  }
+  ~DeviceGuard() {
+    if (switched) cudaSetDevice(prev);
+  }
+};
+
+FftParams forward_params(const float* real, float2* spec, int d1, int d2, int h, int w, int pad_u,
+                         int pad_l, bool transposed) {
+  FftParams p{};
+  p.real_in = real;
+  p.spec = spec;
+  p.h = h;
+  p.w = w;
+  p.off_y = pad_u;
+  p.off_x = pad_l;
+  if (!transposed) {  // [bin][d1][d2]
+    p.n_rows = d1;
+    p.n_inner = d2;
+    p.real_row_stride = d2;
+    p.real_inner_stride = 1;
+  } else {  // [bin][d2][d1]
+    p.n_rows = d2;
+    p.n_inner = d1;
+    p.real_row_stride = 1;
+    p.real_inner_stride = d2;
+  }
+  p.kc = pad4(p.n_inner);
+  return p;
+}
+
+FftParams inverse_params(const float2* spec, float* real, const float* bias, int d1, int d2, int h,
+                         int w, int off_y, int off_x, int accumulate) {
+  FftParams p{};
+  p.real_out = real;
+  p.spec = const_cast<float2*>(spec);
+  p.bias = bias;
+  p.h = h;
+  p.w = w;
+  p.off_y = off_y;
+  p.off_x = off_x;
+  p.n_rows = d1;
+  p.n_inner = d2;
+  p.kc = pad4(d2);
+  p.real_row_stride = d2;
+  p.real_inner_stride = 1;
+  p.accumulate = accumulate;
+  return p;
+}
+
+int contract(const float2* a, const float2* b, float2* c, int bins, int m, int n, int k, float alpha,
+             int conj_a, int conj_b, bool simt, cudaStream_t s) {
+  ContractParams p{};
+  p.a = a;
+  p.b = b;
+  p.c = c;
+  p.bins = bins;
+  p.m = m;
+  p.n = n;
+  p.k = k;
+  p.lda = p.ldb = pad4(k);
+  p.ldc = pad4(n);
+  p.alpha = alpha;
+  p.conj_a = conj_a;
+  p.conj_b = conj_b;
+  (void)simt;  // the CUDA-core kernel is the only contraction built so far
+  FBF_CUDA(launch_contract_simt(p, s));
+  return FBFFTCONV_OK;
+}
+
+bool valid_fft_size(int n) { return n == 8 || n == 16 || n == 32 || n == 64 || n == 128; }
+
+}  // namespace
+
+extern "C" {
+
+const char* fbfftconv_last_error(void) { return t_error.c_str(); }
+
+const char* fbfftconv_status_string(int status) {
+  switch (status) {
+    case FBFFTCONV_OK: return "ok";
+    case FBFFTCONV_ERR_INVALID_ARGUMENT: return "invalid argument";
+    case FBFFTCONV_ERR_UNSUPPORTED_SIZE: return "unsupported transform size";
+    case FBFFTCONV_ERR_NOMEM: return "out of device memory";
+    case FBFFTCONV_ERR_CUDA: return "CUDA error";
+    case FBFFTCONV_ERR_COMM: return "communicator error";
+  }
+  return "unknown status";
+}
+
+uint64_t fbfftconv_kernel_launches(void) { return launch_count(); }
+
+size_t fbfftconv_spectrum_bytes(int fft_size, int rows, int inner) {
+  if (!valid_fft_size(fft_size) || rows <= 0 || inner <= 0) return 0;
+  return (size_t)(fft_size / 2 + 1) * fft_size * rows * pad4(inner) * sizeof(float2);
+}
+
+int fbfftconv_create(const fbfftconv_desc* desc, fbfftconv_handle** out) {
+  if (!desc || !out) return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "null argument");
+  *out = nullptr;
+  const fbfftconv_desc& d = *desc;
+  if (d.batch <= 0 || d.n_input_plane <= 0 || d.n_output_plane <= 0 || d.input_h <= 0 ||
+      d.input_w <= 0 || d.kernel_h <= 0 || d.kernel_w <= 0)
+    return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "sizes must be positive");
+  if (d.stride_h != 1 || d.stride_w != 1)
+    return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "fft only supports stride-1 convolutions");
+  if (d.pad_h < 0 || d.pad_w < 0 || d.pad_h >= d.kernel_h || d.pad_w >= d.kernel_w)
+    return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "padding must be non-negative and smaller than the kernel");
+  const int oH = d.input_h + 2 * d.pad_h - d.kernel_h + 1;
+  const int oW = d.input_w + 2 * d.pad_w - d.kernel_w + 1;
+  if (oH <= 0 || oW <= 0)
+    return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "kernel larger than the padded input");
+  int need = d.input_h + 2 * d.pad_h;
+  if (d.input_w + 2 * d.pad_w > need) need = d.input_w + 2 * d.pad_w;
+  if (d.kernel_h > need) need = d.kernel_h;
+  if (d.kernel_w > need) need = d.kernel_w;
+  int N = next_pow2(need);
+  if (N < 8) N = 8;
+  if (N > 128)
+    return fail(FBFFTCONV_ERR_UNSUPPORTED_SIZE, "transform size %d exceeds 128", N);
+  if ((long long)d.batch > 65535 || d.n_input_plane > 65535 || d.n_output_plane > 65535)
+    return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "batch / plane counts above 65535 are not supported");
+
+  int device = d.device;
+  if (device < 0) {
+    if (cudaGetDevice(&device) != cudaSuccess) {
+      cudaGetLastError();
+      device = 0;  // resolved again, with an error, at the first pass
+    }
+  }
+  fbfftconv_handle* h = new fbfftconv_handle();
+  h->d = d;
+  h->device = device;
+  h->N = N;
+  h->bins = (N / 2 + 1) * N;
+  h->oH = oH;
+  h->oW = oW;
+  const size_t B = d.batch, P = d.n_input_plane, F = d.n_output_plane, bins = h->bins;
+  auto mx = [](size_t a, size_t b) { return a > b ? a : b; };
+  h->bytes_in = align256(bins * mx(B * pad4(P), P * pad4(B)) * sizeof(float2));
+  h->bytes_out = align256(bins * mx(B * pad4(F), F * pad4(B)) * sizeof(float2));
+  h->bytes_w = align256(bins * mx(F * pad4(P), P * pad4(F)) * sizeof(float2));
+  h->bytes_small = align256((B * F + F) * sizeof(float));
+  h->bytes_total = h->bytes_in + h->bytes_out + h->bytes_w + h->bytes_small;
+  *out = h;
+  return FBFFTCONV_OK;
+}
+
+int fbfftconv_destroy(fbfftconv_handle* h) {
+  if (!h) return FBFFTCONV_OK;
+  DeviceGuard g;
+  g.enter(h->device);
+  if (h->comm) {
+    if (NcclApi* api = nccl_api()) api->CommDestroy(h->comm);
+  }
+  if (h->ws && h->ws_owned) cudaFree(h->ws);
+  if (h->stage) cudaFree(h->stage);
+  for (auto& per_pass : h->events)
+    for (auto& pool : per_pass)
+      for (auto& p : pool) {
+        cudaEventDestroy(p.start);
+        cudaEventDestroy(p.stop);
+      }
+  delete h;
+  return FBFFTCONV_OK;
+}
+
+int fbfftconv_fft_size(const fbfftconv_handle* h) { return h ? h->N : 0; }
+size_t fbfftconv_workspace_bytes(const fbfftconv_handle* h) { return h ? h->bytes_total : 0; }
+
+int fbfftconv_set_workspace(fbfftconv_handle* h, void* device_ptr, size_t bytes) {
+  if (!h) return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "null handle");
+  if (!device_ptr || bytes < h->bytes_total || (reinterpret_cast<uintptr_t>(device_ptr) & 255))
+    return fail(FBFFTCONV_ERR_INVALID_ARGUMENT,
+                "workspace must be 256-byte aligned and hold %zu bytes", h->bytes_total);
+  if (h->ws && h->ws_owned) {
+    DeviceGuard g;
+    g.enter(h->device);
+    cudaFree(h->ws);
+  }
+  h->ws = static_cast<char*>(device_ptr);
+  h->ws_owned = false;
+  return FBFFTCONV_OK;
+}
+
+// ---- passes ----------------------------------------------------------------
+
+int fbfftconv_update_output(fbfftconv_handle* h, const float* input, const float* weight,
+                            const float* bias, float* output, fbfftconv_stream stream) {
+  if (!h || !input || !weight || !output) return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "null argument");
+  DeviceGuard g;
+  FBF_CUDA(g.enter(h->device));
+  FBF_TRY(ensure_workspace(h));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const fbfftconv_desc& d = h->d;
+  const int B = d.batch, P = d.n_input_plane, F = d.n_output_plane;
+  const bool simt = d.flags & FBFFTCONV_CONTRACT_SIMT;
+  const int pass = FBFFTCONV_PASS_UPDATE_OUTPUT;
+  // I^[bin][b][p], W^[bin][f][p]
+  {
+    StageTimer t(h, pass, FBFFTCONV_STAGE_FFT_A, s);
+    FBF_CUDA(launch_forward(forward_params(input, h->buf_in(), B, P, d.input_h, d.input_w, d.pad_h, d.pad_w, false), h->N, s));
+  }
+  {
+    StageTimer t(h, pass, FBFFTCONV_STAGE_FFT_B, s);
+    FBF_CUDA(launch_forward(forward_params(weight, h->buf_w(), F, P, d.kernel_h, d.kernel_w, 0, 0, false), h->N, s));
+  }
+  // O^[bin][b][f] = 1/N^2 sum_p I^[b][p] conj(W^[f][p])
+  {
+    StageTimer t(h, pass, FBFFTCONV_STAGE_CONTRACT, s);
+    FBF_TRY(contract(h->buf_in(), h->buf_w(), h->buf_out(), h->bins, B, F, P,
+                     1.0f / (float)(h->N * h->N), 0, 1, simt, s));
+  }
+  {
+    StageTimer t(h, pass, FBFFTCONV_STAGE_IFFT, s);
+    FBF_CUDA(launch_inverse(inverse_params(h->buf_out(), output, bias, B, F, h->oH, h->oW, 0, 0, 0), h->N, s));
+  }
+  return FBFFTCONV_OK;
+}
+
+int fbfftconv_update_grad_input(fbfftconv_handle* h, const float* grad_output, const float* weight,
+                                float* grad_input, fbfftconv_stream stream) {
+  if (!h || !grad_output || !weight || !grad_input)
+    return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "null argument");
+  DeviceGuard g;
+  FBF_CUDA(g.enter(h->device));
+  FBF_TRY(ensure_workspace(h));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const fbfftconv_desc& d = h->d;
+  const int B = d.batch, P = d.n_input_plane, F = d.n_output_plane;
+  const bool simt = d.flags & FBFFTCONV_CONTRACT_SIMT;
+  const int pass = FBFFTCONV_PASS_UPDATE_GRAD_INPUT;
+  // O'^[bin][b][f], W^[bin][p][f] (weight planes transposed on the fly)
+  {
+    StageTimer t(h, pass, FBFFTCONV_STAGE_FFT_A, s);
+    FBF_CUDA(launch_forward(forward_params(grad_output, h->buf_out(), B, F, h->oH, h->oW, 0, 0, false), h->N, s));
+  }
+  {
+    StageTimer t(h, pass, FBFFTCONV_STAGE_FFT_B, s);
+    FBF_CUDA(launch_forward(forward_params(weight, h->buf_w(), F, P, d.kernel_h, d.kernel_w, 0, 0, true), h->N, s));
+  }
+  // I'^[bin][b][p] = 1/N^2 sum_f O'^[b][f] W^[p][f]
+  {
+    StageTimer t(h, pass, FBFFTCONV_STAGE_CONTRACT, s);
+    FBF_TRY(contract(h->buf_out(), h->buf_w(), h->buf_in(), h->bins, B, P, F,
+                     1.0f / (float)(h->N * h->N), 0, 0, simt, s));
+  }
+  {
+    StageTimer t(h, pass, FBFFTCONV_STAGE_IFFT, s);
+    FBF_CUDA(launch_inverse(inverse_params(h->buf_in(), grad_input, nullptr, B, P, d.input_h, d.input_w,
+                                           d.pad_h, d.pad_w, 0), h->N, s));
+  }
+  return FBFFTCONV_OK;
+}
+
+int fbfftconv_acc_grad_parameters(fbfftconv_handle* h, const float* input, const float* grad_output,
+                                  float* grad_weight, float* grad_bias, float scale,
+                                  fbfftconv_stream stream) {
+  if (!h || !input || !grad_output || !grad_weight)
+    return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "null argument");
+  DeviceGuard g;
+  FBF_CUDA(g.enter(h->device));
+  FBF_TRY(ensure_workspace(h));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const fbfftconv_desc& d = h->d;
+  const int B = d.batch, P = d.n_input_plane, F = d.n_output_plane;
+  const bool simt = d.flags & FBFFTCONV_CONTRACT_SIMT;
+  const int accumulate = (d.flags & FBFFTCONV_ACCUMULATE_GRADS) ? 1 : 0;
+  const int pass = FBFFTCONV_PASS_ACC_GRAD_PARAMETERS;
+  // O'^[bin][f][b], I^[bin][p][b]: the batch is the contraction index here
+  {
+    StageTimer t(h, pass, FBFFTCONV_STAGE_FFT_A, s);
+    FBF_CUDA(launch_forward(forward_params(grad_output, h->buf_out(), B, F, h->oH, h->oW, 0, 0, true), h->N, s));
+  }
+  {
+    StageTimer t(h, pass, FBFFTCONV_STAGE_FFT_B, s);
+    FBF_CUDA(launch_forward(forward_params(input, h->buf_in(), B, P, d.input_h, d.input_w, d.pad_h, d.pad_w, true), h->N, s));
+  }
+  NcclApi* api = h->comm ? nccl_api() : nullptr;
+  if (h->comm && !api) return fail(FBFFTCONV_ERR_COMM, "libnccl is not loadable");
+  if (grad_bias) {
+    StageTimer t(h, pass, FBFFTCONV_STAGE_BIAS, s);
+    // bin (0,0) of O'^[bin][f][b] is the plain sum of gradOutput plane (b, f): its real
+    // parts, summed over b, are the bias gradient (src/ConvolutionBias.cu:61-97).
+    const float* dc = reinterpret_cast<const float*>(h->buf_out());
+    const long long ld = 2LL * pad4(B);
+    float* tmp = h->small() + (size_t)B * F;
+    if (h->comm) {
+      FBF_CUDA(launch_row_sum(dc, tmp, F, B, ld, 2, scale, 0, s));
+      ncclResult_t r = api->AllReduce(tmp, tmp, (size_t)F, ncclFloat, ncclSum, h->comm, s);
+      if (r != ncclSuccess) return nccl_fail(api, r, "ncclAllReduce(gradBias)");
+      FBF_CUDA(launch_row_sum(tmp, grad_bias, F, 1, 1, 1, 1.0f, accumulate, s));
+    } else {
+      FBF_CUDA(launch_row_sum(dc, grad_bias, F, B, ld, 2, scale, accumulate, s));
+    }
+  }
+  // W'^[bin][f][p] = scale/N^2 sum_b conj(O'^[f][b]) I^[p][b]
+  {
+    StageTimer t(h, pass, FBFFTCONV_STAGE_CONTRACT, s);
+    FBF_TRY(contract(h->buf_out(), h->buf_in(), h->buf_w(), h->bins, F, P, B,
+                     scale / (float)(h->N * h->N), 1, 0, simt, s));
+  }
+  if (h->comm) {
+    StageTimer t(h, pass, FBFFTCONV_STAGE_ALLREDUCE, s);
+    const size_t count = (size_t)h->bins * F * pad4(P) * 2;
+    ncclResult_t r = api->AllReduce(h->buf_w(), h->buf_w(), count, ncclFloat, ncclSum, h->comm, s);
+    if (r != ncclSuccess) return nccl_fail(api, r, "ncclAllReduce(gradWeight spectrum)");
+  }
+  {
+    StageTimer t(h, pass, FBFFTCONV_STAGE_IFFT, s);
+    FBF_CUDA(launch_inverse(inverse_params(h->buf_w(), grad_weight, nullptr, F, P, d.kernel_h, d.kernel_w,
+                                           0, 0, accumulate), h->N, s));
+  }
+  return FBFFTCONV_OK;
+}
+
+// ---- host-buffer variants ----------------------------------------------------
+
+namespace {
+
+struct StageLayout {
+  size_t input, weight, bias, output, grad_bias, total;
+};
+
+StageLayout stage_layout(const fbfftconv_handle* h) {
+  const fbfftconv_desc& d = h->d;
+  StageLayout l;
+  const size_t in = align256((size_t)d.batch * d.n_input_plane * d.input_h * d.input_w * 4);
+  const size_t w = align256((size_t)d.n_output_plane * d.n_input_plane * d.kernel_h * d.kernel_w * 4);
+  const size_t b = align256((size_t)d.n_output_plane * 4);
+  const size_t o = align256((size_t)d.batch * d.n_output_plane * h->oH * h->oW * 4);
+  l.input = 0;
+  l.weight = in;
+  l.bias = in + w;
+  l.output = in + w + b;
+  l.grad_bias = in + w + b + o;
+  l.total = in + w + b + o + b;
+  return l;
+}
+
+int ensure_stage(fbfftconv_handle* h) {
+  if (h->stage) return FBFFTCONV_OK;
+  const StageLayout l = stage_layout(h);
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, l.total);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(FBFFTCONV_ERR_NOMEM, "staging of %zu bytes: %s", l.total, cudaGetErrorString(e));
+  }
+  h->stage = static_cast<char*>(p);
+  h->stage_bytes = l.total;
+  return FBFFTCONV_OK;
+}
+
+}  // namespace
+
+int fbfftconv_update_output_host(fbfftconv_handle* h, const float* input, const float* weight,
+                                 const float* bias, float* output, fbfftconv_stream stream) {
+  if (!h || !input || !weight || !output) return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "null argument");
+  DeviceGuard g;
+  FBF_CUDA(g.enter(h->device));
+  FBF_TRY(ensure_stage(h));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const fbfftconv_desc& d = h->d;
+  const StageLayout l = stage_layout(h);
+  float* din = reinterpret_cast<float*>(h->stage + l.input);
+  float* dw = reinterpret_cast<float*>(h->stage + l.weight);
+  float* db = reinterpret_cast<float*>(h->stage + l.bias);
+  float* dout = reinterpret_cast<float*>(h->stage + l.output);
+  const size_t n_in = (size_t)d.batch * d.n_input_plane * d.input_h * d.input_w;
+  const size_t n_w = (size_t)d.n_output_plane * d.n_input_plane * d.kernel_h * d.kernel_w;
+  const size_t n_out = (size_t)d.batch * d.n_output_plane * h->oH * h->oW;
+  FBF_CUDA(cudaMemcpyAsync(din, input, n_in * 4, cudaMemcpyHostToDevice, s));
+  FBF_CUDA(cudaMemcpyAsync(dw, weight, n_w * 4, cudaMemcpyHostToDevice, s));
+  if (bias) FBF_CUDA(cudaMemcpyAsync(db, bias, (size_t)d.n_output_plane * 4, cudaMemcpyHostToDevice, s));
+  FBF_TRY(fbfftconv_update_output(h, din, dw, bias ? db : nullptr, dout, stream));
+  FBF_CUDA(cudaMemcpyAsync(output, dout, n_out * 4, cudaMemcpyDeviceToHost, s));
+  FBF_CUDA(cudaStreamSynchronize(s));
+  return FBFFTCONV_OK;
+}
+
+int fbfftconv_update_grad_input_host(fbfftconv_handle* h, const float* grad_output,
+                                     const float* weight, float* grad_input, fbfftconv_stream stream) {
+  if (!h || !grad_output || !weight || !grad_input)
+    return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "null argument");
+  DeviceGuard g;
+  FBF_CUDA(g.enter(h->device));
+  FBF_TRY(ensure_stage(h));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const fbfftconv_desc& d = h->d;
+  const StageLayout l = stage_layout(h);
+  float* din = reinterpret_cast<float*>(h->stage + l.input);
+  float* dw = reinterpret_cast<float*>(h->stage + l.weight);
+  float* dout = reinterpret_cast<float*>(h->stage + l.output);
+  const size_t n_in = (size_t)d.batch * d.n_input_plane * d.input_h * d.input_w;
+  const size_t n_w = (size_t)d.n_output_plane * d.n_input_plane * d.kernel_h * d.kernel_w;
+  const size_t n_out = (size_t)d.batch * d.n_output_plane * h->oH * h->oW;
+  FBF_CUDA(cudaMemcpyAsync(dout, grad_output, n_out * 4, cudaMemcpyHostToDevice, s));
+  FBF_CUDA(cudaMemcpyAsync(dw, weight, n_w * 4, cudaMemcpyHostToDevice, s));
+  FBF_TRY(fbfftconv_update_grad_input(h, dout, dw, din, stream));
+  FBF_CUDA(cudaMemcpyAsync(grad_input, din, n_in * 4, cudaMemcpyDeviceToHost, s));
+  FBF_CUDA(cudaStreamSynchronize(s));
+  return FBFFTCONV_OK;
+}
+
+int fbfftconv_acc_grad_parameters_host(fbfftconv_handle* h, const float* input,
+                                       const float* grad_output, float* grad_weight,
+                                       float* grad_bias, float scale, fbfftconv_stream stream) {
+  if (!h || !input || !grad_output || !grad_weight)
+    return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "null argument");
+  DeviceGuard g;
+  FBF_CUDA(g.enter(h->device));
+  FBF_TRY(ensure_stage(h));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const fbfftconv_desc& d = h->d;
+  const StageLayout l = stage_layout(h);
+  float* din = reinterpret_cast<float*>(h->stage + l.input);
+  float* dw = reinterpret_cast<float*>(h->stage + l.weight);
+  float* dgb = reinterpret_cast<float*>(h->stage + l.grad_bias);
+  float* dout = reinterpret_cast<float*>(h->stage + l.output);
+  const size_t n_in = (size_t)d.batch * d.n_input_plane * d.input_h * d.input_w;
+  const size_t n_w = (size_t)d.n_output_plane * d.n_input_plane * d.kernel_h * d.kernel_w;
+  const size_t n_out = (size_t)d.batch * d.n_output_plane * h->oH * h->oW;
+  const bool accumulate = d.flags & FBFFTCONV_ACCUMULATE_GRADS;
+  FBF_CUDA(cudaMemcpyAsync(din, input, n_in * 4, cudaMemcpyHostToDevice, s));
+  FBF_CUDA(cudaMemcpyAsync(dout, grad_output, n_out * 4, cudaMemcpyHostToDevice, s));
+  if (accumulate) {
+    FBF_CUDA(cudaMemcpyAsync(dw, grad_weight, n_w * 4, cudaMemcpyHostToDevice, s));
+    if (grad_bias) FBF_CUDA(cudaMemcpyAsync(dgb, grad_bias, (size_t)d.n_output_plane * 4, cudaMemcpyHostToDevice, s));
+  }
+  FBF_TRY(fbfftconv_acc_grad_parameters(h, din, dout, dw, grad_bias ? dgb : nullptr, scale, stream));
+  FBF_CUDA(cudaMemcpyAsync(grad_weight, dw, n_w * 4, cudaMemcpyDeviceToHost, s));
+  if (grad_bias) FBF_CUDA(cudaMemcpyAsync(grad_bias, dgb, (size_t)d.n_output_plane * 4, cudaMemcpyDeviceToHost, s));
+  FBF_CUDA(cudaStreamSynchronize(s));
+  return FBFFTCONV_OK;
+}
+
+// ---- sub-steps ---------------------------------------------------------------
+
+int fbfftconv_fft2d(const float* real, void* spectrum, int d1, int d2, int h, int w, int fft_size,
+                    int pad_u, int pad_l, int transposed, fbfftconv_stream stream) {
+  if (!real || !spectrum) return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "null argument");
+  if (!valid_fft_size(fft_size)) return fail(FBFFTCONV_ERR_UNSUPPORTED_SIZE, "transform size %d not in {8,16,32,64,128}", fft_size);
+  if (d1 <= 0 || d2 <= 0 || h <= 0 || w <= 0 || pad_u < 0 || pad_l < 0 || h + pad_u > fft_size ||
+      w + pad_l > fft_size || d1 > 65535 || d2 > 65535)
+    return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "plane of %dx%d at (%d,%d) does not fit %d", h, w, pad_u, pad_l, fft_size);
+  FBF_CUDA(launch_forward(forward_params(real, static_cast<float2*>(spectrum), d1, d2, h, w, pad_u, pad_l, transposed != 0),
+                          fft_size, static_cast<cudaStream_t>(stream)));
+  return FBFFTCONV_OK;
+}
+
+int fbfftconv_ifft2d(const void* spectrum, float* real, const float* bias, int d1, int d2, int h,
+                     int w, int fft_size, int off_y, int off_x, int accumulate,
+                     fbfftconv_stream stream) {
+  if (!real || !spectrum) return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "null argument");
+  if (!valid_fft_size(fft_size)) return fail(FBFFTCONV_ERR_UNSUPPORTED_SIZE, "transform size %d not in {8,16,32,64,128}", fft_size);
+  if (d1 <= 0 || d2 <= 0 || h <= 0 || w <= 0 || off_y < 0 || off_x < 0 || h + off_y > fft_size ||
+      w + off_x > fft_size || d1 > 65535 || d2 > 65535)
+    return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "window of %dx%d at (%d,%d) does not fit %d", h, w, off_y, off_x, fft_size);
+  FBF_CUDA(launch_inverse(inverse_params(static_cast<const float2*>(spectrum), real, bias, d1, d2, h, w, off_y, off_x, accumulate != 0),
+                          fft_size, static_cast<cudaStream_t>(stream)));
+  return FBFFTCONV_OK;
+}
+
+int fbfftconv_transpose_mm(const void* a, const void* b, void* c, int bins, int m, int n, int k,
+                           float alpha, int conj_a, int conj_b, int use_simt,
+                           fbfftconv_stream stream) {
+  if (!a || !b || !c) return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "null argument");
+  if (bins <= 0 || m <= 0 || n <= 0 || k <= 0 || bins > 65535)
+    return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "bad contraction sizes");
+  return contract(static_cast<const float2*>(a), static_cast<const float2*>(b), static_cast<float2*>(c),
+                  bins, m, n, k, alpha, conj_a != 0, conj_b != 0, use_simt != 0,
+                  static_cast<cudaStream_t>(stream));
+}
+
+int fbfftconv_update_output_bias(float* output, const float* bias, int batch, int planes, int h,
+                                 int w, fbfftconv_stream stream) {
+  if (!output || !bias || batch <= 0 || planes <= 0 || h <= 0 || w <= 0)
+    return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "bad bias arguments");
+  FBF_CUDA(launch_bias_add(output, bias, batch, planes, h * w, static_cast<cudaStream_t>(stream)));
+  return FBFFTCONV_OK;
+}
+
+int fbfftconv_acc_grad_parameters_bias(const float* grad_output, float* grad_bias, float* scratch,
+                                       int batch, int planes, int h, int w, float scale,
+                                       int accumulate, fbfftconv_stream stream) {
+  if (!grad_output || !grad_bias || !scratch || batch <= 0 || planes <= 0 || h <= 0 || w <= 0 || batch > 65535)
+    return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "bad bias-gradient arguments");
+  FBF_CUDA(launch_bias_grad(grad_output, grad_bias, scratch, batch, planes, h * w, scale, accumulate != 0,
+                            static_cast<cudaStream_t>(stream)));
+  return FBFFTCONV_OK;
+}
+
+// ---- per-kernel timing ---------------------------------------------------------
+
+int fbfftconv_profile_enable(fbfftconv_handle* h, int enable) {
+  if (!h) return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "null handle");
+  h->profiling = enable != 0;
+  return FBFFTCONV_OK;
+}
+
+int fbfftconv_profile_reset(fbfftconv_handle* h) {
+  if (!h) return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "null handle");
+  memset(h->events_used, 0, sizeof(h->events_used));
+  return FBFFTCONV_OK;
+}
+
+int fbfftconv_profile_read(fbfftconv_handle* h, int pass, int stage, double* total_ms, int* launches) {
+  if (!h || pass < 0 || pass > 2 || stage < 0 || stage >= FBFFTCONV_STAGE_COUNT || !total_ms || !launches)
+    return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "bad profile query");
+  DeviceGuard g;
+  FBF_CUDA(g.enter(h->device));
+  double sum = 0.0;
+  const int n = h->events_used[pass][stage];
+  for (int i = 0; i < n; ++i) {
+    const EventPair& p = h->events[pass][stage][i];
+    FBF_CUDA(cudaEventSynchronize(p.stop));
+    float ms = 0.f;
+    FBF_CUDA(cudaEventElapsedTime(&ms, p.start, p.stop));
+    sum += ms;
+  }
+  *total_ms = sum;
+  *launches = n;
+  return FBFFTCONV_OK;
+}
+
+// ---- communicator ------------------------------------------------------------
+
+int fbfftconv_comm_unique_id(void* id128) {
+  if (!id128) return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "null id");
+  NcclApi* api = nccl_api();
+  if (!api) return fail(FBFFTCONV_ERR_COMM, "libnccl is not loadable: %s", dlerror());
+  static_assert(sizeof(ncclUniqueId) == 128, "ncclUniqueId is 128 bytes");
+  ncclUniqueId id;
+  ncclResult_t r = api->GetUniqueId(&id);
+  if (r != ncclSuccess) return nccl_fail(api, r, "ncclGetUniqueId");
+  memcpy(id128, &id, sizeof(id));
+  return FBFFTCONV_OK;
+}
+
+int fbfftconv_comm_init(fbfftconv_handle* h, const void* id128, int rank, int nranks) {
+  if (!h || !id128 || nranks <= 0 || rank < 0 || rank >= nranks)
+    return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "bad communicator arguments");
+  NcclApi* api = nccl_api();
+  if (!api) return fail(FBFFTCONV_ERR_COMM, "libnccl is not loadable: %s", dlerror());
+  DeviceGuard g;
+  FBF_CUDA(g.enter(h->device));
+  if (h->comm) {
+    api->CommDestroy(h->comm);
+    h->comm = nullptr;
+  }
+  ncclUniqueId id;
+  memcpy(&id, id128, sizeof(id));
+  ncclResult_t r = api->CommInitRank(&h->comm, nranks, id, rank);
+  if (r != ncclSuccess) {
+    h->comm = nullptr;
+    return nccl_fail(api, r, "ncclCommInitRank");
+  }
+  h->rank = rank;
+  h->nranks = nranks;
+  return FBFFTCONV_OK;
+}
+
+int fbfftconv_comm_destroy(fbfftconv_handle* h) {
+  if (!h || !h->comm) return FBFFTCONV_OK;
+  NcclApi* api = nccl_api();
+  if (api) {
+    DeviceGuard g;
+    g.enter(h->device);
+    api->CommDestroy(h->comm);
+  }
+  h->comm = nullptr;
+  h->nranks = 1;
+  h->rank = 0;
+  return FBFFTCONV_OK;
+}
+
+}  // extern "C"

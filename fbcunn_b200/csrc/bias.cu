@@ -1,0 +1,85 @@
+// Bias kernels (sm_100a).  The forward bias add is normally fused into the inverse
+// FFT's store; the stand-alone kernels here back the entry points that mirror the
+// reference's updateOutputBiasFFI / accGradParametersBiasFFI
+// (src/ConvolutionBias.cu:39-51, :61-97).
+#include "kernels.h"
+
+namespace fbfft {
+
+namespace {
+
+__global__ void bias_add_kernel(float* out, const float* __restrict__ bias, int planes, int hw,
+                                long long total) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int f = (int)((i / hw) % planes);
+    out[i] += bias[f];
+  }
+}
+
+__device__ __forceinline__ float block_sum(float v) {
+  __shared__ float warp_part[32];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) warp_part[warp] = v;
+  __syncthreads();
+  const int nwarps = (blockDim.x + 31) >> 5;
+  v = (threadIdx.x < nwarps) ? warp_part[threadIdx.x] : 0.f;
+  if (warp == 0) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  }
+  return v;  // valid in thread 0
+}
+
+// scratch[f * batch + b] = sum of plane (b, f)
+__global__ void __launch_bounds__(256)
+plane_sum_kernel(const float* __restrict__ grad_out, float* scratch, int batch, int planes, int hw) {
+  const int f = blockIdx.x, b = blockIdx.y;
+  const float* src = grad_out + ((long long)b * planes + f) * hw;
+  float v = 0.f;
+  for (int i = threadIdx.x; i < hw; i += blockDim.x) v += src[i];
+  v = block_sum(v);
+  if (threadIdx.x == 0) scratch[(long long)f * batch + b] = v;
+}
+
+// grad_bias[f] (=|+=) scale * sum_b src[f * ld + b * step]
+__global__ void __launch_bounds__(128)
+row_sum_kernel(const float* __restrict__ src, float* grad_bias, int batch, long long ld, int step,
+               float scale, int accumulate) {
+  const int f = blockIdx.x;
+  float v = 0.f;
+  for (int b = threadIdx.x; b < batch; b += blockDim.x) v += src[(long long)f * ld + (long long)b * step];
+  v = block_sum(v);
+  if (threadIdx.x == 0) grad_bias[f] = accumulate ? grad_bias[f] + scale * v : scale * v;
+}
+
+}  // namespace
+
+cudaError_t launch_bias_add(float* out, const float* bias, int batch, int planes, int hw,
+                            cudaStream_t stream) {
+  const long long total = (long long)batch * planes * hw;
+  const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  bias_add_kernel<<<blocks > 0 ? blocks : 1, 256, 0, stream>>>(out, bias, planes, hw, total);
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t launch_bias_grad(const float* grad_out, float* grad_bias, float* scratch, int batch,
+                             int planes, int hw, float scale, int accumulate, cudaStream_t stream) {
+  if (batch > 65535) return cudaErrorInvalidValue;
+  plane_sum_kernel<<<dim3(planes, batch), 256, 0, stream>>>(grad_out, scratch, batch, planes, hw);
+  row_sum_kernel<<<planes, 128, 0, stream>>>(scratch, grad_bias, batch, batch, 1, scale, accumulate);
+  count_launch(2);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_row_sum(const float* src, float* dst, int rows, int count, long long ld, int step,
+                           float scale, int accumulate, cudaStream_t stream) {
+  row_sum_kernel<<<rows, 128, 0, stream>>>(src, dst, count, ld, step, scale, accumulate);
+  count_launch();
+  return cudaGetLastError();
+}
+
+}  // namespace fbfft

@@ -1,0 +1,157 @@
+// Batched 2-D R2C / C2R FFT kernels (sm_100a): one thread block transforms a tile
+// of T planes that are neighbours in the spectrum's innermost index, entirely in
+// shared memory and registers, and writes / reads the bin-major spectrum in runs of
+// T complex values.  Phases and index arithmetic live in fft_core.cuh.
+//
+// Stands where the reference launches fbfft2D / fbifft2D
+// (src/fft/FBFFTHost.cpp:84-111); unlike the reference's sizes 64 and 128
+// (two launches through a transposed global buffer, :56-104) every size is a
+// single launch with no global scratch.
+#include <atomic>
+
+#include "kernels.h"
+
+namespace fbfft {
+
+namespace {
+
+std::atomic<uint64_t> g_launches{0};
+
+template <int N, int T>
+constexpr int block_threads() {
+  return ((N / 2 + 1) * T + 31) / 32 * 32 < 64 ? 64 : ((N / 2 + 1) * T + 31) / 32 * 32;
+}
+
+template <int N, int T>
+__global__ void __launch_bounds__(block_threads<N, T>())
+fft2d_forward_kernel(const __grid_constant__ FftParams p, const __grid_constant__ FftGeom g) {
+  extern __shared__ __align__(16) char smem[];
+  const int tid = threadIdx.x;
+  const int row = blockIdx.y;
+  const int inner0 = blockIdx.x * T;
+  Forward<N, T>::load(p, g, smem, tid, blockDim.x, row, inner0);
+  __syncthreads();
+  LineRegs<N> regs;
+  Forward<N, T>::row_fetch(g, smem, tid, regs);
+  if (N <= 32) __syncthreads();  // the column buffer aliases the row buffer
+  Forward<N, T>::row_pass(g, smem, tid, regs);
+  __syncthreads();
+  Forward<N, T>::col_pass(p, g, smem, tid, row, inner0);
+}
+
+template <int N, int T>
+__global__ void __launch_bounds__(block_threads<N, T>())
+fft2d_inverse_kernel(const __grid_constant__ FftParams p, const __grid_constant__ FftGeom g) {
+  extern __shared__ __align__(16) char smem[];
+  const int tid = threadIdx.x;
+  const int row = blockIdx.y;
+  const int inner0 = blockIdx.x * T;
+  Inverse<N, T>::col_pass(p, g, smem, tid, row, inner0);
+  __syncthreads();
+  LineRegs<N> regs;
+  Inverse<N, T>::row_fetch(g, smem, tid, regs);
+  __syncthreads();  // the staged output aliases the column buffer
+  Inverse<N, T>::row_pass(p, g, smem, tid, regs);
+  __syncthreads();
+  Inverse<N, T>::store(p, g, smem, tid, blockDim.x, row, inner0);
+}
+
+constexpr int kSmemMax = 227 * 1024;
+constexpr int kSmemTwoBlocks = 113 * 1024;
+
+constexpr bool tile_allowed(int N, int T) { return (N / 2 + 1) * T <= 512; }
+
+template <class GeomFn>
+int pick_tile(int N, GeomFn geom) {
+  int best_any = 0;
+  for (int T = 16; T >= 1; T >>= 1) {
+    if (!tile_allowed(N, T)) continue;
+    const int bytes = geom(T).smem_bytes;
+    if (bytes <= kSmemTwoBlocks) return T;
+    if (bytes <= kSmemMax && best_any == 0) best_any = T;
+  }
+  return best_any;
+}
+
+template <int N, int T>
+cudaError_t run_forward(const FftParams& p, cudaStream_t stream) {
+  if constexpr (!tile_allowed(N, T)) {
+    return cudaErrorInvalidConfiguration;
+  } else {
+    const FftGeom g = forward_geom(N, T, p.h, p.w, p.off_y, p.off_x);
+    if (g.threads != block_threads<N, T>()) return cudaErrorInvalidConfiguration;
+    auto kernel = fft2d_forward_kernel<N, T>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, g.smem_bytes);
+    if (e != cudaSuccess) return e;
+    dim3 grid((p.kc + T - 1) / T, p.n_rows);
+    kernel<<<grid, g.threads, g.smem_bytes, stream>>>(p, g);
+    count_launch();
+    return cudaGetLastError();
+  }
+}
+
+template <int N, int T>
+cudaError_t run_inverse(const FftParams& p, cudaStream_t stream) {
+  if constexpr (!tile_allowed(N, T)) {
+    return cudaErrorInvalidConfiguration;
+  } else {
+    const FftGeom g = inverse_geom(N, T, p.h, p.w);
+    if (g.threads != block_threads<N, T>()) return cudaErrorInvalidConfiguration;
+    auto kernel = fft2d_inverse_kernel<N, T>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, g.smem_bytes);
+    if (e != cudaSuccess) return e;
+    dim3 grid((p.n_inner + T - 1) / T, p.n_rows);
+    kernel<<<grid, g.threads, g.smem_bytes, stream>>>(p, g);
+    count_launch();
+    return cudaGetLastError();
+  }
+}
+
+template <int N>
+cudaError_t dispatch_tile(bool inverse, const FftParams& p, int T, cudaStream_t s) {
+  switch (T) {
+    case 1: return inverse ? run_inverse<N, 1>(p, s) : run_forward<N, 1>(p, s);
+    case 2: return inverse ? run_inverse<N, 2>(p, s) : run_forward<N, 2>(p, s);
+    case 4: return inverse ? run_inverse<N, 4>(p, s) : run_forward<N, 4>(p, s);
+    case 8: return inverse ? run_inverse<N, 8>(p, s) : run_forward<N, 8>(p, s);
+    case 16: return inverse ? run_inverse<N, 16>(p, s) : run_forward<N, 16>(p, s);
+  }
+  return cudaErrorInvalidConfiguration;
+}
+
+cudaError_t dispatch(bool inverse, const FftParams& p, int N, int T, cudaStream_t s) {
+  switch (N) {
+    case 8: return dispatch_tile<8>(inverse, p, T, s);
+    case 16: return dispatch_tile<16>(inverse, p, T, s);
+    case 32: return dispatch_tile<32>(inverse, p, T, s);
+    case 64: return dispatch_tile<64>(inverse, p, T, s);
+    case 128: return dispatch_tile<128>(inverse, p, T, s);
+  }
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace
+
+void count_launch(int n) { g_launches.fetch_add(static_cast<uint64_t>(n), std::memory_order_relaxed); }
+uint64_t launch_count() { return g_launches.load(std::memory_order_relaxed); }
+
+int pick_forward_tile(int N, int h, int w, int pad_u, int pad_l) {
+  return pick_tile(N, [&](int T) { return forward_geom(N, T, h, w, pad_u, pad_l); });
+}
+int pick_inverse_tile(int N, int oh, int ow) {
+  return pick_tile(N, [&](int T) { return inverse_geom(N, T, oh, ow); });
+}
+
+cudaError_t launch_forward(const FftParams& p, int N, cudaStream_t stream) {
+  const int T = pick_forward_tile(N, p.h, p.w, p.off_y, p.off_x);
+  if (T == 0 || p.n_rows > 65535) return cudaErrorInvalidConfiguration;
+  return dispatch(false, p, N, T, stream);
+}
+
+cudaError_t launch_inverse(const FftParams& p, int N, cudaStream_t stream) {
+  const int T = pick_inverse_tile(N, p.h, p.w);
+  if (T == 0 || p.n_rows > 65535) return cudaErrorInvalidConfiguration;
+  return dispatch(true, p, N, T, stream);
+}
+
+}  // namespace fbfft

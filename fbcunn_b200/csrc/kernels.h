@@ -1,0 +1,41 @@
+// Internal launch interface between the C ABI (api.cu) and the kernel files.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "fft_core.cuh"
+
+namespace fbfft {
+
+// Counts every kernel this library launches (reported through the C ABI).
+void count_launch(int n = 1);
+uint64_t launch_count();
+
+// Largest plane tile (planes per block) whose shared memory fits, preferring two
+// resident blocks per SM; 0 when even one plane does not fit.
+int pick_forward_tile(int N, int h, int w, int pad_u, int pad_l);
+int pick_inverse_tile(int N, int oh, int ow);
+
+cudaError_t launch_forward(const FftParams& p, int N, cudaStream_t stream);
+cudaError_t launch_inverse(const FftParams& p, int N, cudaStream_t stream);
+
+struct ContractParams {
+  const float2* a;   // [bins][m][lda]
+  const float2* b;   // [bins][n][ldb]
+  float2* c;         // [bins][m][ldc]
+  int bins, m, n, k; // k counts valid complex columns; lda/ldb >= k, zero padded
+  int lda, ldb, ldc; // multiples of 4
+  float alpha;
+  int conj_a, conj_b;
+};
+cudaError_t launch_contract_simt(const ContractParams& p, cudaStream_t stream);
+
+cudaError_t launch_bias_add(float* out, const float* bias, int batch, int planes, int hw,
+                            cudaStream_t stream);
+cudaError_t launch_bias_grad(const float* grad_out, float* grad_bias, float* scratch, int batch,
+                             int planes, int hw, float scale, int accumulate, cudaStream_t stream);
+// dst[r] (=|+=) scale * sum_{i<count} src[r*ld + i*step]
+cudaError_t launch_row_sum(const float* src, float* dst, int rows, int count, long long ld, int step,
+                           float scale, int accumulate, cudaStream_t stream);
+
+}  // namespace fbfft

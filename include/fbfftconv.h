@@ -1,0 +1,200 @@
+/*
+ * fbfftconv -- C ABI of the B200 (sm_100a) FFT spatial convolution.
+ *
+ * A plain-C boundary (raw device pointers, sizes, a CUDA stream, an int status)
+ * that stands where the reference's Torch7 bindings for nn.SpatialConvolutionFBFFT
+ * stand.  Each entry point names the reference interface it replaces (paths are
+ * relative to the reference checkout).
+ *
+ * Conventions
+ *   - all tensors are fp32, contiguous, NCHW, on the handle's device, 4-byte aligned
+ *       input       (batch, nInputPlane,  iH, iW)
+ *       weight      (nOutputPlane, nInputPlane, kH, kW)
+ *       bias        (nOutputPlane)
+ *       output      (batch, nOutputPlane, oH, oW),  oH = iH + 2*padH - kH + 1
+ *   - stride is 1 and padding symmetric, as the reference module requires
+ *     (fbcunn/SpatialConvolutionFBFFT.lua:60-61, fbcunn/SpatialConvolutionFFT.lua:171-174)
+ *   - every call returns FBFFTCONV_OK or an error code; nothing throws or aborts.
+ *     fbfftconv_last_error() gives the message of the calling thread's last failure.
+ *   - work is enqueued on the caller's stream and is asynchronous to the host.
+ *   - a handle is used by one host thread at a time.
+ *   - there is no CPU or library fallback: without a CUDA device every compute entry
+ *     point returns FBFFTCONV_ERR_CUDA.
+ */
+#ifndef FBFFTCONV_H_
+#define FBFFTCONV_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct fbfftconv_handle fbfftconv_handle;
+typedef void* fbfftconv_stream; /* cudaStream_t */
+
+enum {
+  FBFFTCONV_OK = 0,
+  FBFFTCONV_ERR_INVALID_ARGUMENT = 1,
+  FBFFTCONV_ERR_UNSUPPORTED_SIZE = 2, /* transform larger than 128 (reference: src/fft/FBFFTHost.cpp:96-98,115) */
+  FBFFTCONV_ERR_NOMEM = 3,
+  FBFFTCONV_ERR_CUDA = 4,
+  FBFFTCONV_ERR_COMM = 5
+};
+
+/* flags of fbfftconv_desc */
+enum {
+  /* accGradParameters adds into gradWeight / gradBias (the nn.Module contract).
+   * Default (flag clear) overwrites them, which is what the reference does:
+   * fbcunn/SpatialConvolutionFBFFT.lua:337-349, src/ConvolutionBias.cu:95. */
+  FBFFTCONV_ACCUMULATE_GRADS = 1,
+  /* contraction on the CUDA cores in plain fp32 instead of the tensor cores */
+  FBFFTCONV_CONTRACT_SIMT = 2
+};
+
+/* Constructor arguments of nn.SpatialConvolutionFBFFT
+ * (fbcunn/SpatialConvolutionFBFFT.lua:26-35) plus the sizes the Lua module reads
+ * from its first input. */
+typedef struct fbfftconv_desc {
+  int32_t batch;
+  int32_t n_input_plane;
+  int32_t n_output_plane;
+  int32_t input_h, input_w;
+  int32_t kernel_h, kernel_w;
+  int32_t stride_h, stride_w; /* must be 1 */
+  int32_t pad_h, pad_w;       /* padUp, padLeft; must be smaller than the kernel */
+  int32_t device;             /* CUDA device ordinal, -1 = current device */
+  uint32_t flags;
+} fbfftconv_desc;
+
+/* ---- lifetime ------------------------------------------------------------ */
+
+/* Replaces nn.SpatialConvolutionFBFFT:__init plus prepareFBFFTSizeAndBuffers
+ * (fbcunn/SpatialConvolutionFBFFT.lua:26-100, fbcunn/SpatialConvolutionFFT.lua:947-964):
+ * validates the arguments, picks the square power-of-two transform size and sizes
+ * the three frequency buffers.  Allocates no device memory yet. */
+int fbfftconv_create(const fbfftconv_desc* desc, fbfftconv_handle** out);
+/* Replaces cleanupBuffers (fbcunn/SpatialConvolutionFFT.lua:852-870). */
+int fbfftconv_destroy(fbfftconv_handle* h);
+
+/* Transform size N chosen for the layer (fbcunn/SpatialConvolutionFFT.lua:875-882). */
+int fbfftconv_fft_size(const fbfftconv_handle* h);
+/* Bytes of device scratch the three passes need (the reference's inputBuffer /
+ * outputBuffer / weightBuffer, fbcunn/SpatialConvolutionFFT.lua:652-688). */
+size_t fbfftconv_workspace_bytes(const fbfftconv_handle* h);
+/* Optional: hand the library a caller-owned scratch block of at least
+ * fbfftconv_workspace_bytes(); otherwise it is allocated with cudaMalloc on the
+ * first pass and freed by fbfftconv_destroy. */
+int fbfftconv_set_workspace(fbfftconv_handle* h, void* device_ptr, size_t bytes);
+
+/* ---- the three nn passes, device pointers ----------------------------------- */
+
+/* Replaces SpatialConvolutionFBFFT:updateOutputFFTImpl
+ * (fbcunn/SpatialConvolutionFBFFT.lua:102-183): FFT(input), FFT(weight),
+ * transposeMMFFI(.., conjB), inverse FFT, updateOutputBiasFFI.  bias may be NULL
+ * (the reference's metaData.skipBias, :172). */
+int fbfftconv_update_output(fbfftconv_handle* h, const float* input, const float* weight,
+                            const float* bias, float* output, fbfftconv_stream stream);
+/* Replaces updateGradInputFFTImpl (fbcunn/SpatialConvolutionFBFFT.lua:189-263). */
+int fbfftconv_update_grad_input(fbfftconv_handle* h, const float* grad_output, const float* weight,
+                                float* grad_input, fbfftconv_stream stream);
+/* Replaces accGradParametersFFTImpl (fbcunn/SpatialConvolutionFBFFT.lua:269-354),
+ * including accGradParametersBiasFFI.  grad_bias may be NULL (skipBias, :298).
+ * With a communicator attached the frequency-domain weight gradient is summed over
+ * all ranks before the inverse transform, and so is grad_bias. */
+int fbfftconv_acc_grad_parameters(fbfftconv_handle* h, const float* input, const float* grad_output,
+                                  float* grad_weight, float* grad_bias, float scale,
+                                  fbfftconv_stream stream);
+
+/* ---- the same passes with HOST buffers --------------------------------------
+ * Copies the operands to the device, runs the pass and copies the result back on
+ * `stream`, then waits for it.  Pinned host memory makes the copies asynchronous;
+ * pageable memory works too.  These stand for a Torch7 caller that keeps its
+ * tensors on the host and moves them per call. */
+int fbfftconv_update_output_host(fbfftconv_handle* h, const float* input, const float* weight,
+                                 const float* bias, float* output, fbfftconv_stream stream);
+int fbfftconv_update_grad_input_host(fbfftconv_handle* h, const float* grad_output,
+                                     const float* weight, float* grad_input, fbfftconv_stream stream);
+int fbfftconv_acc_grad_parameters_host(fbfftconv_handle* h, const float* input,
+                                       const float* grad_output, float* grad_weight,
+                                       float* grad_bias, float scale, fbfftconv_stream stream);
+
+/* ---- the sub-steps, for callers and tests that drive them one by one --------- */
+
+/* Frequency buffers are complex fp32 laid out [bin][row][inner_padded] with
+ * bin = kx*N + ky, kx in [0, N/2], ky in [0, N): bin-major, plane index innermost,
+ * inner_padded = inner rounded up to a multiple of 4 (padding is written as zero). */
+size_t fbfftconv_spectrum_bytes(int fft_size, int rows, int inner);
+
+/* Replaces FFTWrapper_fft for the 2-D batched case (src/fft/FFTWrapperLua.cpp:209-272,
+ * src/fft/FBFFTHost.cpp:39-116): real (d1, d2, h, w) placed at (pad_u, pad_l) of an
+ * N x N zero square -> half spectrum.  transposed == 0 writes [bin][d1][d2],
+ * transposed != 0 writes [bin][d2][d1]. */
+int fbfftconv_fft2d(const float* real, void* spectrum, int d1, int d2, int h, int w, int fft_size,
+                    int pad_u, int pad_l, int transposed, fbfftconv_stream stream);
+/* Replaces FFTWrapper_ffti (src/fft/FFTWrapperLua.cpp:209-272): un-normalised inverse
+ * of spectrum [bin][d1][d2], cropped to the h x w window whose corner is (off_y, off_x).
+ * bias (d2 values, may be NULL) is added to every element of plane (., j);
+ * accumulate != 0 adds into `real` instead of overwriting. */
+int fbfftconv_ifft2d(const void* spectrum, float* real, const float* bias, int d1, int d2, int h,
+                     int w, int fft_size, int off_y, int off_x, int accumulate,
+                     fbfftconv_stream stream);
+/* Replaces transposeMMFFI (fbcunn/FFTCDefs.lua:7-14, src/MM.cu:54-73) on bin-major
+ * operands: for every bin  C[m][n] = alpha * sum_k opA(A[m][k]) * opB(B[n][k]),
+ * op = complex conjugate when the flag is set.  A is [bins][m][k_padded],
+ * B [bins][n][k_padded], C [bins][m][n_padded].  use_simt != 0 forces the fp32
+ * CUDA-core kernel. */
+int fbfftconv_transpose_mm(const void* a, const void* b, void* c, int bins, int m, int n, int k,
+                           float alpha, int conj_a, int conj_b, int use_simt,
+                           fbfftconv_stream stream);
+/* Replaces updateOutputBiasFFI (fbcunn/FFTCDefs.lua:4, src/ConvolutionBias.cu:39-51). */
+int fbfftconv_update_output_bias(float* output, const float* bias, int batch, int planes, int h,
+                                 int w, fbfftconv_stream stream);
+/* Replaces accGradParametersBiasFFI (fbcunn/FFTCDefs.lua:5-6, src/ConvolutionBias.cu:61-97):
+ * grad_bias[f] (=, or += when accumulate != 0) scale * sum grad_output[:, f, :, :].
+ * scratch must hold batch*planes floats. */
+int fbfftconv_acc_grad_parameters_bias(const float* grad_output, float* grad_bias, float* scratch,
+                                       int batch, int planes, int h, int w, float scale,
+                                       int accumulate, fbfftconv_stream stream);
+
+/* ---- multi-GPU: one process per GPU ------------------------------------------
+ * Replaces the gather / add / broadcast of nn.DataParallel
+ * (fbcunn/DataParallel.lua:105-131) by one NCCL all-reduce over NVLink.  Rank 0
+ * makes an id, every rank gets the same 128 bytes (by any side channel) and calls
+ * fbfftconv_comm_init.  libnccl is loaded at run time on the first of these calls. */
+int fbfftconv_comm_unique_id(void* id128);
+int fbfftconv_comm_init(fbfftconv_handle* h, const void* id128, int rank, int nranks);
+int fbfftconv_comm_destroy(fbfftconv_handle* h);
+
+/* ---- per-kernel timing ---------------------------------------------------------
+ * With profiling enabled every kernel (and collective) a pass enqueues is bracketed
+ * by a pair of CUDA events on the caller's stream; fbfftconv_profile_read waits for
+ * them and returns the summed device time and the number of launches of one stage of
+ * one pass since the last reset.  Stands where the reference wraps its FFT and GEMM
+ * calls in cuda::KernelTimer (src/fft/FFTWrapperLua.cpp:52-66,
+ * src/CuBLASWrapperLua.cpp:90-108). */
+enum { FBFFTCONV_PASS_UPDATE_OUTPUT = 0, FBFFTCONV_PASS_UPDATE_GRAD_INPUT = 1, FBFFTCONV_PASS_ACC_GRAD_PARAMETERS = 2 };
+enum {
+  FBFFTCONV_STAGE_FFT_A = 0,     /* first forward transform: input / gradOutput / gradOutput */
+  FBFFTCONV_STAGE_FFT_B = 1,     /* second forward transform: weight / weight / input */
+  FBFFTCONV_STAGE_CONTRACT = 2,  /* per-bin complex contraction */
+  FBFFTCONV_STAGE_ALLREDUCE = 3, /* NCCL sum of the weight-gradient spectrum */
+  FBFFTCONV_STAGE_IFFT = 4,      /* inverse transform + crop (+ bias) */
+  FBFFTCONV_STAGE_BIAS = 5,      /* bias-gradient reduction */
+  FBFFTCONV_STAGE_COUNT = 6
+};
+int fbfftconv_profile_enable(fbfftconv_handle* h, int enable);
+int fbfftconv_profile_reset(fbfftconv_handle* h);
+int fbfftconv_profile_read(fbfftconv_handle* h, int pass, int stage, double* total_ms, int* launches);
+
+/* ---- diagnostics ------------------------------------------------------------ */
+const char* fbfftconv_last_error(void);
+const char* fbfftconv_status_string(int status);
+/* Number of kernels this library has launched from the calling process so far. */
+uint64_t fbfftconv_kernel_launches(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FBFFTCONV_H_ */

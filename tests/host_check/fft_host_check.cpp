@@ -1,0 +1,130 @@
+// Host harness for the FFT kernel phases -- TEST INFRASTRUCTURE ONLY.
+// Compiles fbcunn_b200/csrc/fft_core.cuh as plain C++ and runs each thread block as
+// loops over thread indices, phase by phase, with shared memory pre-filled with NaN
+// so that a read of an unwritten slot shows up in the result.  Checks the index
+// arithmetic of the kernels without a GPU; it is never part of the product path.
+#include <cstring>
+#include <limits>
+#include <vector>
+
+#include "../../fbcunn_b200/csrc/fft_core.cuh"
+
+using namespace fbfft;
+
+namespace {
+
+template <int N, int T>
+void run_forward(const FftParams& p) {
+  const FftGeom g = forward_geom(N, T, p.h, p.w, p.off_y, p.off_x);
+  const int tiles = (p.kc + T - 1) / T;
+  std::vector<char> smem(g.smem_bytes);
+  std::vector<LineRegs<N>> regs(g.threads);
+  for (int row = 0; row < p.n_rows; ++row) {
+    for (int tile = 0; tile < tiles; ++tile) {
+      const int inner0 = tile * T;
+      std::memset(smem.data(), 0xFF, smem.size());
+      for (int tid = 0; tid < g.threads; ++tid)
+        Forward<N, T>::load(p, g, smem.data(), tid, g.threads, row, inner0);
+      for (int tid = 0; tid < g.threads; ++tid)
+        Forward<N, T>::row_fetch(g, smem.data(), tid, regs[tid]);
+      if (!two_step(N)) std::memset(smem.data(), 0xFF, smem.size());  // aliasing: A is dead now
+      for (int tid = 0; tid < g.threads; ++tid)
+        Forward<N, T>::row_pass(g, smem.data(), tid, regs[tid]);
+      for (int tid = 0; tid < g.threads; ++tid)
+        Forward<N, T>::col_pass(p, g, smem.data(), tid, row, inner0);
+    }
+  }
+}
+
+template <int N, int T>
+void run_inverse(const FftParams& p, int oh, int ow) {
+  const FftGeom g = inverse_geom(N, T, oh, ow);
+  const int tiles = (p.n_inner + T - 1) / T;
+  std::vector<char> smem(g.smem_bytes);
+  std::vector<LineRegs<N>> regs(g.threads);
+  for (int row = 0; row < p.n_rows; ++row) {
+    for (int tile = 0; tile < tiles; ++tile) {
+      const int inner0 = tile * T;
+      std::memset(smem.data(), 0xFF, smem.size());
+      for (int tid = 0; tid < g.threads; ++tid)
+        Inverse<N, T>::col_pass(p, g, smem.data(), tid, row, inner0);
+      for (int tid = 0; tid < g.threads; ++tid)
+        Inverse<N, T>::row_fetch(g, smem.data(), tid, regs[tid]);
+      std::memset(smem.data() + g.off_b, 0xFF, smem.size() - g.off_b);  // mid is dead now
+      for (int tid = 0; tid < g.threads; ++tid)
+        Inverse<N, T>::row_pass(p, g, smem.data(), tid, regs[tid]);
+      for (int tid = 0; tid < g.threads; ++tid)
+        Inverse<N, T>::store(p, g, smem.data(), tid, g.threads, row, inner0);
+    }
+  }
+}
+
+template <int N>
+int dispatch_t(bool inverse, const FftParams& p, int T, int oh, int ow) {
+#define FBF_CASE(TT)                                  \
+  case TT:                                            \
+    if (inverse) run_inverse<N, TT>(p, oh, ow);       \
+    else run_forward<N, TT>(p);                       \
+    return 0;
+  switch (T) {
+    FBF_CASE(1) FBF_CASE(2) FBF_CASE(4) FBF_CASE(8) FBF_CASE(16)
+  }
+#undef FBF_CASE
+  return 2;
+}
+
+int dispatch(bool inverse, const FftParams& p, int N, int T, int oh, int ow) {
+  switch (N) {
+    case 8: return dispatch_t<8>(inverse, p, T, oh, ow);
+    case 16: return dispatch_t<16>(inverse, p, T, oh, ow);
+    case 32: return dispatch_t<32>(inverse, p, T, oh, ow);
+    case 64: return dispatch_t<64>(inverse, p, T, oh, ow);
+    case 128: return dispatch_t<128>(inverse, p, T, oh, ow);
+  }
+  return 1;
+}
+
+}  // namespace
+
+extern "C" {
+
+int hostcheck_fft_forward(const float* real, float* spec, int N, int T, int h, int w, int pad_u,
+                          int pad_l, int n_rows, int n_inner, int kc, long long row_stride,
+                          long long inner_stride) {
+  FftParams p{};
+  p.real_in = real;
+  p.spec = reinterpret_cast<float2*>(spec);
+  p.h = h; p.w = w; p.off_y = pad_u; p.off_x = pad_l;
+  p.n_rows = n_rows; p.n_inner = n_inner; p.kc = kc;
+  p.real_row_stride = row_stride; p.real_inner_stride = inner_stride;
+  return dispatch(false, p, N, T, 0, 0);
+}
+
+int hostcheck_fft_inverse(const float* spec, float* real, const float* bias, int N, int T, int oh,
+                          int ow, int off_y, int off_x, int n_rows, int n_inner, int kc,
+                          long long row_stride, long long inner_stride, int accumulate) {
+  FftParams p{};
+  p.real_out = real;
+  p.spec = reinterpret_cast<float2*>(const_cast<float*>(spec));
+  p.bias = bias;
+  p.h = oh; p.w = ow; p.off_y = off_y; p.off_x = off_x;
+  p.n_rows = n_rows; p.n_inner = n_inner; p.kc = kc;
+  p.real_row_stride = row_stride; p.real_inner_stride = inner_stride;
+  p.accumulate = accumulate;
+  return dispatch(true, p, N, T, oh, ow);
+}
+
+int hostcheck_forward_smem_bytes(int N, int T, int h, int w, int pad_u, int pad_l) {
+  return forward_geom(N, T, h, w, pad_u, pad_l).smem_bytes;
+}
+int hostcheck_forward_threads(int N, int T, int h, int w, int pad_u, int pad_l) {
+  const FftGeom g = forward_geom(N, T, h, w, pad_u, pad_l);
+  return (g.lines1 > g.threads || g.lines2 > g.threads) ? -1 : g.threads;
+}
+int hostcheck_inverse_smem_bytes(int N, int T, int oh, int ow) { return inverse_geom(N, T, oh, ow).smem_bytes; }
+int hostcheck_inverse_threads(int N, int T, int oh, int ow) {
+  const FftGeom g = inverse_geom(N, T, oh, ow);
+  return (g.lines1 > g.threads || g.lines2 > g.threads) ? -1 : g.threads;
+}
+
+}  // extern "C"

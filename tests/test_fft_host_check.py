@@ -1,0 +1,88 @@
+"""Runs the FFT kernels' phase functions on the host (threads as loops, shared memory
+pre-filled with NaN) and checks them against the DFT restatement of the oracle: the
+index arithmetic of every size / tile combination is verified without a GPU."""
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+import pytest
+
+from oracle import spectral
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+SRC = os.path.join(ROOT, "tests", "host_check", "fft_host_check.cpp")
+LIB = os.path.join(ROOT, "tests", "host_check", "libfft_host_check.so")
+CORE = os.path.join(ROOT, "fbcunn_b200", "csrc", "fft_core.cuh")
+LL = ctypes.c_longlong
+
+
+@pytest.fixture(scope="module")
+def hc():
+    newest = max(os.path.getmtime(SRC), os.path.getmtime(CORE))
+    if not os.path.exists(LIB) or os.path.getmtime(LIB) < newest:
+        subprocess.check_call(["g++", "-O1", "-std=c++17", "-fPIC", "-shared", "-o", LIB, SRC])
+    return ctypes.CDLL(LIB)
+
+
+def _bin_major(spec_plane_major):
+    """(d1, d2, ky, kx) -> (kx*N+ky, d1, d2)."""
+    d1, d2, n, half = spec_plane_major.shape
+    return spec_plane_major.transpose(3, 2, 0, 1).reshape(half * n, d1, d2)
+
+
+CASES = [(N, T) for N in (8, 16, 32, 64, 128) for T in (1, 4, 16) if (N // 2 + 1) * T <= 512]
+
+
+@pytest.mark.parametrize("N,T", CASES)
+def test_forward(hc, N, T):
+    rng = np.random.default_rng(N * 100 + T)
+    for (h, w, pu, pl) in [(N, N, 0, 0), (3, 3, 0, 0), (N - 3, N - 5, 1, 2), (1, 1, 0, 0)]:
+        if hc.hostcheck_forward_smem_bytes(N, T, h, w, pu, pl) > 227 * 1024:
+            continue
+        assert hc.hostcheck_forward_threads(N, T, h, w, pu, pl) > 0
+        for transposed in (False, True):
+            d1, d2 = (2, 5) if not transposed else (5, 2)
+            x = rng.standard_normal((d1, d2, h, w)).astype(np.float32)
+            rows, inner = (d2, d1) if transposed else (d1, d2)
+            rs, is_ = (1, d2) if transposed else (d2, 1)
+            kc = (inner + 3) // 4 * 4
+            spec = np.full(((N // 2 + 1) * N, rows, kc, 2), np.nan, np.float32)
+            rc = hc.hostcheck_fft_forward(x.ctypes.data_as(ctypes.c_void_p), spec.ctypes.data_as(ctypes.c_void_p),
+                                          N, T, h, w, pu, pl, rows, inner, kc, LL(rs), LL(is_))
+            assert rc == 0
+            ref = _bin_major(spectral.rfft2_padded(x, N, N, pu, pl))
+            if transposed:
+                ref = ref.transpose(0, 2, 1)
+            got = spec[..., 0] + 1j * spec[..., 1]
+            assert np.abs(got[:, :, :inner] - ref).max() <= 3e-6 * np.abs(ref).max()
+            assert np.all(got[:, :, inner:] == 0), "padding planes must be written as zero"
+
+
+@pytest.mark.parametrize("N,T", CASES)
+def test_inverse(hc, N, T):
+    rng = np.random.default_rng(N * 100 + T + 7)
+    for (oh, ow, oy, ox) in [(N, N, 0, 0), (3, 3, 0, 0), (N - 3, N - 5, 1, 2), (N - 4, N - 4, 0, 0), (1, 1, 2, 3)]:
+        if hc.hostcheck_inverse_smem_bytes(N, T, oh, ow) > 227 * 1024:
+            continue
+        assert hc.hostcheck_inverse_threads(N, T, oh, ow) > 0
+        rows, inner, kc = 2, 5, 8
+        full = rng.standard_normal((rows, inner, N, N))
+        sb = _bin_major(np.fft.rfft2(full))
+        spec = np.full(((N // 2 + 1) * N, rows, kc, 2), np.nan, np.float32)  # padding must not be read
+        spec[:, :, :inner, 0] = sb.real
+        spec[:, :, :inner, 1] = sb.imag
+        bias = rng.standard_normal(inner).astype(np.float32)
+        out = np.full((rows, inner, oh, ow), np.nan, np.float32)
+        rc = hc.hostcheck_fft_inverse(spec.ctypes.data_as(ctypes.c_void_p), out.ctypes.data_as(ctypes.c_void_p),
+                                      bias.ctypes.data_as(ctypes.c_void_p), N, T, oh, ow, oy, ox, rows, inner, kc,
+                                      LL(inner), LL(1), 0)
+        assert rc == 0
+        # un-normalised inverse (src/fft/FFTWrapperLua.cpp:235-237), cropped, bias added
+        ref = spectral.irfft2_unnormalised(np.fft.rfft2(full), N)[:, :, oy:oy + oh, ox:ox + ow] + bias[None, :, None, None]
+        assert np.abs(out - ref).max() <= 3e-6 * np.abs(ref).max()
+        init = rng.standard_normal((rows, inner, oh, ow)).astype(np.float32)
+        acc = init.copy()
+        hc.hostcheck_fft_inverse(spec.ctypes.data_as(ctypes.c_void_p), acc.ctypes.data_as(ctypes.c_void_p), None,
+                                 N, T, oh, ow, oy, ox, rows, inner, kc, LL(inner), LL(1), 1)
+        assert np.abs(acc - (ref - bias[None, :, None, None] + init)).max() <= 3e-6 * np.abs(ref).max()
