@@ -7,6 +7,7 @@ that it travels with the source tree; nothing is installed into site-packages.
 """
 from __future__ import annotations
 
+import hashlib
 import os
 import subprocess
 import sys
@@ -36,11 +37,26 @@ def _deps():
     return out
 
 
+def _digest() -> str:
+    h = hashlib.sha256()
+    for path in sorted(_deps()):
+        h.update(os.path.basename(path).encode())
+        with open(path, "rb") as f:
+            h.update(f.read())
+    h.update(" ".join(NVCC_FLAGS).encode())
+    return h.hexdigest()
+
+
 def build(force: bool = False, verbose: bool = False) -> str:
+    """Rebuilds when the sources' content hash differs from the one the library was
+    built from (file times do not survive a copy of the tree)."""
+    stamp = LIB + ".stamp"
+    digest = _digest()
+    if not force and os.path.exists(LIB) and os.path.exists(stamp):
+        with open(stamp) as f:
+            if f.read().strip() == digest:
+                return LIB
     os.makedirs(OBJ, exist_ok=True)
-    newest = max(os.path.getmtime(p) for p in _deps())
-    if not force and os.path.exists(LIB) and os.path.getmtime(LIB) >= newest:
-        return LIB
     nvcc = _nvcc()
     extra = ["-Xptxas", "-v"] if verbose else []
 
@@ -60,6 +76,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+    with open(stamp, "w") as f:
+        f.write(digest)
     return LIB
 
 

@@ -8,6 +8,7 @@ present at build time.
 from __future__ import annotations
 
 import ctypes
+import hashlib
 import os
 import subprocess
 from dataclasses import dataclass
@@ -49,16 +50,43 @@ class Shape:
         return _CShape(self.B, self.P, self.F, self.iH, self.iW, self.kH, self.kW, self.padH, self.padW)
 
 
+_REFERENCE_SRC = "/root/reference/test/ReferenceConvolutions.cpp"
+
+
+def _stale(lib: str, sources) -> str:
+    """Content hash of the sources if it differs from the one `lib` was built from
+    (file times do not survive a copy of the tree), else ''."""
+    h = hashlib.sha256()
+    for src in sources:
+        with open(src, "rb") as f:
+            h.update(f.read())
+    digest = h.hexdigest()
+    stamp = lib + ".stamp"
+    if os.path.exists(lib) and os.path.exists(stamp):
+        with open(stamp) as f:
+            if f.read().strip() == digest:
+                return ""
+    return digest
+
+
 def build(force: bool = False) -> None:
-    """Compile refconv.c and, where the reference checkout is present, the reference file."""
-    src = os.path.join(_HERE, "refconv.c")
-    stale = not os.path.exists(_LIB) or os.path.getmtime(_LIB) < os.path.getmtime(src)
-    if force or stale:
-        subprocess.check_call(["make", "-s", "-C", _HERE, os.path.join(_HERE, "liboracle.so")])
-    bridge = os.path.join(_HERE, "ref_bridge.cpp")
-    ref_stale = not os.path.exists(_REF) or os.path.getmtime(_REF) < os.path.getmtime(bridge)
-    if force or ref_stale:
-        subprocess.check_call(["make", "-s", "-C", _HERE, "ref"])
+    """Compile refconv.c and, where the reference checkout is present, the reference's own
+    CPU convolution from where it lies (outputs stay under _ref/).  A machine without the
+    checkout keeps using the prebuilt _ref/ library."""
+    digest = _stale(_LIB, [os.path.join(_HERE, "refconv.c"), os.path.join(_HERE, "Makefile")])
+    if force or digest:
+        subprocess.check_call(["make", "-s", "-B", "-C", _HERE, os.path.join(_HERE, "liboracle.so")])
+        with open(_LIB + ".stamp", "w") as f:
+            f.write(digest or _stale(_LIB + ".none", [os.path.join(_HERE, "refconv.c"), os.path.join(_HERE, "Makefile")]))
+    if os.path.exists(_REFERENCE_SRC):
+        shim = [os.path.join(_HERE, "shim", d, f) for d, f in
+                (("thpp", "Tensor.h"), ("thpp", "Storage.h"), ("folly", "Optional.h"), ("glog", "logging.h"))]
+        srcs = [os.path.join(_HERE, "ref_bridge.cpp"), _REFERENCE_SRC] + shim
+        digest = _stale(_REF, srcs)
+        if force or digest:
+            subprocess.check_call(["make", "-s", "-C", _HERE, "ref"])
+            with open(_REF + ".stamp", "w") as f:
+                f.write(digest or _stale(_REF + ".none", srcs))
 
 
 _lib = None
