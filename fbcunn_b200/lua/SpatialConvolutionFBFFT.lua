@@ -1,0 +1,186 @@
+--[[
+   nn.SpatialConvolutionFBFFT on top of libfbfftconv (B200, sm_100a).
+
+   Drop-in for fbcunn/SpatialConvolutionFBFFT.lua: same class name, constructor
+   arguments, nn.Module methods and weight / bias / gradWeight / gradBias layout, so a
+   Torch7 model that builds the reference module runs unchanged.  The three passes are
+   one C call each (include/fbfftconv.h) instead of the FFTWrapper / transposeMMFFI /
+   bias-FFI sequence of the reference (fbcunn/SpatialConvolutionFBFFT.lua:102-354);
+   there is no cudnn fallback: a failed pass raises a Lua error.
+
+   Requires LuaJIT (ffi), torch, cutorch.  Not executed by this repository's tests
+   (no Lua toolchain there); the same C ABI is exercised from Python.
+--]]
+local ffi = require 'ffi'
+
+ffi.cdef[[
+typedef struct fbfftconv_handle fbfftconv_handle;
+typedef struct fbfftconv_desc {
+  int32_t batch, n_input_plane, n_output_plane;
+  int32_t input_h, input_w, kernel_h, kernel_w;
+  int32_t stride_h, stride_w, pad_h, pad_w;
+  int32_t device;
+  uint32_t flags;
+} fbfftconv_desc;
+int fbfftconv_create(const fbfftconv_desc* desc, fbfftconv_handle** out);
+int fbfftconv_destroy(fbfftconv_handle* h);
+int fbfftconv_fft_size(const fbfftconv_handle* h);
+size_t fbfftconv_workspace_bytes(const fbfftconv_handle* h);
+int fbfftconv_update_output(fbfftconv_handle* h, const float* input, const float* weight,
+                            const float* bias, float* output, void* stream);
+int fbfftconv_update_grad_input(fbfftconv_handle* h, const float* grad_output, const float* weight,
+                                float* grad_input, void* stream);
+int fbfftconv_acc_grad_parameters(fbfftconv_handle* h, const float* input, const float* grad_output,
+                                  float* grad_weight, float* grad_bias, float scale, void* stream);
+int fbfftconv_comm_unique_id(void* id128);
+int fbfftconv_comm_init(fbfftconv_handle* h, const void* id128, int rank, int nranks);
+const char* fbfftconv_last_error(void);
+void* THCState_getCurrentStream(void* state);
+]]
+
+local lib_name = 'fbfftconv'
+local lib_path = package.searchpath(lib_name, package.cpath)
+local C = ffi.load(lib_path and lib_path or lib_name)
+
+local FBFFTCONV_ACCUMULATE_GRADS = 1
+
+local SpatialConvolutionFBFFT, parent =
+   torch.class('nn.SpatialConvolutionFBFFT', 'nn.Module')
+
+SpatialConvolutionFBFFT.memoryReuseNone = "none"
+SpatialConvolutionFBFFT.memoryReuseInput = "input"
+SpatialConvolutionFBFFT.memoryReuseOutput = "output"
+SpatialConvolutionFBFFT.memoryReuseWeight = "weight"
+SpatialConvolutionFBFFT.memoryReuseAll = "all"
+
+local function check(status)
+   if status ~= 0 then
+      error('fbfftconv: ' .. ffi.string(C.fbfftconv_last_error()))
+   end
+end
+
+function SpatialConvolutionFBFFT:__init(nInputPlane, nOutputPlane, kW, kH, dW, dH,
+                                        padLeft, padUp, memoryReusePolicy, numCudaStreams)
+   parent.__init(self)
+   for _, v in ipairs({nInputPlane, nOutputPlane, kW, kH}) do
+      assert(torch.type(v) == 'number')
+   end
+   assert(memoryReusePolicy == nil or torch.type(memoryReusePolicy) == 'string' or
+             torch.type(memoryReusePolicy) == 'table')
+   assert(numCudaStreams == nil or torch.type(numCudaStreams) == 'number')
+   self.nInputPlane, self.nOutputPlane = nInputPlane, nOutputPlane
+   self.kW, self.kH = kW, kH
+   self.dW, self.dH = dW or 1, dH or 1
+   self.padLeft, self.padUp = padLeft or 0, padUp or 0
+   self.padRight, self.padDown = self.padLeft, self.padUp
+   assert(self.dH == 1, "fft only supports stride-1 convolutions atm")
+   assert(self.dW == 1, "fft only supports stride-1 convolutions atm")
+   assert(self.padUp < self.kH and self.padDown < self.kH and
+             self.padLeft < self.kW and self.padRight < self.kW,
+          "Padding must be smaller than kernel")
+   self.fftImplementation = 'fbfft'
+   self.memoryReusePolicy = memoryReusePolicy or SpatialConvolutionFBFFT.memoryReuseNone
+   self.numCudaStreams = numCudaStreams or 16
+   self.accumulateGrads = false   -- reference behaviour: accGradParameters overwrites
+
+   self.weight = torch.Tensor(nOutputPlane, nInputPlane, kH, kW)
+   self.bias = torch.Tensor(nOutputPlane)
+   self.gradWeight = torch.Tensor(nOutputPlane, nInputPlane, kH, kW)
+   self.gradBias = torch.Tensor(nOutputPlane)
+   self.output = torch.Tensor()
+   self.gradInput = torch.Tensor()
+   self:reset()
+end
+
+function SpatialConvolutionFBFFT:reset(stdv)
+   if stdv then
+      stdv = stdv * math.sqrt(3)
+   else
+      stdv = 1 / math.sqrt(self.kW * self.kH * self.nInputPlane)
+   end
+   self.weight:uniform(-stdv, stdv)
+   self.bias:uniform(-stdv, stdv)
+end
+
+-- One native handle per (device, batch, image size); rebuilt when they change.
+function SpatialConvolutionFBFFT:prepareSizeAndBuffers(input)
+   assert(torch.type(input) == 'torch.CudaTensor', "CUDA support only!")
+   assert(input:dim() == 4, "2D convolutions on 4D tensors atm")
+   assert(input:isContiguous())
+   local key = string.format('%d:%d:%d:%d', cutorch.getDevice(),
+                             input:size(1), input:size(3), input:size(4))
+   if self.handleKey ~= key then
+      self:cleanupBuffers()
+      local desc = ffi.new('fbfftconv_desc', {
+         input:size(1), self.nInputPlane, self.nOutputPlane,
+         input:size(3), input:size(4), self.kH, self.kW,
+         self.dH, self.dW, self.padUp, self.padLeft,
+         cutorch.getDevice() - 1,
+         self.accumulateGrads and FBFFTCONV_ACCUMULATE_GRADS or 0})
+      local out = ffi.new('fbfftconv_handle*[1]')
+      check(C.fbfftconv_create(desc, out))
+      self.handle = ffi.gc(out[0], C.fbfftconv_destroy)
+      self.handleKey = key
+      if self.comm then
+         check(C.fbfftconv_comm_init(self.handle, self.comm.id, self.comm.rank, self.comm.nranks))
+      end
+   end
+   return C.fbfftconv_fft_size(self.handle)
+end
+
+local function stream()
+   return ffi.C.THCState_getCurrentStream(cutorch._state)
+end
+
+function SpatialConvolutionFBFFT:updateOutput(input)
+   self:prepareSizeAndBuffers(input)
+   local oH = input:size(3) + 2 * self.padUp - self.kH + 1
+   local oW = input:size(4) + 2 * self.padLeft - self.kW + 1
+   self.output = self.output:cuda():resize(input:size(1), self.nOutputPlane, oH, oW)
+   local bias = (self.skipBias and nil) or self.bias:data()
+   check(C.fbfftconv_update_output(self.handle, input:data(), self.weight:data(), bias,
+                                   self.output:data(), stream()))
+   return self.output
+end
+
+function SpatialConvolutionFBFFT:updateGradInput(input, gradOutput)
+   self:prepareSizeAndBuffers(input)
+   assert(gradOutput:isContiguous())
+   self.gradInput = self.gradInput:cuda():resizeAs(input)
+   check(C.fbfftconv_update_grad_input(self.handle, gradOutput:data(), self.weight:data(),
+                                       self.gradInput:data(), stream()))
+   return self.gradInput
+end
+
+function SpatialConvolutionFBFFT:accGradParameters(input, gradOutput, scale)
+   self:prepareSizeAndBuffers(input)
+   assert(gradOutput:isContiguous())
+   local gradBias = (self.skipBias and nil) or self.gradBias:data()
+   check(C.fbfftconv_acc_grad_parameters(self.handle, input:data(), gradOutput:data(),
+                                         self.gradWeight:data(), gradBias, scale or 1, stream()))
+end
+
+function SpatialConvolutionFBFFT:backward(input, gradOutput, scale)
+   self:updateGradInput(input, gradOutput)
+   self:accGradParameters(input, gradOutput, scale)
+   return self.gradInput
+end
+
+-- One process per GPU: `id` is the 128-byte value rank 0 got from
+-- fbfftconv_comm_unique_id and shared with the other ranks.
+function SpatialConvolutionFBFFT:attachCommunicator(id, rank, nranks)
+   self.comm = {id = id, rank = rank, nranks = nranks}
+   if self.handle then
+      check(C.fbfftconv_comm_init(self.handle, id, rank, nranks))
+   end
+end
+
+function SpatialConvolutionFBFFT:setReuseInputs(val) self.reuseInputs = val end
+function SpatialConvolutionFBFFT:setReuseOutputs(val) self.reuseOutputs = val end
+function SpatialConvolutionFBFFT:setReuseWeights(val) self.reuseWeights = val end
+
+function SpatialConvolutionFBFFT:cleanupBuffers()
+   self.handle = nil      -- ffi.gc destroys the native handle and its scratch
+   self.handleKey = nil
+   collectgarbage()
+end
