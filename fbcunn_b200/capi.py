@@ -61,6 +61,7 @@ _SIGNATURES = {
     "fbfftconv_transpose_mm": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p]),
     "fbfftconv_update_output_bias": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "fbfftconv_acc_grad_parameters_bias": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p]),
+    "fbfftconv_acc_grad_parameters_bias_noalloc": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p]),
     "fbfftconv_profile_enable": (c_int, [c_void_p, c_int]),
     "fbfftconv_profile_reset": (c_int, [c_void_p]),
     "fbfftconv_profile_read": (c_int, [c_void_p, c_int, c_int, POINTER(ctypes.c_double), POINTER(c_int)]),

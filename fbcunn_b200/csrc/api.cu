@@ -249,6 +249,10 @@ bool valid_fft_size(int n) { return n == 8 || n == 16 || n == 32 || n == 64 || n
 
 }  // namespace
 
+namespace fbfft {
+int report_error(int code, const char* message) { return fail(code, "%s", message); }
+}  // namespace fbfft
+
 extern "C" {
 
 const char* fbfftconv_last_error(void) { return t_error.c_str(); }

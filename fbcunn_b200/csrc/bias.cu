@@ -2,6 +2,10 @@
 // FFT's store; the stand-alone kernels here back the entry points that mirror the
 // reference's updateOutputBiasFFI / accGradParametersBiasFFI
 // (src/ConvolutionBias.cu:39-51, :61-97).
+#include <mutex>
+#include <string>
+
+#include "../../include/fbfftconv.h"
 #include "kernels.h"
 
 namespace fbfft {
@@ -83,3 +87,73 @@ cudaError_t launch_row_sum(const float* src, float* dst, int rows, int count, lo
 }
 
 }  // namespace fbfft
+
+// ---------------------------------------------------------------------------
+// Bias gradient without any allocation
+// ---------------------------------------------------------------------------
+// Some callers must not (or cannot) obtain device memory at the moment they need a
+// bias gradient: a framework whose caching allocator already owns all of the GPU's
+// memory, so that a raw cudaMalloc fails or fragments its pool; a serving or
+// training loop under a fixed memory budget; code running where an allocation's
+// implicit device synchronisation is not acceptable.  For them the per-plane partial
+// sums of the two-stage reduction live in a fixed array inside the library image
+// instead of in caller-provided scratch.
+namespace {
+
+constexpr int kNoAllocMaxPartials = 65536;  // batch * planes; 256 KiB of device memory
+constexpr int kNoAllocMaxDevices = 64;
+
+// One copy per GPU that loads this library, held until the process exits.  In host
+// code this name is only a stand-in for the symbol: the device address has to be
+// asked for (below), it must never be passed to a kernel as it is.
+static __device__ __align__(256) float g_noalloc_partials[kNoAllocMaxPartials];
+
+std::mutex g_noalloc_mutex;
+float* g_noalloc_address[kNoAllocMaxDevices] = {};
+
+// Device address of the array on the current device, resolved on first use.
+cudaError_t noalloc_scratch(float** out) {
+  int device = -1;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return e;
+  if (device < 0 || device >= kNoAllocMaxDevices) return cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (!g_noalloc_address[device]) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_partials);
+    if (e != cudaSuccess) return e;
+    g_noalloc_address[device] = p;
+  }
+  *out = g_noalloc_address[device];
+  return cudaSuccess;
+}
+
+}  // namespace
+
+extern "C" int fbfftconv_acc_grad_parameters_bias_noalloc(const float* grad_output, float* grad_bias,
+                                                          int batch, int planes, int h, int w,
+                                                          float scale, int accumulate,
+                                                          fbfftconv_stream stream) {
+  using fbfft::report_error;
+  if (!grad_output || !grad_bias || batch <= 0 || planes <= 0 || h <= 0 || w <= 0 || batch > 65535)
+    return report_error(FBFFTCONV_ERR_INVALID_ARGUMENT, "bad bias-gradient arguments");
+  if ((long long)batch * planes > kNoAllocMaxPartials) {
+    const std::string msg = "batch * planes = " + std::to_string((long long)batch * planes) +
+                            " exceeds the " + std::to_string(kNoAllocMaxPartials) +
+                            " partial sums of the allocation-free bias gradient; use "
+                            "fbfftconv_acc_grad_parameters_bias with caller scratch";
+    return report_error(FBFFTCONV_ERR_UNSUPPORTED_SIZE, msg.c_str());
+  }
+  float* partials = nullptr;
+  cudaError_t e = noalloc_scratch(&partials);
+  if (e != cudaSuccess)
+    return report_error(FBFFTCONV_ERR_CUDA, (std::string("cudaGetSymbolAddress: ") + cudaGetErrorString(e)).c_str());
+  // Stage one writes every partial that stage two reads (planes * batch of them), so
+  // nothing left in the array by an earlier call is ever consumed and nothing needs
+  // clearing.
+  e = fbfft::launch_bias_grad(grad_output, grad_bias, partials, batch, planes, h * w, scale,
+                              accumulate != 0, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess)
+    return report_error(FBFFTCONV_ERR_CUDA, (std::string("bias gradient launch: ") + cudaGetErrorString(e)).c_str());
+  return FBFFTCONV_OK;
+}

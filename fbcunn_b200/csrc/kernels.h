@@ -38,4 +38,8 @@ cudaError_t launch_bias_grad(const float* grad_out, float* grad_bias, float* scr
 cudaError_t launch_row_sum(const float* src, float* dst, int rows, int count, long long ld, int step,
                            float scale, int accumulate, cudaStream_t stream);
 
+// Records `message` as the calling thread's last error (what fbfftconv_last_error
+// returns) and hands `code` back, for entry points that live outside api.cu.
+int report_error(int code, const char* message);
+
 }  // namespace fbfft

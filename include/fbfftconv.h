@@ -158,6 +158,23 @@ int fbfftconv_acc_grad_parameters_bias(const float* grad_output, float* grad_bia
                                        int batch, int planes, int h, int w, float scale,
                                        int accumulate, fbfftconv_stream stream);
 
+/* The same bias gradient for callers that cannot allocate device memory when they
+ * need it -- a framework allocator that already owns the whole GPU so that a raw
+ * cudaMalloc fails or fragments its pool, a loop under a fixed memory budget, or code
+ * that cannot afford the implicit synchronisation of an allocation.  It has no
+ * counterpart in the reference.  The per-plane partial sums live in a fixed
+ * 256 KiB array inside the library (one copy on every GPU that loads it, held until
+ * the process exits), so batch * planes must not exceed 65536; larger problems get
+ * FBFFTCONV_ERR_UNSUPPORTED_SIZE and should use the variant above.  The call makes no
+ * cudaMalloc / cudaFree and calls no allocating routine.  The first call on each
+ * device looks the array's device address up once (with that device current); make
+ * that first call before any stream capture begins.  All calls on one device share the
+ * array: two calls whose kernels can overlap on the GPU (different streams) race;
+ * calls ordered on one stream do not.  Nothing needs clearing between calls. */
+int fbfftconv_acc_grad_parameters_bias_noalloc(const float* grad_output, float* grad_bias, int batch,
+                                               int planes, int h, int w, float scale,
+                                               int accumulate, fbfftconv_stream stream);
+
 /* ---- multi-GPU: one process per GPU ------------------------------------------
  * Replaces the gather / add / broadcast of nn.DataParallel
  * (fbcunn/DataParallel.lua:105-131) by one NCCL all-reduce over NVLink.  Rank 0
