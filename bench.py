@@ -505,10 +505,15 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--layer", default="C2", choices=list(LAYERS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=0,
+                    help="override the layer's global batch (small cases for profiler captures)")
     ap.add_argument("--layer-iters", type=int, default=5)
     ap.add_argument("--no-layers", action="store_true", help="skip the per-layer / per-pass table")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
+    if args.batch > 0:
+        for k, v in list(LAYERS.items()):
+            LAYERS[k] = (args.batch,) + v[1:]
     if args.impl == "reference":
         return run_reference_arm(args)
     return run_gpu_arm(args)
