@@ -145,9 +145,9 @@ FBF_HD void fft_inreg(float2 (&v)[N]) {
   for (int k = 0; k < N; ++k) v[k] = t[bit_reverse(k, LG)];
 }
 
-// Sizes above 32 are done by one thread in two steps through a private line of
-// shared memory: N = N1 * N2, input index n = N2*n1 + n2, output index
-// k = k1 + N1*k2.  After both steps slot N2*k1 + k2 holds frequency k1 + N1*k2.
+// Sizes above 32 are split as N = N1 * N2 (input index n = N2*n1 + n2, output index
+// k = k1 + N1*k2): N2 threads each do an N1-point transform and a twiddle, then N1
+// threads each do an N2-point transform.
 template <int N>
 struct Split {
   static constexpr int N1 = N, N2 = 1;
@@ -160,43 +160,6 @@ template <>
 struct Split<128> {
   static constexpr int N1 = 8, N2 = 16;
 };
-
-template <int N>
-FBF_HD int slot_of_frequency(int k) {
-  return Split<N>::N2 * (k % Split<N>::N1) + (k / Split<N>::N1);
-}
-
-// ld(n) returns input element n (already zero where pruned); st(slot, value).
-template <int N, bool INV, class LoadFn, class StoreFn>
-FBF_HD void fft_two_step_first(LoadFn ld, StoreFn st) {
-  constexpr int N1 = Split<N>::N1, N2 = Split<N>::N2;
-#pragma unroll 1
-  for (int n2 = 0; n2 < N2; ++n2) {
-    float2 v[N1];
-#pragma unroll
-    for (int n1 = 0; n1 < N1; ++n1) v[n1] = ld(N2 * n1 + n2);
-    fft_inreg<N1, INV>(v);
-#pragma unroll
-    for (int k1 = 1; k1 < N1; ++k1) v[k1] = cmul(v[k1], tw128_runtime<INV>(n2 * k1 * (128 / N)));
-#pragma unroll
-    for (int k1 = 0; k1 < N1; ++k1) st(N2 * k1 + n2, v[k1]);
-  }
-}
-
-// ld(slot); out(frequency, slot, value).
-template <int N, bool INV, class LoadFn, class OutFn>
-FBF_HD void fft_two_step_second(LoadFn ld, OutFn out) {
-  constexpr int N1 = Split<N>::N1, N2 = Split<N>::N2;
-#pragma unroll 1
-  for (int k1 = 0; k1 < N1; ++k1) {
-    float2 u[N2];
-#pragma unroll
-    for (int n2 = 0; n2 < N2; ++n2) u[n2] = ld(N2 * k1 + n2);
-    fft_inreg<N2, INV>(u);
-#pragma unroll
-    for (int k2 = 0; k2 < N2; ++k2) out(k1 + N1 * k2, N2 * k1 + k2, u[k2]);
-  }
-}
 
 // Two real rows a, b transformed as one complex line z = a + i b:
 //   A[k] = (Z[k] + conj(Z[N-k])) / 2,   B[k] = (Z[k] - conj(Z[N-k])) / (2i).
@@ -225,81 +188,68 @@ static inline int plane_pitch(int n, int T) {
 
 struct FftGeom {
   int N, T;
-  int he, we;      // extent of the non-zero region inside the N x N square (offset included)
+  int he, we;      // forward: extent of the data inside the N x N square (offset included);
+                   // inverse: the crop window
   int hh;          // row pairs: rows (j, j + hh) share one complex line
-  int pitch1;      // line pitch of the row-pass buffer  [x][line1], odd
-  int pitch2;      // line pitch of the column buffers   [y][line2]
+  int pitch1;      // line pitch of the row buffer
+  int pitch2;      // row pitch of the column buffer ("mid")
   int lines1;      // hh * T
   int lines2;      // (N/2 + 1) * T
-  int rows1;       // rows of the row-pass buffer
+  int chunk;       // cooperative kernels: row lines processed per round
   int threads;
   int off_a, off_b;  // byte offsets of the two shared-memory regions
   int smem_bytes;
 };
 
-static inline bool two_step(int N) { return N > 32; }
+static inline bool cooperative(int N) { return N > 32; }
+static inline int coop_threads() { return 256; }
 
-// Forward: region A = row-pass buffer, region B = column buffer ("mid").  For the
-// single-step sizes both alias (a thread takes its whole line into registers
-// before the barrier that precedes the first write of mid).
-static inline FftGeom forward_geom(int N, int T, int h, int w, int pad_u, int pad_l) {
+// Thread-per-line kernels (N <= 32): region A = row buffer [x][line1], region B = column
+// buffer [y][kx*T + t]; they alias (a thread takes its whole line into registers before
+// the barrier that precedes the first write of the other region).
+// Cooperative kernels (N > 32): region A = one chunk of row lines
+// [line][k1*(N2+1) + n2], region B = column buffer [y or slot][t*(N/2+1) + kx].
+static inline FftGeom make_geom(int N, int T, int he, int we, bool inverse) {
   FftGeom g;
   g.N = N;
   g.T = T;
-  g.he = h + pad_u;
-  g.we = w + pad_l;
-  g.hh = (g.he + 1) / 2;
+  g.he = he;
+  g.we = we;
+  g.hh = (he + 1) / 2;
   g.lines1 = g.hh * T;
   g.lines2 = (N / 2 + 1) * T;
-  g.pitch1 = g.lines1 | 1;
-  g.pitch2 = plane_pitch(g.lines2, T);
-  g.rows1 = two_step(N) ? N : g.we;
-  const int bytes_a = g.rows1 * g.pitch1 * 8;
-  const int bytes_b = (two_step(N) ? N : g.he) * g.pitch2 * 8;
   g.off_a = 0;
-  if (two_step(N)) {
-    g.off_b = round_up(bytes_a, 16);
-    g.smem_bytes = g.off_b + bytes_b;
-  } else {
+  if (!cooperative(N)) {
+    g.pitch1 = g.lines1 | 1;
+    g.pitch2 = plane_pitch(g.lines2, T);
+    g.chunk = g.lines1;
+    const int bytes_a = (inverse ? 0 : we * g.pitch1 * 8);
+    const int stage = inverse ? T * ((he * we) | 1) * 4 : 0;
+    int bytes_b = he * g.pitch2 * 8;
+    if (stage > bytes_b) bytes_b = stage;
     g.off_b = 0;
     g.smem_bytes = bytes_a > bytes_b ? bytes_a : bytes_b;
+    const int need = g.lines1 > g.lines2 ? g.lines1 : g.lines2;
+    g.threads = round_up(need < 64 ? 64 : need, 32);
+  } else {
+    const int n1 = N == 64 ? 8 : 8, n2 = N / n1;
+    g.pitch1 = n1 * (n2 + 1);          // 72 or 136: both are 8 mod 16
+    g.pitch2 = g.lines2 | 1;
+    g.chunk = N == 64 ? 64 : 32;
+    if (g.chunk > g.lines1) g.chunk = g.lines1;
+    const int bytes_a = g.chunk * g.pitch1 * 8;
+    g.off_b = round_up(bytes_a, 16);
+    g.smem_bytes = g.off_b + N * g.pitch2 * 8;
+    g.threads = coop_threads();
   }
-  const int need = g.lines1 > g.lines2 ? g.lines1 : g.lines2;
-  g.threads = round_up(need < 64 ? 64 : need, 32);
-  if (g.threads > 512) g.threads = 512;
   return g;
 }
 
-// Inverse: he x we is the crop window (oh x ow); region A = column scratch
-// (two-step only) and later the row-pass lines, region B = mid and later the
-// staged real output.
+static inline FftGeom forward_geom(int N, int T, int h, int w, int pad_u, int pad_l) {
+  return make_geom(N, T, h + pad_u, w + pad_l, false);
+}
 static inline FftGeom inverse_geom(int N, int T, int oh, int ow) {
-  FftGeom g;
-  g.N = N;
-  g.T = T;
-  g.he = oh;
-  g.we = ow;
-  g.hh = (oh + 1) / 2;
-  g.lines1 = g.hh * T;
-  g.lines2 = (N / 2 + 1) * T;
-  g.pitch1 = g.lines1 | 1;
-  g.pitch2 = plane_pitch(g.lines2, T);
-  g.rows1 = N;
-  int bytes_a = 0;
-  if (two_step(N)) {
-    const int col = N * g.pitch2 * 8, row = N * g.pitch1 * 8;
-    bytes_a = col > row ? col : row;
-  }
-  const int mid = oh * g.pitch2 * 8;
-  const int stage = T * ((oh * ow) | 1) * 4;
-  const int bytes_b = mid > stage ? mid : stage;
-  g.off_a = 0;
-  g.off_b = round_up(bytes_a, 16);
-  g.smem_bytes = g.off_b + bytes_b;
-  const int need = g.lines1 > g.lines2 ? g.lines1 : g.lines2;
-  g.threads = round_up(need < 64 ? 64 : need, 32);
-  if (g.threads > 512) g.threads = 512;
-  return g;
+  return make_geom(N, T, oh, ow, true);
 }
 
 // ---------------------------------------------------------------------------
@@ -322,62 +272,59 @@ struct FftParams {
   int accumulate;         // inverse only: real_out += result
 };
 
-// Registers a thread keeps across a barrier (single-step sizes only).
+// Registers a thread keeps across a barrier (thread-per-line sizes only).
 template <int N>
 struct LineRegs {
   float2 v[N <= 32 ? N : 1];
 };
 
 // ===========================================================================
-// Forward kernel phases.  Block (tile, row): planes inner0 .. inner0+T-1 of `row`.
+// Thread-per-line kernels, N <= 32.  Block (tile, row): planes inner0 .. inner0+T-1.
 // ===========================================================================
 template <int N, int T>
 struct Forward {
-  static constexpr bool kTwoStep = (N > 32);
-
-  // Phase 0: real planes -> row-pass buffer, rows (j, j+hh) packed as (re, im).
+  // Phase 0: real planes -> row buffer, rows (j, j+hh) packed as (re, im).
   static FBF_HD void load(const FftParams& p, const FftGeom& g, char* smem, int tid, int nthreads,
                           int row, int inner0) {
     float2* ra = reinterpret_cast<float2*>(smem + g.off_a);
     const int per_plane = g.hh * g.we;
-    const int total = per_plane * T;
-    for (int i = tid; i < total; i += nthreads) {
-      const int t = i / per_plane;
-      const int r = i - t * per_plane;
+    // split the T planes over `ts` thread groups so that small planes still use the block
+    int ts = 1;
+    while (ts < T && per_plane * ts * 2 <= nthreads) ts *= 2;
+    const int items = per_plane * ts;
+    const long long plane_elems = (long long)p.h * p.w;
+    const float* base = p.real_in + (row * p.real_row_stride + inner0 * p.real_inner_stride) * plane_elems;
+    const long long tstride = p.real_inner_stride * plane_elems;
+    for (int i = tid; i < items; i += nthreads) {
+      const int part = i / per_plane;
+      const int r = i - part * per_plane;
       const int j = r / g.we;
       const int xx = r - j * g.we;
-      float a = 0.f, b = 0.f;
-      const int inner = inner0 + t;
-      if (inner < p.n_inner) {
-        const float* plane =
-            p.real_in + (row * p.real_row_stride + inner * p.real_inner_stride) * (long long)(p.h * p.w);
-        const int x = xx - p.off_x;
-        const int ya = j - p.off_y, yb = j + g.hh - p.off_y;
-        if (x >= 0) {
-          if (ya >= 0 && ya < p.h) a = plane[ya * p.w + x];
-          if (yb >= 0 && yb < p.h) b = plane[yb * p.w + x];
+      const int x = xx - p.off_x;
+      const int ya = j - p.off_y, yb = j + g.hh - p.off_y;
+      const bool va = x >= 0 && ya >= 0 && ya < p.h;
+      const bool vb = x >= 0 && yb >= 0 && yb < p.h;
+      const int oa = ya * p.w + x, ob = yb * p.w + x;
+      float2* dst = ra + xx * g.pitch1 + j * T;
+      for (int t = part; t < T; t += ts) {
+        float a = 0.f, b = 0.f;
+        if (inner0 + t < p.n_inner) {
+          const float* plane = base + t * tstride;
+          if (va) a = plane[oa];
+          if (vb) b = plane[ob];
         }
-      }
-      ra[xx * g.pitch1 + j * T + t] = make_float2(a, b);
-    }
-    if (kTwoStep) {  // columns the in-place transform reads beyond the data
-      const int extra = (N - g.we) * g.lines1;
-      for (int i = tid; i < extra; i += nthreads) {
-        const int xx = g.we + i / g.lines1;
-        ra[xx * g.pitch1 + (i % g.lines1)] = make_float2(0.f, 0.f);
+        dst[t] = make_float2(a, b);
       }
     }
   }
 
-  // Phase 1a (single step): a line into registers.
+  // Phase 1a: a line into registers.
   static FBF_HD void row_fetch(const FftGeom& g, const char* smem, int line, LineRegs<N>& regs) {
-    if constexpr (!kTwoStep) {
-      if (line >= g.lines1) return;
-      const float2* ra = reinterpret_cast<const float2*>(smem + g.off_a);
+    if (line >= g.lines1) return;
+    const float2* ra = reinterpret_cast<const float2*>(smem + g.off_a);
 #pragma unroll
-      for (int xx = 0; xx < N; ++xx)
-        regs.v[xx] = xx < g.we ? ra[xx * g.pitch1 + line] : make_float2(0.f, 0.f);
-    }
+    for (int xx = 0; xx < N; ++xx)
+      regs.v[xx] = xx < g.we ? ra[xx * g.pitch1 + line] : make_float2(0.f, 0.f);
   }
 
   // Phase 1b: transform along x, split the row pair, write mid[y][kx*T + t].
@@ -386,30 +333,13 @@ struct Forward {
     float2* mid = reinterpret_cast<float2*>(smem + g.off_b);
     const int j = line / T, t = line - j * T;
     const bool has_b = (j + g.hh) < g.he;
-    if constexpr (!kTwoStep) {
-      fft_inreg<N, false>(regs.v);
+    fft_inreg<N, false>(regs.v);
 #pragma unroll
-      for (int k = 0; k <= N / 2; ++k) {
-        float2 a, b;
-        untangle_pair(regs.v[k], regs.v[(N - k) % N], a, b);
-        mid[j * g.pitch2 + k * T + t] = a;
-        if (has_b) mid[(j + g.hh) * g.pitch2 + k * T + t] = b;
-      }
-    } else {
-      float2* ra = reinterpret_cast<float2*>(smem + g.off_a) + line;
-      const int pitch = g.pitch1;
-      fft_two_step_first<N, false>([&](int n) { return ra[n * pitch]; },
-                                   [&](int slot, float2 v) { ra[slot * pitch] = v; });
-      fft_two_step_second<N, false>([&](int slot) { return ra[slot * pitch]; },
-                                    [&](int, int slot, float2 v) { ra[slot * pitch] = v; });
-#pragma unroll 1
-      for (int k = 0; k <= N / 2; ++k) {
-        float2 a, b;
-        untangle_pair(ra[slot_of_frequency<N>(k) * pitch],
-                      ra[slot_of_frequency<N>((N - k) % N) * pitch], a, b);
-        mid[j * g.pitch2 + k * T + t] = a;
-        if (has_b) mid[(j + g.hh) * g.pitch2 + k * T + t] = b;
-      }
+    for (int k = 0; k <= N / 2; ++k) {
+      float2 a, b;
+      untangle_pair(regs.v[k], regs.v[(N - k) % N], a, b);
+      mid[j * g.pitch2 + k * T + t] = a;
+      if (has_b) mid[(j + g.hh) * g.pitch2 + k * T + t] = b;
     }
   }
 
@@ -417,7 +347,7 @@ struct Forward {
   static FBF_HD void col_pass(const FftParams& p, const FftGeom& g, char* smem, int line, int row,
                               int inner0) {
     if (line >= g.lines2) return;
-    float2* mid = reinterpret_cast<float2*>(smem + g.off_b) + line;
+    const float2* mid = reinterpret_cast<const float2*>(smem + g.off_b) + line;
     const int kx = line / T, t = line - kx * T;
     const int inner = inner0 + t;
     if (inner >= p.kc) return;
@@ -425,30 +355,17 @@ struct Forward {
     float2* dst = p.spec + ((long long)kx * N) * bin_stride + (long long)row * p.kc + inner;
     const int pitch = g.pitch2;
     const int he = g.he;
-    if constexpr (!kTwoStep) {
-      float2 u[N];
+    float2 u[N];
 #pragma unroll
-      for (int y = 0; y < N; ++y) u[y] = y < he ? mid[y * pitch] : make_float2(0.f, 0.f);
-      fft_inreg<N, false>(u);
+    for (int y = 0; y < N; ++y) u[y] = y < he ? mid[y * pitch] : make_float2(0.f, 0.f);
+    fft_inreg<N, false>(u);
 #pragma unroll
-      for (int ky = 0; ky < N; ++ky) dst[ky * bin_stride] = u[ky];
-    } else {
-      fft_two_step_first<N, false>(
-          [&](int n) { return n < he ? mid[n * pitch] : make_float2(0.f, 0.f); },
-          [&](int slot, float2 v) { mid[slot * pitch] = v; });
-      fft_two_step_second<N, false>([&](int slot) { return mid[slot * pitch]; },
-                                    [&](int ky, int, float2 v) { dst[ky * bin_stride] = v; });
-    }
+    for (int ky = 0; ky < N; ++ky) dst[ky * bin_stride] = u[ky];
   }
 };
 
-// ===========================================================================
-// Inverse kernel phases.
-// ===========================================================================
 template <int N, int T>
 struct Inverse {
-  static constexpr bool kTwoStep = (N > 32);
-
   // Phase 1: inverse transform along y of line2 = kx*T + t, keep the crop rows.
   static FBF_HD void col_pass(const FftParams& p, const FftGeom& g, char* smem, int line, int row,
                               int inner0) {
@@ -461,28 +378,16 @@ struct Inverse {
     const float2* src = p.spec + ((long long)kx * N) * bin_stride + (long long)row * p.kc + inner;
     const int pitch = g.pitch2;
     const int y0 = p.off_y, y1 = p.off_y + g.he;
-    if constexpr (!kTwoStep) {
-      float2 u[N];
+    float2 u[N];
 #pragma unroll
-      for (int ky = 0; ky < N; ++ky) u[ky] = live ? src[ky * bin_stride] : make_float2(0.f, 0.f);
-      fft_inreg<N, true>(u);
+    for (int ky = 0; ky < N; ++ky) u[ky] = live ? src[ky * bin_stride] : make_float2(0.f, 0.f);
+    fft_inreg<N, true>(u);
 #pragma unroll
-      for (int y = 0; y < N; ++y)
-        if (y >= y0 && y < y1) mid[(y - y0) * pitch] = u[y];
-    } else {
-      float2* col = reinterpret_cast<float2*>(smem + g.off_a) + line;
-      fft_two_step_first<N, true>(
-          [&](int n) { return live ? src[n * bin_stride] : make_float2(0.f, 0.f); },
-          [&](int slot, float2 v) { col[slot * pitch] = v; });
-      fft_two_step_second<N, true>([&](int slot) { return col[slot * pitch]; },
-                                   [&](int y, int, float2 v) {
-                                     if (y >= y0 && y < y1) mid[(y - y0) * pitch] = v;
-                                   });
-    }
+    for (int y = 0; y < N; ++y)
+      if (y >= y0 && y < y1) mid[(y - y0) * pitch] = u[y];
   }
 
-  // Phase 2a: gather the two half spectra of rows (j, j+hh) into one complex line
-  // (registers, or the private shared-memory line for the two-step sizes).
+  // Phase 2a: gather the two half spectra of rows (j, j+hh) into one complex line.
   static FBF_HD void row_fetch(const FftGeom& g, char* smem, int line, LineRegs<N>& regs) {
     if (line >= g.lines1) return;
     const float2* mid = reinterpret_cast<const float2*>(smem + g.off_b);
@@ -490,24 +395,12 @@ struct Inverse {
     const bool has_b = (j + g.hh) < g.he;
     const float2* pa = mid + j * g.pitch2 + t;
     const float2* pb = mid + (j + g.hh) * g.pitch2 + t;
-    if constexpr (!kTwoStep) {
 #pragma unroll
-      for (int k = 0; k <= N / 2; ++k) {
-        const float2 a = pa[k * T];
-        const float2 b = has_b ? pb[k * T] : make_float2(0.f, 0.f);
-        regs.v[k] = tangle_low(a, b);
-        if (k > 0 && k < N / 2) regs.v[N - k] = tangle_high(a, b);
-      }
-    } else {
-      float2* ra = reinterpret_cast<float2*>(smem + g.off_a) + line;
-      const int pitch = g.pitch1;
-#pragma unroll 1
-      for (int k = 0; k <= N / 2; ++k) {
-        const float2 a = pa[k * T];
-        const float2 b = has_b ? pb[k * T] : make_float2(0.f, 0.f);
-        ra[k * pitch] = tangle_low(a, b);
-        if (k > 0 && k < N / 2) ra[(N - k) * pitch] = tangle_high(a, b);
-      }
+    for (int k = 0; k <= N / 2; ++k) {
+      const float2 a = pa[k * T];
+      const float2 b = has_b ? pb[k * T] : make_float2(0.f, 0.f);
+      regs.v[k] = tangle_low(a, b);
+      if (k > 0 && k < N / 2) regs.v[N - k] = tangle_high(a, b);
     }
   }
 
@@ -522,27 +415,13 @@ struct Inverse {
     float* sa = stage + t * plane_pitch_f + j * g.we;
     float* sb = stage + t * plane_pitch_f + (j + g.hh) * g.we;
     const int x0 = p.off_x, x1 = p.off_x + g.we;
-    if constexpr (!kTwoStep) {
-      fft_inreg<N, true>(regs.v);
+    fft_inreg<N, true>(regs.v);
 #pragma unroll
-      for (int x = 0; x < N; ++x) {
-        if (x >= x0 && x < x1) {
-          sa[x - x0] = regs.v[x].x;
-          if (has_b) sb[x - x0] = regs.v[x].y;
-        }
+    for (int x = 0; x < N; ++x) {
+      if (x >= x0 && x < x1) {
+        sa[x - x0] = regs.v[x].x;
+        if (has_b) sb[x - x0] = regs.v[x].y;
       }
-    } else {
-      float2* ra = reinterpret_cast<float2*>(smem + g.off_a) + line;
-      const int pitch = g.pitch1;
-      fft_two_step_first<N, true>([&](int n) { return ra[n * pitch]; },
-                                  [&](int slot, float2 v) { ra[slot * pitch] = v; });
-      fft_two_step_second<N, true>([&](int slot) { return ra[slot * pitch]; },
-                                   [&](int x, int, float2 v) {
-                                     if (x >= x0 && x < x1) {
-                                       sa[x - x0] = v.x;
-                                       if (has_b) sb[x - x0] = v.y;
-                                     }
-                                   });
     }
   }
 
@@ -552,17 +431,267 @@ struct Inverse {
     const float* stage = reinterpret_cast<const float*>(smem + g.off_b);
     const int per_plane = g.he * g.we;
     const int plane_pitch_f = per_plane | 1;
-    const int total = per_plane * T;
-    for (int i = tid; i < total; i += nthreads) {
-      const int t = i / per_plane;
-      const int r = i - t * per_plane;
+    float* base = p.real_out + (row * p.real_row_stride + inner0 * p.real_inner_stride) * (long long)per_plane;
+    const long long tstride = p.real_inner_stride * (long long)per_plane;
+    for (int t = 0; t < T; ++t) {
+      const int inner = inner0 + t;
+      if (inner >= p.n_inner) break;
+      const float bias = p.bias ? p.bias[inner] : 0.f;
+      const float* src = stage + t * plane_pitch_f;
+      float* dst = base + t * tstride;
+      for (int r = tid; r < per_plane; r += nthreads) {
+        const float v = src[r] + bias;
+        dst[r] = p.accumulate ? (dst[r] + v) : v;
+      }
+    }
+  }
+};
+
+// ===========================================================================
+// Cooperative kernels, N = 64 / 128.  Work is split into items that the threads of
+// the block pick up round-robin; barriers separate the phases.
+// ===========================================================================
+template <int N, int T>
+struct CoopForward {
+  static constexpr int N1 = Split<N>::N1, N2 = Split<N>::N2, KX = N / 2 + 1;
+
+  // Row step 1 for lines [line0, line0 + nl): straight from global memory (N2
+  // neighbouring floats per row and lane group: whole 32-byte sectors), N1-point
+  // transform, twiddle, into the row buffer.
+  static FBF_HD void row_step1(const FftParams& p, const FftGeom& g, char* smem, int tid, int nthreads,
+                               int row, int inner0, int line0, int nl) {
+    float2* rb = reinterpret_cast<float2*>(smem + g.off_a);
+    const long long plane_elems = (long long)p.h * p.w;
+    const float* base = p.real_in + (row * p.real_row_stride + inner0 * p.real_inner_stride) * plane_elems;
+    const long long tstride = p.real_inner_stride * plane_elems;
+    for (int item = tid; item < nl * N2; item += nthreads) {
+      const int ll = item / N2, n2 = item - ll * N2;
+      const int line = line0 + ll;
+      const int t = line / g.hh, j = line - t * g.hh;
+      const bool live = inner0 + t < p.n_inner;
+      const float* plane = base + t * tstride;
+      const int ya = j - p.off_y, yb = j + g.hh - p.off_y;
+      const bool va = live && ya >= 0 && ya < p.h, vb = live && yb >= 0 && yb < p.h;
+      float2 v[N1];
+#pragma unroll
+      for (int n1 = 0; n1 < N1; ++n1) {
+        const int x = N2 * n1 + n2 - p.off_x;
+        const bool vx = x >= 0 && x < p.w;
+        v[n1] = make_float2(va && vx ? plane[ya * p.w + x] : 0.f, vb && vx ? plane[yb * p.w + x] : 0.f);
+      }
+      fft_inreg<N1, false>(v);
+      float2* dst = rb + ll * g.pitch1 + n2;
+      dst[0] = v[0];
+#pragma unroll
+      for (int k1 = 1; k1 < N1; ++k1)
+        dst[k1 * (N2 + 1)] = cmul(v[k1], tw128_runtime<false>(n2 * k1 * (128 / N)));
+    }
+  }
+
+  // Row step 2: N2-point transforms of residues k1 and N1-k1 together, so that Z[k] and
+  // Z[N-k] meet in one thread; the row pair is split there and written to mid.
+  static FBF_HD void row_step2(const FftGeom& g, char* smem, int tid, int nthreads, int line0, int nl) {
+    const float2* rb = reinterpret_cast<const float2*>(smem + g.off_a);
+    float2* mid = reinterpret_cast<float2*>(smem + g.off_b);
+    constexpr int Q = N1 / 2 + 1;
+    for (int item = tid; item < nl * Q; item += nthreads) {
+      const int ll = item / Q, q = item - ll * Q;
+      const int line = line0 + ll;
+      const int t = line / g.hh, j = line - t * g.hh;
+      const bool has_b = (j + g.hh) < g.he;
+      const bool self = (q == 0) || (q == N1 / 2);
+      const float2* src = rb + ll * g.pitch1;
+      float2 u[N2], ub[N2];
+#pragma unroll
+      for (int n2 = 0; n2 < N2; ++n2) u[n2] = src[q * (N2 + 1) + n2];
+      fft_inreg<N2, false>(u);
+      if (!self) {
+#pragma unroll
+        for (int n2 = 0; n2 < N2; ++n2) ub[n2] = src[(N1 - q) * (N2 + 1) + n2];
+        fft_inreg<N2, false>(ub);
+      }
+      float2* ma = mid + j * g.pitch2 + t * KX;
+      float2* mb = mid + (j + g.hh) * g.pitch2 + t * KX;
+#pragma unroll
+      for (int k2 = 0; k2 < N2; ++k2) {
+        const int k = q + N1 * k2;
+        float2 zk, znk;
+        int kk;
+        if (self) {
+          if (k > N / 2) continue;
+          zk = u[k2];
+          znk = (q == 0) ? u[(N2 - k2) % N2] : u[N2 - 1 - k2];
+          kk = k;
+        } else if (k <= N / 2) {
+          zk = u[k2];
+          znk = ub[N2 - 1 - k2];
+          kk = k;
+        } else {
+          zk = ub[N2 - 1 - k2];
+          znk = u[k2];
+          kk = N - k;
+        }
+        float2 a, b;
+        untangle_pair(zk, znk, a, b);
+        ma[kk] = a;
+        if (has_b) mb[kk] = b;
+      }
+    }
+  }
+
+  // Column step 1, in place on mid: item (col, n2) owns rows {N2*n1 + n2}.
+  static FBF_HD void col_step1(const FftGeom& g, char* smem, int tid, int nthreads) {
+    float2* mid = reinterpret_cast<float2*>(smem + g.off_b);
+    const int cols = g.lines2;
+    for (int item = tid; item < cols * N2; item += nthreads) {
+      const int n2 = item / cols, col = item - n2 * cols;
+      float2* c = mid + col;
+      float2 v[N1];
+#pragma unroll
+      for (int n1 = 0; n1 < N1; ++n1) {
+        const int y = N2 * n1 + n2;
+        v[n1] = y < g.he ? c[y * g.pitch2] : make_float2(0.f, 0.f);
+      }
+      fft_inreg<N1, false>(v);
+      c[n2 * g.pitch2] = v[0];
+#pragma unroll
+      for (int k1 = 1; k1 < N1; ++k1)
+        c[(N2 * k1 + n2) * g.pitch2] = cmul(v[k1], tw128_runtime<false>(n2 * k1 * (128 / N)));
+    }
+  }
+
+  // Column step 2: item (col, k1) reads rows {N2*k1 + n2} and writes bins ky = k1 + N1*k2.
+  static FBF_HD void col_step2(const FftParams& p, const FftGeom& g, const char* smem, int tid,
+                               int nthreads, int row, int inner0) {
+    const float2* mid = reinterpret_cast<const float2*>(smem + g.off_b);
+    const int cols = g.lines2;
+    const long long bin_stride = (long long)p.n_rows * p.kc;
+    for (int item = tid; item < cols * N1; item += nthreads) {
+      const int k1 = item / cols, col = item - k1 * cols;
+      const int t = col / KX, kx = col - t * KX;
+      const int inner = inner0 + t;
+      if (inner >= p.kc) continue;
+      const float2* c = mid + col;
+      float2 u[N2];
+#pragma unroll
+      for (int n2 = 0; n2 < N2; ++n2) u[n2] = c[(N2 * k1 + n2) * g.pitch2];
+      fft_inreg<N2, false>(u);
+      float2* dst = p.spec + ((long long)kx * N + k1) * bin_stride + (long long)row * p.kc + inner;
+#pragma unroll
+      for (int k2 = 0; k2 < N2; ++k2) dst[(long long)(N1 * k2) * bin_stride] = u[k2];
+    }
+  }
+};
+
+template <int N, int T>
+struct CoopInverse {
+  static constexpr int N1 = Split<N>::N1, N2 = Split<N>::N2, KX = N / 2 + 1;
+
+  // Column step 1: bins of column (t, kx) from global memory, N1-point inverse transform,
+  // twiddle, written to rows k1 + N1*n2 of mid so that step 2 can run in place.
+  static FBF_HD void col_step1(const FftParams& p, const FftGeom& g, char* smem, int tid, int nthreads,
+                               int row, int inner0) {
+    float2* mid = reinterpret_cast<float2*>(smem + g.off_b);
+    const int cols = g.lines2;
+    const long long bin_stride = (long long)p.n_rows * p.kc;
+    for (int item = tid; item < cols * N2; item += nthreads) {
+      const int n2 = item / cols, col = item - n2 * cols;
+      const int t = col / KX, kx = col - t * KX;
+      const bool live = inner0 + t < p.n_inner;
+      const float2* src = p.spec + ((long long)kx * N + n2) * bin_stride + (long long)row * p.kc + inner0 + t;
+      float2 v[N1];
+#pragma unroll
+      for (int n1 = 0; n1 < N1; ++n1)
+        v[n1] = live ? src[(long long)(N2 * n1) * bin_stride] : make_float2(0.f, 0.f);
+      fft_inreg<N1, true>(v);
+      float2* c = mid + col;
+      c[(N1 * n2) * g.pitch2] = v[0];
+#pragma unroll
+      for (int k1 = 1; k1 < N1; ++k1)
+        c[(k1 + N1 * n2) * g.pitch2] = cmul(v[k1], tw128_runtime<true>(n2 * k1 * (128 / N)));
+    }
+  }
+
+  // Column step 2, in place: item (col, k1) owns rows {k1 + N1*n2}; afterwards row y of
+  // mid holds the half spectrum along x of real row y.
+  static FBF_HD void col_step2(const FftGeom& g, char* smem, int tid, int nthreads) {
+    float2* mid = reinterpret_cast<float2*>(smem + g.off_b);
+    const int cols = g.lines2;
+    for (int item = tid; item < cols * N1; item += nthreads) {
+      const int k1 = item / cols, col = item - k1 * cols;
+      float2* c = mid + col;
+      float2 u[N2];
+#pragma unroll
+      for (int n2 = 0; n2 < N2; ++n2) u[n2] = c[(k1 + N1 * n2) * g.pitch2];
+      fft_inreg<N2, true>(u);
+#pragma unroll
+      for (int k2 = 0; k2 < N2; ++k2) c[(k1 + N1 * k2) * g.pitch2] = u[k2];
+    }
+  }
+
+  // Row step 1 for lines [line0, line0+nl): rows (y0+j, y0+j+hh) of mid become one complex
+  // line (Hermitian extension), N1-point inverse transform, twiddle, into the row buffer.
+  static FBF_HD void row_step1(const FftParams& p, const FftGeom& g, char* smem, int tid, int nthreads,
+                               int line0, int nl) {
+    float2* rb = reinterpret_cast<float2*>(smem + g.off_a);
+    const float2* mid = reinterpret_cast<const float2*>(smem + g.off_b);
+    for (int item = tid; item < nl * N2; item += nthreads) {
+      const int ll = item / N2, n2 = item - ll * N2;
+      const int line = line0 + ll;
+      const int t = line / g.hh, j = line - t * g.hh;
+      const bool has_b = (j + g.hh) < g.he;
+      const float2* pa = mid + (p.off_y + j) * g.pitch2 + t * KX;
+      const float2* pb = mid + (p.off_y + j + g.hh) * g.pitch2 + t * KX;
+      float2 v[N1];
+#pragma unroll
+      for (int n1 = 0; n1 < N1; ++n1) {
+        const int k = N2 * n1 + n2;
+        const int kk = k <= N / 2 ? k : N - k;
+        const float2 a = pa[kk];
+        const float2 b = has_b ? pb[kk] : make_float2(0.f, 0.f);
+        v[n1] = k <= N / 2 ? tangle_low(a, b) : tangle_high(a, b);
+      }
+      fft_inreg<N1, true>(v);
+      float2* dst = rb + ll * g.pitch1 + n2;
+      dst[0] = v[0];
+#pragma unroll
+      for (int k1 = 1; k1 < N1; ++k1)
+        dst[k1 * (N2 + 1)] = cmul(v[k1], tw128_runtime<true>(n2 * k1 * (128 / N)));
+    }
+  }
+
+  // Row step 2: item (line, k1) produces x = k1 + N1*k2 of both rows of the pair and
+  // writes the crop columns straight to global memory (N1 neighbouring floats per row and
+  // lane group: whole 32-byte sectors), bias added.
+  static FBF_HD void row_step2(const FftParams& p, const FftGeom& g, const char* smem, int tid,
+                               int nthreads, int row, int inner0, int line0, int nl) {
+    const float2* rb = reinterpret_cast<const float2*>(smem + g.off_a);
+    const long long plane_elems = (long long)g.he * g.we;
+    float* base = p.real_out + (row * p.real_row_stride + inner0 * p.real_inner_stride) * plane_elems;
+    const long long tstride = p.real_inner_stride * plane_elems;
+    for (int item = tid; item < nl * N1; item += nthreads) {
+      const int ll = item / N1, k1 = item - ll * N1;
+      const int line = line0 + ll;
+      const int t = line / g.hh, j = line - t * g.hh;
       const int inner = inner0 + t;
       if (inner >= p.n_inner) continue;
-      float v = stage[t * plane_pitch_f + r];
-      if (p.bias) v += p.bias[inner];
-      float* dst = p.real_out +
-                   (row * p.real_row_stride + inner * p.real_inner_stride) * (long long)per_plane + r;
-      *dst = p.accumulate ? (*dst + v) : v;
+      const bool has_b = (j + g.hh) < g.he;
+      const float2* src = rb + ll * g.pitch1 + k1 * (N2 + 1);
+      float2 u[N2];
+#pragma unroll
+      for (int n2 = 0; n2 < N2; ++n2) u[n2] = src[n2];
+      fft_inreg<N2, true>(u);
+      const float bias = p.bias ? p.bias[inner] : 0.f;
+      float* da = base + t * tstride + (long long)j * g.we;
+      float* db = da + (long long)g.hh * g.we;
+#pragma unroll
+      for (int k2 = 0; k2 < N2; ++k2) {
+        const int x = k1 + N1 * k2 - p.off_x;
+        if (x < 0 || x >= g.we) continue;
+        const float va = u[k2].x + bias, vb = u[k2].y + bias;
+        da[x] = p.accumulate ? da[x] + va : va;
+        if (has_b) db[x] = p.accumulate ? db[x] + vb : vb;
+      }
     }
   }
 };

@@ -8,6 +8,7 @@
 // (two launches through a transposed global buffer, :56-104) every size is a
 // single launch with no global scratch.
 #include <atomic>
+#include <cstdlib>
 
 #include "kernels.h"
 
@@ -56,13 +57,65 @@ fft2d_inverse_kernel(const __grid_constant__ FftParams p, const __grid_constant_
   Inverse<N, T>::store(p, g, smem, tid, blockDim.x, row, inner0);
 }
 
+template <int N, int T>
+__global__ void __launch_bounds__(256)
+fft2d_forward_coop_kernel(const __grid_constant__ FftParams p, const __grid_constant__ FftGeom g) {
+  extern __shared__ __align__(16) char smem[];
+  const int tid = threadIdx.x, nth = blockDim.x;
+  const int row = blockIdx.y;
+  const int inner0 = blockIdx.x * T;
+  for (int line0 = 0; line0 < g.lines1; line0 += g.chunk) {
+    const int nl = min(g.chunk, g.lines1 - line0);
+    CoopForward<N, T>::row_step1(p, g, smem, tid, nth, row, inner0, line0, nl);
+    __syncthreads();
+    CoopForward<N, T>::row_step2(g, smem, tid, nth, line0, nl);
+    __syncthreads();
+  }
+  CoopForward<N, T>::col_step1(g, smem, tid, nth);
+  __syncthreads();
+  CoopForward<N, T>::col_step2(p, g, smem, tid, nth, row, inner0);
+}
+
+template <int N, int T>
+__global__ void __launch_bounds__(256)
+fft2d_inverse_coop_kernel(const __grid_constant__ FftParams p, const __grid_constant__ FftGeom g) {
+  extern __shared__ __align__(16) char smem[];
+  const int tid = threadIdx.x, nth = blockDim.x;
+  const int row = blockIdx.y;
+  const int inner0 = blockIdx.x * T;
+  CoopInverse<N, T>::col_step1(p, g, smem, tid, nth, row, inner0);
+  __syncthreads();
+  CoopInverse<N, T>::col_step2(g, smem, tid, nth);
+  __syncthreads();
+  for (int line0 = 0; line0 < g.lines1; line0 += g.chunk) {
+    const int nl = min(g.chunk, g.lines1 - line0);
+    CoopInverse<N, T>::row_step1(p, g, smem, tid, nth, line0, nl);
+    __syncthreads();
+    CoopInverse<N, T>::row_step2(p, g, smem, tid, nth, row, inner0, line0, nl);
+    __syncthreads();
+  }
+}
+
 constexpr int kSmemMax = 227 * 1024;
 constexpr int kSmemTwoBlocks = 113 * 1024;
 
-constexpr bool tile_allowed(int N, int T) { return (N / 2 + 1) * T <= 512; }
+constexpr bool tile_allowed(int N, int T) { return N > 32 ? T <= 8 : (N / 2 + 1) * T <= 512; }
+
+// Tuning aid: FBFFTCONV_TILE=<planes per block> overrides the automatic choice when valid.
+int tile_override() {
+  static int value = [] {
+    const char* e = getenv("FBFFTCONV_TILE");
+    return e ? atoi(e) : 0;
+  }();
+  return value;
+}
 
 template <class GeomFn>
 int pick_tile(int N, GeomFn geom) {
+  const int forced = tile_override();
+  if (forced > 0 && forced <= 16 && (forced & (forced - 1)) == 0 && tile_allowed(N, forced) &&
+      geom(forced).smem_bytes <= kSmemMax)
+    return forced;
   int best_any = 0;
   for (int T = 16; T >= 1; T >>= 1) {
     if (!tile_allowed(N, T)) continue;
@@ -79,8 +132,13 @@ cudaError_t run_forward(const FftParams& p, cudaStream_t stream) {
     return cudaErrorInvalidConfiguration;
   } else {
     const FftGeom g = forward_geom(N, T, p.h, p.w, p.off_y, p.off_x);
-    if (g.threads != block_threads<N, T>()) return cudaErrorInvalidConfiguration;
-    auto kernel = fft2d_forward_kernel<N, T>;
+    void (*kernel)(FftParams, FftGeom);
+    if constexpr (N > 32) {
+      kernel = fft2d_forward_coop_kernel<N, T>;
+    } else {
+      if (g.threads != block_threads<N, T>()) return cudaErrorInvalidConfiguration;
+      kernel = fft2d_forward_kernel<N, T>;
+    }
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, g.smem_bytes);
     if (e != cudaSuccess) return e;
     dim3 grid((p.kc + T - 1) / T, p.n_rows);
@@ -96,8 +154,13 @@ cudaError_t run_inverse(const FftParams& p, cudaStream_t stream) {
     return cudaErrorInvalidConfiguration;
   } else {
     const FftGeom g = inverse_geom(N, T, p.h, p.w);
-    if (g.threads != block_threads<N, T>()) return cudaErrorInvalidConfiguration;
-    auto kernel = fft2d_inverse_kernel<N, T>;
+    void (*kernel)(FftParams, FftGeom);
+    if constexpr (N > 32) {
+      kernel = fft2d_inverse_coop_kernel<N, T>;
+    } else {
+      if (g.threads != block_threads<N, T>()) return cudaErrorInvalidConfiguration;
+      kernel = fft2d_inverse_kernel<N, T>;
+    }
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, g.smem_bytes);
     if (e != cudaSuccess) return e;
     dim3 grid((p.n_inner + T - 1) / T, p.n_rows);

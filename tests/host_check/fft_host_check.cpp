@@ -3,6 +3,7 @@
 // loops over thread indices, phase by phase, with shared memory pre-filled with NaN
 // so that a read of an unwritten slot shows up in the result.  Checks the index
 // arithmetic of the kernels without a GPU; it is never part of the product path.
+#include <algorithm>
 #include <cstring>
 #include <limits>
 #include <vector>
@@ -19,19 +20,34 @@ void run_forward(const FftParams& p) {
   const int tiles = (p.kc + T - 1) / T;
   std::vector<char> smem(g.smem_bytes);
   std::vector<LineRegs<N>> regs(g.threads);
+  const int nth = g.threads;
   for (int row = 0; row < p.n_rows; ++row) {
     for (int tile = 0; tile < tiles; ++tile) {
       const int inner0 = tile * T;
       std::memset(smem.data(), 0xFF, smem.size());
-      for (int tid = 0; tid < g.threads; ++tid)
-        Forward<N, T>::load(p, g, smem.data(), tid, g.threads, row, inner0);
-      for (int tid = 0; tid < g.threads; ++tid)
-        Forward<N, T>::row_fetch(g, smem.data(), tid, regs[tid]);
-      if (!two_step(N)) std::memset(smem.data(), 0xFF, smem.size());  // aliasing: A is dead now
-      for (int tid = 0; tid < g.threads; ++tid)
-        Forward<N, T>::row_pass(g, smem.data(), tid, regs[tid]);
-      for (int tid = 0; tid < g.threads; ++tid)
-        Forward<N, T>::col_pass(p, g, smem.data(), tid, row, inner0);
+      if constexpr (N > 32) {
+        for (int line0 = 0; line0 < g.lines1; line0 += g.chunk) {
+          const int nl = std::min(g.chunk, g.lines1 - line0);
+          std::memset(smem.data() + g.off_a, 0xFF, g.off_b - g.off_a);
+          for (int tid = 0; tid < nth; ++tid)
+            CoopForward<N, T>::row_step1(p, g, smem.data(), tid, nth, row, inner0, line0, nl);
+          for (int tid = 0; tid < nth; ++tid)
+            CoopForward<N, T>::row_step2(g, smem.data(), tid, nth, line0, nl);
+        }
+        for (int tid = 0; tid < nth; ++tid) CoopForward<N, T>::col_step1(g, smem.data(), tid, nth);
+        for (int tid = 0; tid < nth; ++tid)
+          CoopForward<N, T>::col_step2(p, g, smem.data(), tid, nth, row, inner0);
+      } else {
+        for (int tid = 0; tid < g.threads; ++tid)
+          Forward<N, T>::load(p, g, smem.data(), tid, g.threads, row, inner0);
+        for (int tid = 0; tid < g.threads; ++tid)
+          Forward<N, T>::row_fetch(g, smem.data(), tid, regs[tid]);
+        std::memset(smem.data(), 0xFF, smem.size());  // aliasing: the row buffer is dead now
+        for (int tid = 0; tid < g.threads; ++tid)
+          Forward<N, T>::row_pass(g, smem.data(), tid, regs[tid]);
+        for (int tid = 0; tid < g.threads; ++tid)
+          Forward<N, T>::col_pass(p, g, smem.data(), tid, row, inner0);
+      }
     }
   }
 }
@@ -46,15 +62,30 @@ void run_inverse(const FftParams& p, int oh, int ow) {
     for (int tile = 0; tile < tiles; ++tile) {
       const int inner0 = tile * T;
       std::memset(smem.data(), 0xFF, smem.size());
-      for (int tid = 0; tid < g.threads; ++tid)
-        Inverse<N, T>::col_pass(p, g, smem.data(), tid, row, inner0);
-      for (int tid = 0; tid < g.threads; ++tid)
-        Inverse<N, T>::row_fetch(g, smem.data(), tid, regs[tid]);
-      std::memset(smem.data() + g.off_b, 0xFF, smem.size() - g.off_b);  // mid is dead now
-      for (int tid = 0; tid < g.threads; ++tid)
-        Inverse<N, T>::row_pass(p, g, smem.data(), tid, regs[tid]);
-      for (int tid = 0; tid < g.threads; ++tid)
-        Inverse<N, T>::store(p, g, smem.data(), tid, g.threads, row, inner0);
+      if constexpr (N > 32) {
+        const int nth = g.threads;
+        for (int tid = 0; tid < nth; ++tid)
+          CoopInverse<N, T>::col_step1(p, g, smem.data(), tid, nth, row, inner0);
+        for (int tid = 0; tid < nth; ++tid) CoopInverse<N, T>::col_step2(g, smem.data(), tid, nth);
+        for (int line0 = 0; line0 < g.lines1; line0 += g.chunk) {
+          const int nl = std::min(g.chunk, g.lines1 - line0);
+          std::memset(smem.data() + g.off_a, 0xFF, g.off_b - g.off_a);
+          for (int tid = 0; tid < nth; ++tid)
+            CoopInverse<N, T>::row_step1(p, g, smem.data(), tid, nth, line0, nl);
+          for (int tid = 0; tid < nth; ++tid)
+            CoopInverse<N, T>::row_step2(p, g, smem.data(), tid, nth, row, inner0, line0, nl);
+        }
+      } else {
+        for (int tid = 0; tid < g.threads; ++tid)
+          Inverse<N, T>::col_pass(p, g, smem.data(), tid, row, inner0);
+        for (int tid = 0; tid < g.threads; ++tid)
+          Inverse<N, T>::row_fetch(g, smem.data(), tid, regs[tid]);
+        std::memset(smem.data() + g.off_b, 0xFF, smem.size() - g.off_b);  // mid is dead now
+        for (int tid = 0; tid < g.threads; ++tid)
+          Inverse<N, T>::row_pass(p, g, smem.data(), tid, regs[tid]);
+        for (int tid = 0; tid < g.threads; ++tid)
+          Inverse<N, T>::store(p, g, smem.data(), tid, g.threads, row, inner0);
+      }
     }
   }
 }
@@ -119,11 +150,13 @@ int hostcheck_forward_smem_bytes(int N, int T, int h, int w, int pad_u, int pad_
 }
 int hostcheck_forward_threads(int N, int T, int h, int w, int pad_u, int pad_l) {
   const FftGeom g = forward_geom(N, T, h, w, pad_u, pad_l);
+  if (cooperative(N)) return T <= 8 ? g.threads : -1;
   return (g.lines1 > g.threads || g.lines2 > g.threads) ? -1 : g.threads;
 }
 int hostcheck_inverse_smem_bytes(int N, int T, int oh, int ow) { return inverse_geom(N, T, oh, ow).smem_bytes; }
 int hostcheck_inverse_threads(int N, int T, int oh, int ow) {
   const FftGeom g = inverse_geom(N, T, oh, ow);
+  if (cooperative(N)) return T <= 8 ? g.threads : -1;
   return (g.lines1 > g.threads || g.lines2 > g.threads) ? -1 : g.threads;
 }
 

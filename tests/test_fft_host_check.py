@@ -31,16 +31,19 @@ def _bin_major(spec_plane_major):
     return spec_plane_major.transpose(3, 2, 0, 1).reshape(half * n, d1, d2)
 
 
-CASES = [(N, T) for N in (8, 16, 32, 64, 128) for T in (1, 4, 16) if (N // 2 + 1) * T <= 512]
+CASES = [(N, T) for N in (8, 16, 32, 64, 128) for T in (1, 2, 4, 8, 16)
+         if (T <= (8 if N == 64 else 2) if N > 32 else (N // 2 + 1) * T <= 512)]
 
 
 @pytest.mark.parametrize("N,T", CASES)
 def test_forward(hc, N, T):
     rng = np.random.default_rng(N * 100 + T)
+    ran = 0
     for (h, w, pu, pl) in [(N, N, 0, 0), (3, 3, 0, 0), (N - 3, N - 5, 1, 2), (1, 1, 0, 0)]:
         if hc.hostcheck_forward_smem_bytes(N, T, h, w, pu, pl) > 227 * 1024:
             continue
         assert hc.hostcheck_forward_threads(N, T, h, w, pu, pl) > 0
+        ran += 1
         for transposed in (False, True):
             d1, d2 = (2, 5) if not transposed else (5, 2)
             x = rng.standard_normal((d1, d2, h, w)).astype(np.float32)
@@ -57,6 +60,7 @@ def test_forward(hc, N, T):
             got = spec[..., 0] + 1j * spec[..., 1]
             assert np.abs(got[:, :, :inner] - ref).max() <= 3e-6 * np.abs(ref).max()
             assert np.all(got[:, :, inner:] == 0), "padding planes must be written as zero"
+    assert ran > 0
 
 
 @pytest.mark.parametrize("N,T", CASES)
