@@ -11,7 +11,8 @@ import os
 from ctypes import POINTER, c_char_p, c_float, c_int, c_int32, c_size_t, c_uint32, c_uint64, c_void_p
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libfbfftconv.so")
+# FBFFTCONV_LIB points at another build of the same library (tuning experiments)
+LIB_PATH = os.environ.get("FBFFTCONV_LIB") or os.path.join(HERE, "libfbfftconv.so")
 
 OK = 0
 ERR_INVALID_ARGUMENT = 1

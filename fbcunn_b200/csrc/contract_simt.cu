@@ -14,7 +14,6 @@ namespace fbfft {
 
 namespace {
 
-constexpr int BM = 64, BN = 64, BK = 8, PAD = 2;
 constexpr int THREADS = 256;
 
 __device__ __forceinline__ void cmac(float2& acc, const float2 a, const float2 b) {
@@ -24,8 +23,17 @@ __device__ __forceinline__ void cmac(float2& acc, const float2 a, const float2 b
   acc.y = fmaf(a.y, b.x, acc.y);
 }
 
+// Block tile BM x BN complex results, thread tile TM x TN, K step of 8 complex.
+// (64,64,4,4) is the general shape; (128,4,1,2) serves operands with at most four
+// columns (three input planes padded to four), where a wide tile would compute zeros.
+template <int BM, int BN, int TM, int TN>
 __global__ void __launch_bounds__(THREADS)
 contract_simt_kernel(const __grid_constant__ ContractParams p) {
+  constexpr int BK = 8, PAD = 2;
+  constexpr int TX = BN / TN;  // threads along n
+  static_assert((BM / TM) * TX == THREADS, "tile shape must use the whole block");
+  static_assert(TM == 1 || TM % 2 == 0, "vector loads need pairs");
+  static_assert(TN % 2 == 0, "vector loads need pairs");
   __shared__ __align__(16) float2 As[2][BK][BM + PAD];
   __shared__ __align__(16) float2 Bs[2][BK][BN + PAD];
 
@@ -33,78 +41,111 @@ contract_simt_kernel(const __grid_constant__ ContractParams p) {
   const int m0 = blockIdx.y * BM;
   const int n0 = blockIdx.x * BN;
   const int tid = threadIdx.x;
-  const int tx = tid & 15, ty = tid >> 4;
+  const int tx = tid % TX, ty = tid / TX;
 
   const float2* A = p.a + (long long)bin * p.m * p.lda;
   const float2* B = p.b + (long long)bin * p.n * p.ldb;
   float2* C = p.c + (long long)bin * p.m * p.ldc;
 
-  // loader mapping: one float4 (two complex) per thread and operand
-  const int lr = tid >> 2;        // tile row 0..63
-  const int lc = (tid & 3) * 2;   // complex column 0,2,4,6
+  // loaders: one float4 (two complex) per slot; a tile has rows*4 slots
   const float sa = p.conj_a ? -1.f : 1.f;
   const float sb = p.conj_b ? -1.f : 1.f;
+  constexpr int A_SLOTS = BM * 4, B_SLOTS = BN * 4;
+  constexpr int A_PER = (A_SLOTS + THREADS - 1) / THREADS, B_PER = (B_SLOTS + THREADS - 1) / THREADS;
 
-  auto fetch = [&](const float2* base, int rows, int ld, int r0, int k0) -> float4 {
-    const int r = r0 + lr, k = k0 + lc;
+  auto fetch = [&](const float2* base, int rows, int ld, int r, int k) -> float4 {
     if (r < rows && k < ld) return *reinterpret_cast<const float4*>(base + (long long)r * ld + k);
     return make_float4(0.f, 0.f, 0.f, 0.f);
   };
 
-  float2 acc[4][4];
+  float2 acc[TM][TN];
 #pragma unroll
-  for (int i = 0; i < 4; ++i)
+  for (int i = 0; i < TM; ++i)
 #pragma unroll
-    for (int j = 0; j < 4; ++j) acc[i][j] = make_float2(0.f, 0.f);
+    for (int j = 0; j < TN; ++j) acc[i][j] = make_float2(0.f, 0.f);
+
+  float4 ra[A_PER], rb[B_PER];
+  auto fetch_tiles = [&](int k0) {
+#pragma unroll
+    for (int i = 0; i < A_PER; ++i) {
+      const int slot = tid + i * THREADS;
+      ra[i] = slot < A_SLOTS ? fetch(A, p.m, p.lda, m0 + (slot >> 2), k0 + (slot & 3) * 2) : make_float4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int i = 0; i < B_PER; ++i) {
+      const int slot = tid + i * THREADS;
+      rb[i] = slot < B_SLOTS ? fetch(B, p.n, p.ldb, n0 + (slot >> 2), k0 + (slot & 3) * 2) : make_float4(0, 0, 0, 0);
+    }
+  };
+  auto stash = [&](int buf) {
+#pragma unroll
+    for (int i = 0; i < A_PER; ++i) {
+      const int slot = tid + i * THREADS;
+      if (slot < A_SLOTS) {
+        const int r = slot >> 2, c = (slot & 3) * 2;
+        As[buf][c][r] = make_float2(ra[i].x, sa * ra[i].y);
+        As[buf][c + 1][r] = make_float2(ra[i].z, sa * ra[i].w);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < B_PER; ++i) {
+      const int slot = tid + i * THREADS;
+      if (slot < B_SLOTS) {
+        const int r = slot >> 2, c = (slot & 3) * 2;
+        Bs[buf][c][r] = make_float2(rb[i].x, sb * rb[i].y);
+        Bs[buf][c + 1][r] = make_float2(rb[i].z, sb * rb[i].w);
+      }
+    }
+  };
 
   const int ksteps = (p.k + BK - 1) / BK;
-  float4 ra = fetch(A, p.m, p.lda, m0, 0);
-  float4 rb = fetch(B, p.n, p.ldb, n0, 0);
-
+  fetch_tiles(0);
   for (int ks = 0; ks < ksteps; ++ks) {
     const int buf = ks & 1;
-    As[buf][lc][lr] = make_float2(ra.x, sa * ra.y);
-    As[buf][lc + 1][lr] = make_float2(ra.z, sa * ra.w);
-    Bs[buf][lc][lr] = make_float2(rb.x, sb * rb.y);
-    Bs[buf][lc + 1][lr] = make_float2(rb.z, sb * rb.w);
+    stash(buf);
     __syncthreads();
-    if (ks + 1 < ksteps) {
-      ra = fetch(A, p.m, p.lda, m0, (ks + 1) * BK);
-      rb = fetch(B, p.n, p.ldb, n0, (ks + 1) * BK);
-    }
+    if (ks + 1 < ksteps) fetch_tiles((ks + 1) * BK);
 #pragma unroll
     for (int k = 0; k < BK; ++k) {
-      float2 a[4], b[4];
-      const float4 a01 = *reinterpret_cast<const float4*>(&As[buf][k][ty * 4]);
-      const float4 a23 = *reinterpret_cast<const float4*>(&As[buf][k][ty * 4 + 2]);
-      const float4 b01 = *reinterpret_cast<const float4*>(&Bs[buf][k][tx * 4]);
-      const float4 b23 = *reinterpret_cast<const float4*>(&Bs[buf][k][tx * 4 + 2]);
-      a[0] = make_float2(a01.x, a01.y); a[1] = make_float2(a01.z, a01.w);
-      a[2] = make_float2(a23.x, a23.y); a[3] = make_float2(a23.z, a23.w);
-      b[0] = make_float2(b01.x, b01.y); b[1] = make_float2(b01.z, b01.w);
-      b[2] = make_float2(b23.x, b23.y); b[3] = make_float2(b23.z, b23.w);
+      float2 a[TM], b[TN];
+      if constexpr (TM == 1) {
+        a[0] = As[buf][k][ty];
+      } else {
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
+        for (int i = 0; i < TM; i += 2) {
+          const float4 v = *reinterpret_cast<const float4*>(&As[buf][k][ty * TM + i]);
+          a[i] = make_float2(v.x, v.y);
+          a[i + 1] = make_float2(v.z, v.w);
+        }
+      }
 #pragma unroll
-        for (int j = 0; j < 4; ++j) cmac(acc[i][j], a[i], b[j]);
+      for (int j = 0; j < TN; j += 2) {
+        const float4 v = *reinterpret_cast<const float4*>(&Bs[buf][k][tx * TN + j]);
+        b[j] = make_float2(v.x, v.y);
+        b[j + 1] = make_float2(v.z, v.w);
+      }
+#pragma unroll
+      for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) cmac(acc[i][j], a[i], b[j]);
     }
-    // the other buffer is rewritten next iteration; one barrier per step suffices
-    // because a thread can only get there after everyone left this compute loop
-    // of the previous use of that buffer (two steps ago) -- guaranteed by the
-    // barrier above of the step in between.
+    // One barrier per step is enough with two buffers: nobody can overwrite buffer
+    // `buf` (two steps from now) before passing the barrier of the step in between,
+    // which every thread reaches only after leaving this loop.
   }
 
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int m = m0 + ty * 4 + i;
+  for (int i = 0; i < TM; ++i) {
+    const int m = m0 + ty * TM + i;
     if (m >= p.m) continue;
-    const int n = n0 + tx * 4;
-    if (n >= p.ldc) continue;  // ldc is a multiple of 4: whole groups of four
-    float4* dst = reinterpret_cast<float4*>(C + (long long)m * p.ldc + n);
-    dst[0] = make_float4(p.alpha * acc[i][0].x, p.alpha * acc[i][0].y,
-                         p.alpha * acc[i][1].x, p.alpha * acc[i][1].y);
-    dst[1] = make_float4(p.alpha * acc[i][2].x, p.alpha * acc[i][2].y,
-                         p.alpha * acc[i][3].x, p.alpha * acc[i][3].y);
+#pragma unroll
+    for (int j = 0; j < TN; j += 2) {
+      const int n = n0 + tx * TN + j;
+      if (n >= p.ldc) continue;  // ldc is a multiple of 4: pairs never straddle it
+      *reinterpret_cast<float4*>(C + (long long)m * p.ldc + n) =
+          make_float4(p.alpha * acc[i][j].x, p.alpha * acc[i][j].y, p.alpha * acc[i][j + 1].x,
+                      p.alpha * acc[i][j + 1].y);
+    }
   }
 }
 
@@ -112,8 +153,13 @@ contract_simt_kernel(const __grid_constant__ ContractParams p) {
 
 cudaError_t launch_contract_simt(const ContractParams& p, cudaStream_t stream) {
   if (p.bins > 65535 || (p.lda & 3) || (p.ldb & 3) || (p.ldc & 3)) return cudaErrorInvalidValue;
-  dim3 grid((p.ldc + BN - 1) / BN, (p.m + BM - 1) / BM, p.bins);
-  contract_simt_kernel<<<grid, THREADS, 0, stream>>>(p);
+  if (p.ldc <= 4) {
+    dim3 grid(1, (p.m + 127) / 128, p.bins);
+    contract_simt_kernel<128, 4, 1, 2><<<grid, THREADS, 0, stream>>>(p);
+  } else {
+    dim3 grid((p.ldc + 63) / 64, (p.m + 63) / 64, p.bins);
+    contract_simt_kernel<64, 64, 4, 4><<<grid, THREADS, 0, stream>>>(p);
+  }
   count_launch();
   return cudaGetLastError();
 }

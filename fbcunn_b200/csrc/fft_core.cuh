@@ -12,7 +12,7 @@
 // Hermitian half kept, inverse un-normalised and cropped to the real tensor's
 // extent.  The layout of the half spectrum is private to this library:
 //
-//     spectrum[bin][row][inner]   complex fp32,  bin = kx * N + ky,  kx in [0, N/2]
+//     spectrum[bin][row][inner]   complex fp32,  bin = ky * (N/2+1) + kx,  kx in [0, N/2]
 //
 // i.e. bin-major with the plane index innermost, which is what the per-bin
 // contraction reads (the reference needed a separate transpose for that,
@@ -202,7 +202,10 @@ struct FftGeom {
 };
 
 static inline bool cooperative(int N) { return N > 32; }
-static inline int coop_threads() { return 256; }
+#ifndef FBF_COOP_THREADS
+#define FBF_COOP_THREADS 256
+#endif
+static inline int coop_threads() { return FBF_COOP_THREADS; }
 
 // Thread-per-line kernels (N <= 32): region A = row buffer [x][line1], region B = column
 // buffer [y][kx*T + t]; they alias (a thread takes its whole line into registers before
@@ -233,7 +236,7 @@ static inline FftGeom make_geom(int N, int T, int he, int we, bool inverse) {
     g.threads = round_up(need < 64 ? 64 : need, 32);
   } else {
     const int n1 = N == 64 ? 8 : 8, n2 = N / n1;
-    g.pitch1 = n1 * (n2 + 1);          // 72 or 136: both are 8 mod 16
+    g.pitch1 = (n1 * (n2 + 1)) | 1;    // odd: neighbouring lines fall on different banks
     g.pitch2 = g.lines2 | 1;
     g.chunk = N == 64 ? 64 : 32;
     if (g.chunk > g.lines1) g.chunk = g.lines1;
@@ -352,7 +355,7 @@ struct Forward {
     const int inner = inner0 + t;
     if (inner >= p.kc) return;
     const long long bin_stride = (long long)p.n_rows * p.kc;
-    float2* dst = p.spec + ((long long)kx * N) * bin_stride + (long long)row * p.kc + inner;
+    float2* dst = p.spec + (long long)kx * bin_stride + (long long)row * p.kc + inner;
     const int pitch = g.pitch2;
     const int he = g.he;
     float2 u[N];
@@ -360,7 +363,7 @@ struct Forward {
     for (int y = 0; y < N; ++y) u[y] = y < he ? mid[y * pitch] : make_float2(0.f, 0.f);
     fft_inreg<N, false>(u);
 #pragma unroll
-    for (int ky = 0; ky < N; ++ky) dst[ky * bin_stride] = u[ky];
+    for (int ky = 0; ky < N; ++ky) dst[(long long)(ky * (N / 2 + 1)) * bin_stride] = u[ky];
   }
 };
 
@@ -375,12 +378,13 @@ struct Inverse {
     const int inner = inner0 + t;
     const bool live = inner < p.n_inner;
     const long long bin_stride = (long long)p.n_rows * p.kc;
-    const float2* src = p.spec + ((long long)kx * N) * bin_stride + (long long)row * p.kc + inner;
+    const float2* src = p.spec + (long long)kx * bin_stride + (long long)row * p.kc + inner;
     const int pitch = g.pitch2;
     const int y0 = p.off_y, y1 = p.off_y + g.he;
     float2 u[N];
 #pragma unroll
-    for (int ky = 0; ky < N; ++ky) u[ky] = live ? src[ky * bin_stride] : make_float2(0.f, 0.f);
+    for (int ky = 0; ky < N; ++ky)
+      u[ky] = live ? src[(long long)(ky * (N / 2 + 1)) * bin_stride] : make_float2(0.f, 0.f);
     fft_inreg<N, true>(u);
 #pragma unroll
     for (int y = 0; y < N; ++y)
@@ -495,7 +499,7 @@ struct CoopForward {
     float2* mid = reinterpret_cast<float2*>(smem + g.off_b);
     constexpr int Q = N1 / 2 + 1;
     for (int item = tid; item < nl * Q; item += nthreads) {
-      const int ll = item / Q, q = item - ll * Q;
+      const int q = item / nl, ll = item - q * nl;  // lanes walk over lines: one q per warp
       const int line = line0 + ll;
       const int t = line / g.hh, j = line - t * g.hh;
       const bool has_b = (j + g.hh) < g.he;
@@ -576,9 +580,9 @@ struct CoopForward {
 #pragma unroll
       for (int n2 = 0; n2 < N2; ++n2) u[n2] = c[(N2 * k1 + n2) * g.pitch2];
       fft_inreg<N2, false>(u);
-      float2* dst = p.spec + ((long long)kx * N + k1) * bin_stride + (long long)row * p.kc + inner;
+      float2* dst = p.spec + ((long long)k1 * KX + kx) * bin_stride + (long long)row * p.kc + inner;
 #pragma unroll
-      for (int k2 = 0; k2 < N2; ++k2) dst[(long long)(N1 * k2) * bin_stride] = u[k2];
+      for (int k2 = 0; k2 < N2; ++k2) dst[(long long)(N1 * k2 * KX) * bin_stride] = u[k2];
     }
   }
 };
@@ -598,11 +602,11 @@ struct CoopInverse {
       const int n2 = item / cols, col = item - n2 * cols;
       const int t = col / KX, kx = col - t * KX;
       const bool live = inner0 + t < p.n_inner;
-      const float2* src = p.spec + ((long long)kx * N + n2) * bin_stride + (long long)row * p.kc + inner0 + t;
+      const float2* src = p.spec + ((long long)n2 * KX + kx) * bin_stride + (long long)row * p.kc + inner0 + t;
       float2 v[N1];
 #pragma unroll
       for (int n1 = 0; n1 < N1; ++n1)
-        v[n1] = live ? src[(long long)(N2 * n1) * bin_stride] : make_float2(0.f, 0.f);
+        v[n1] = live ? src[(long long)(N2 * n1 * KX) * bin_stride] : make_float2(0.f, 0.f);
       fft_inreg<N1, true>(v);
       float2* c = mid + col;
       c[(N1 * n2) * g.pitch2] = v[0];

@@ -58,7 +58,7 @@ fft2d_inverse_kernel(const __grid_constant__ FftParams p, const __grid_constant_
 }
 
 template <int N, int T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(FBF_COOP_THREADS, 2)
 fft2d_forward_coop_kernel(const __grid_constant__ FftParams p, const __grid_constant__ FftGeom g) {
   extern __shared__ __align__(16) char smem[];
   const int tid = threadIdx.x, nth = blockDim.x;
@@ -77,7 +77,7 @@ fft2d_forward_coop_kernel(const __grid_constant__ FftParams p, const __grid_cons
 }
 
 template <int N, int T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(FBF_COOP_THREADS, 2)
 fft2d_inverse_coop_kernel(const __grid_constant__ FftParams p, const __grid_constant__ FftGeom g) {
   extern __shared__ __align__(16) char smem[];
   const int tid = threadIdx.x, nth = blockDim.x;

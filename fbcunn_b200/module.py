@@ -251,7 +251,7 @@ class FFTWrapper:
     for 4-D real tensors (two batch dimensions, 2-D transform), the case the
     convolution uses (fbcunn/FFTWrapper.lua:53-132).  ``frequency`` is a complex64
     tensor shaped (bins, d1, d2_padded) -- or (bins, d2, d1_padded) when
-    ``transposed`` -- with bins = (N/2+1)*N ordered kx-major; `to_plane_major` turns it
+    ``transposed`` -- with bins = N*(N/2+1), bin = ky*(N/2+1) + kx; `to_plane_major` turns it
     into (d1, d2, N, N/2+1) [ky][kx]."""
 
     def __init__(self, implementation="fbfft", padLeft=0, padUp=0):
@@ -281,8 +281,8 @@ class FFTWrapper:
     @staticmethod
     def to_plane_major(frequency: torch.Tensor, inner: int, fft_size: int, transposed=False):
         n = fft_size
-        f = frequency[:, :, :inner].reshape(n // 2 + 1, n, frequency.shape[1], inner)  # kx, ky, row, inner
-        f = f.permute(2, 3, 1, 0)  # row, inner, ky, kx
+        f = frequency[:, :, :inner].reshape(n, n // 2 + 1, frequency.shape[1], inner)  # ky, kx, row, inner
+        f = f.permute(2, 3, 0, 1)  # row, inner, ky, kx
         return f.transpose(0, 1).contiguous() if transposed else f.contiguous()
 
     @staticmethod
@@ -291,5 +291,5 @@ class FFTWrapper:
         d1, d2, n, half = spec.shape
         assert n == fft_size and half == n // 2 + 1
         out = torch.zeros((half * n, d1, (d2 + 3) // 4 * 4), dtype=torch.complex64, device=spec.device)
-        out[:, :, :d2] = spec.permute(3, 2, 0, 1).reshape(half * n, d1, d2)
+        out[:, :, :d2] = spec.permute(2, 3, 0, 1).reshape(half * n, d1, d2)
         return out

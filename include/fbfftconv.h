@@ -123,7 +123,7 @@ int fbfftconv_acc_grad_parameters_host(fbfftconv_handle* h, const float* input,
 /* ---- the sub-steps, for callers and tests that drive them one by one --------- */
 
 /* Frequency buffers are complex fp32 laid out [bin][row][inner_padded] with
- * bin = kx*N + ky, kx in [0, N/2], ky in [0, N): bin-major, plane index innermost,
+ * bin = ky*(N/2+1) + kx, kx in [0, N/2], ky in [0, N): bin-major, plane index innermost,
  * inner_padded = inner rounded up to a multiple of 4 (padding is written as zero). */
 size_t fbfftconv_spectrum_bytes(int fft_size, int rows, int inner);
 

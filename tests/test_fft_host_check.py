@@ -26,9 +26,9 @@ def hc():
 
 
 def _bin_major(spec_plane_major):
-    """(d1, d2, ky, kx) -> (kx*N+ky, d1, d2)."""
+    """(d1, d2, ky, kx) -> (ky*(N/2+1)+kx, d1, d2)."""
     d1, d2, n, half = spec_plane_major.shape
-    return spec_plane_major.transpose(3, 2, 0, 1).reshape(half * n, d1, d2)
+    return spec_plane_major.transpose(2, 3, 0, 1).reshape(half * n, d1, d2)
 
 
 CASES = [(N, T) for N in (8, 16, 32, 64, 128) for T in (1, 2, 4, 8, 16)

@@ -135,7 +135,8 @@ def test_ifft2d_crop_bias_and_round_trip(N):
 @pytest.mark.parametrize("conj_a,conj_b", [(0, 1), (0, 0), (1, 0)])
 def test_transpose_mm(use_simt, conj_a, conj_b):
     rng = np.random.default_rng(3)
-    for (bins, m, n, k) in [(5, 7, 9, 3), (3, 64, 64, 8), (2, 130, 70, 21), (1, 1, 1, 1), (4, 16, 128, 128)]:
+    for (bins, m, n, k) in [(5, 7, 9, 3), (3, 64, 64, 8), (2, 130, 70, 21), (1, 1, 1, 1), (4, 16, 128, 128),
+                            (3, 130, 3, 96), (2, 96, 4, 128)]:
         kp, npad = (k + 3) // 4 * 4, (n + 3) // 4 * 4
         a = np.zeros((bins, m, kp), np.complex64)
         b = np.zeros((bins, n, kp), np.complex64)
