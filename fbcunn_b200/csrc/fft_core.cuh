@@ -236,8 +236,8 @@ static inline FftGeom make_geom(int N, int T, int he, int we, bool inverse) {
     g.threads = round_up(need < 64 ? 64 : need, 32);
   } else {
     const int n1 = N == 64 ? 8 : 8, n2 = N / n1;
-    g.pitch1 = (n1 * (n2 + 1)) | 1;    // odd: neighbouring lines fall on different banks
-    g.pitch2 = g.lines2 | 1;
+    g.pitch1 = (n1 * (n2 + 1)) | 1;    // = CoopLayout::PITCH1 (odd: neighbouring lines, different banks)
+    g.pitch2 = g.lines2 | 1;           // = CoopLayout::PITCH2
     g.chunk = N == 64 ? 64 : 32;
     if (g.chunk > g.lines1) g.chunk = g.lines1;
     const int bytes_a = g.chunk * g.pitch1 * 8;
@@ -453,92 +453,139 @@ struct Inverse {
 
 // ===========================================================================
 // Cooperative kernels, N = 64 / 128.  Work is split into items that the threads of
-// the block pick up round-robin; barriers separate the phases.
+// the block pick up round-robin; barriers separate the phases.  Shared-memory
+// pitches are compile-time constants so that every access has an immediate offset.
 // ===========================================================================
 template <int N, int T>
-struct CoopForward {
+struct CoopLayout {
   static constexpr int N1 = Split<N>::N1, N2 = Split<N>::N2, KX = N / 2 + 1;
+  static constexpr int COLS = T * KX;                 // columns of mid: (t, kx)
+  static constexpr int PITCH1 = (N1 * (N2 + 1)) | 1;  // row buffer line pitch (float2), odd
+  static constexpr int PITCH2 = COLS | 1;             // mid row pitch (float2), odd
+  static_assert(N1 == 8, "the residue pairing below is written for eight residues");
+};
+
+// Order of the residues k1 inside a group of eight neighbouring lanes: residues that
+// hold each other's mirror image (k1, N1 - k1) sit in lanes that differ in bit 0;
+// residues 0 and N1/2 mirror onto themselves.
+FBF_HD int coop_residue_of_lane(int p) {
+  return p == 0 ? 0 : p == 1 ? 4 : p == 2 ? 1 : p == 3 ? 7 : p == 4 ? 2 : p == 5 ? 6 : p == 6 ? 3 : 5;
+}
+
+template <int N, int T>
+struct CoopForward {
+  using L = CoopLayout<N, T>;
+  static constexpr int N1 = L::N1, N2 = L::N2, KX = L::KX;
+
+  struct RowLoad {
+    float2 v[N1];
+    int slot;  // ll * PITCH1 + n2, or -1
+    int n2;
+  };
+
+  static FBF_HD void row_fetch(const FftParams& p, const FftGeom& g, const float* base, long long tstride,
+                               int inner0, int line0, int nl, int item, RowLoad& r) {
+    r.slot = -1;
+    if (item >= nl * N2) return;
+    const int ll = item / N2, n2 = item - ll * N2;
+    const int line = line0 + ll;
+    const int t = line / g.hh, j = line - t * g.hh;
+    const bool live = inner0 + t < p.n_inner;
+    const float* plane = base + t * tstride;
+    const int ya = j - p.off_y, yb = j + g.hh - p.off_y;
+    const bool va = live && ya >= 0 && ya < p.h, vb = live && yb >= 0 && yb < p.h;
+    const float* pa = plane + ya * p.w + (n2 - p.off_x);
+    const float* pb = plane + yb * p.w + (n2 - p.off_x);
+#pragma unroll
+    for (int n1 = 0; n1 < N1; ++n1) {
+      const int x = N2 * n1 + n2 - p.off_x;
+      const bool vx = x >= 0 && x < p.w;
+      r.v[n1] = make_float2(va && vx ? pa[N2 * n1] : 0.f, vb && vx ? pb[N2 * n1] : 0.f);
+    }
+    r.slot = ll * L::PITCH1 + n2;
+    r.n2 = n2;
+  }
+
+  static FBF_HD void row_transform(float2* rb, RowLoad& r) {
+    if (r.slot < 0) return;
+    fft_inreg<N1, false>(r.v);
+    float2* dst = rb + r.slot;
+    dst[0] = r.v[0];
+#pragma unroll
+    for (int k1 = 1; k1 < N1; ++k1)
+      dst[k1 * (N2 + 1)] = cmul(r.v[k1], tw128_runtime<false>(r.n2 * k1 * (128 / N)));
+  }
 
   // Row step 1 for lines [line0, line0 + nl): straight from global memory (N2
-  // neighbouring floats per row and lane group: whole 32-byte sectors), N1-point
-  // transform, twiddle, into the row buffer.
+  // neighbouring floats per row and lane group: whole 32-byte sectors), two items in
+  // flight per thread, N1-point transform, twiddle, into the row buffer.
   static FBF_HD void row_step1(const FftParams& p, const FftGeom& g, char* smem, int tid, int nthreads,
                                int row, int inner0, int line0, int nl) {
     float2* rb = reinterpret_cast<float2*>(smem + g.off_a);
     const long long plane_elems = (long long)p.h * p.w;
     const float* base = p.real_in + (row * p.real_row_stride + inner0 * p.real_inner_stride) * plane_elems;
     const long long tstride = p.real_inner_stride * plane_elems;
-    for (int item = tid; item < nl * N2; item += nthreads) {
-      const int ll = item / N2, n2 = item - ll * N2;
-      const int line = line0 + ll;
-      const int t = line / g.hh, j = line - t * g.hh;
-      const bool live = inner0 + t < p.n_inner;
-      const float* plane = base + t * tstride;
-      const int ya = j - p.off_y, yb = j + g.hh - p.off_y;
-      const bool va = live && ya >= 0 && ya < p.h, vb = live && yb >= 0 && yb < p.h;
-      float2 v[N1];
-#pragma unroll
-      for (int n1 = 0; n1 < N1; ++n1) {
-        const int x = N2 * n1 + n2 - p.off_x;
-        const bool vx = x >= 0 && x < p.w;
-        v[n1] = make_float2(va && vx ? plane[ya * p.w + x] : 0.f, vb && vx ? plane[yb * p.w + x] : 0.f);
-      }
-      fft_inreg<N1, false>(v);
-      float2* dst = rb + ll * g.pitch1 + n2;
-      dst[0] = v[0];
-#pragma unroll
-      for (int k1 = 1; k1 < N1; ++k1)
-        dst[k1 * (N2 + 1)] = cmul(v[k1], tw128_runtime<false>(n2 * k1 * (128 / N)));
+    for (int item = tid; item < nl * N2; item += 2 * nthreads) {
+      RowLoad r0, r1;
+      row_fetch(p, g, base, tstride, inner0, line0, nl, item, r0);
+      row_fetch(p, g, base, tstride, inner0, line0, nl, item + nthreads, r1);
+      row_transform(rb, r0);
+      row_transform(rb, r1);
     }
   }
 
-  // Row step 2: N2-point transforms of residues k1 and N1-k1 together, so that Z[k] and
-  // Z[N-k] meet in one thread; the row pair is split there and written to mid.
-  static FBF_HD void row_step2(const FftGeom& g, char* smem, int tid, int nthreads, int line0, int nl) {
+  // Row step 2, first half: item = (line, lane position); the N2-point transform of
+  // residue k1 of that line.
+  static FBF_HD bool row_step2_fft(const FftGeom& g, const char* smem, int item, int nl, float2 (&u)[N2]) {
+    if (item >= nl * N1) return false;
     const float2* rb = reinterpret_cast<const float2*>(smem + g.off_a);
+    const int ll = item / N1, k1 = coop_residue_of_lane(item % N1);
+    const float2* src = rb + ll * L::PITCH1 + k1 * (N2 + 1);
+#pragma unroll
+    for (int n2 = 0; n2 < N2; ++n2) u[n2] = src[n2];
+    fft_inreg<N2, false>(u);
+    return true;
+  }
+
+  // Row step 2, second half: Z[k] (own) meets Z[N-k] (own for residues 0 and N1/2, else
+  // the odd-indexed outputs of the mirror residue, handed over by the neighbouring
+  // lane); the row pair is split and written to mid.  Each lane of a mirror pair takes
+  // the even-indexed half of its own outputs, which covers every frequency once.
+  static FBF_HD void row_step2_split(const FftGeom& g, char* smem, int item, int line0,
+                                     const float2 (&u)[N2], const float2 (&mirror_odd)[N2 / 2]) {
     float2* mid = reinterpret_cast<float2*>(smem + g.off_b);
-    constexpr int Q = N1 / 2 + 1;
-    for (int item = tid; item < nl * Q; item += nthreads) {
-      const int q = item / nl, ll = item - q * nl;  // lanes walk over lines: one q per warp
-      const int line = line0 + ll;
-      const int t = line / g.hh, j = line - t * g.hh;
-      const bool has_b = (j + g.hh) < g.he;
-      const bool self = (q == 0) || (q == N1 / 2);
-      const float2* src = rb + ll * g.pitch1;
-      float2 u[N2], ub[N2];
+    const int ll = item / N1, k1 = coop_residue_of_lane(item % N1);
+    const int line = line0 + ll;
+    const int t = line / g.hh, j = line - t * g.hh;
+    const bool has_b = (j + g.hh) < g.he;
+    float2* ma = mid + j * L::PITCH2 + t * KX;
+    float2* mb = mid + (j + g.hh) * L::PITCH2 + t * KX;
+    if (k1 == 0 || k1 == N1 / 2) {
 #pragma unroll
-      for (int n2 = 0; n2 < N2; ++n2) u[n2] = src[q * (N2 + 1) + n2];
-      fft_inreg<N2, false>(u);
-      if (!self) {
-#pragma unroll
-        for (int n2 = 0; n2 < N2; ++n2) ub[n2] = src[(N1 - q) * (N2 + 1) + n2];
-        fft_inreg<N2, false>(ub);
-      }
-      float2* ma = mid + j * g.pitch2 + t * KX;
-      float2* mb = mid + (j + g.hh) * g.pitch2 + t * KX;
-#pragma unroll
-      for (int k2 = 0; k2 < N2; ++k2) {
-        const int k = q + N1 * k2;
-        float2 zk, znk;
-        int kk;
-        if (self) {
-          if (k > N / 2) continue;
-          zk = u[k2];
-          znk = (q == 0) ? u[(N2 - k2) % N2] : u[N2 - 1 - k2];
-          kk = k;
-        } else if (k <= N / 2) {
-          zk = u[k2];
-          znk = ub[N2 - 1 - k2];
-          kk = k;
-        } else {
-          zk = ub[N2 - 1 - k2];
-          znk = u[k2];
-          kk = N - k;
-        }
+      for (int k2 = 0; k2 <= N2 / 2; ++k2) {
+        const int k = k1 + N1 * k2;
+        if (k > N / 2) continue;
+        const float2 znk = (k1 == 0) ? u[(N2 - k2) % N2] : u[N2 - 1 - k2];
         float2 a, b;
-        untangle_pair(zk, znk, a, b);
-        ma[kk] = a;
-        if (has_b) mb[kk] = b;
+        untangle_pair(u[k2], znk, a, b);
+        ma[k] = a;
+        if (has_b) mb[k] = b;
+      }
+    } else {
+#pragma unroll
+      for (int k2 = 0; k2 < N2; k2 += 2) {
+        const int k = k1 + N1 * k2;
+        const float2 other = mirror_odd[(N2 - 1 - k2) / 2];  // Z[N-k] = mirror[N2-1-k2]
+        float2 a, b;
+        if (k <= N / 2) {
+          untangle_pair(u[k2], other, a, b);
+          ma[k] = a;
+          if (has_b) mb[k] = b;
+        } else {
+          untangle_pair(other, u[k2], a, b);
+          ma[N - k] = a;
+          if (has_b) mb[N - k] = b;
+        }
       }
     }
   }
@@ -546,21 +593,18 @@ struct CoopForward {
   // Column step 1, in place on mid: item (col, n2) owns rows {N2*n1 + n2}.
   static FBF_HD void col_step1(const FftGeom& g, char* smem, int tid, int nthreads) {
     float2* mid = reinterpret_cast<float2*>(smem + g.off_b);
-    const int cols = g.lines2;
-    for (int item = tid; item < cols * N2; item += nthreads) {
-      const int n2 = item / cols, col = item - n2 * cols;
-      float2* c = mid + col;
+    for (int item = tid; item < L::COLS * N2; item += nthreads) {
+      const int n2 = item / L::COLS, col = item - n2 * L::COLS;
+      float2* c = mid + col + n2 * L::PITCH2;
       float2 v[N1];
 #pragma unroll
-      for (int n1 = 0; n1 < N1; ++n1) {
-        const int y = N2 * n1 + n2;
-        v[n1] = y < g.he ? c[y * g.pitch2] : make_float2(0.f, 0.f);
-      }
+      for (int n1 = 0; n1 < N1; ++n1)
+        v[n1] = (N2 * n1 + n2) < g.he ? c[N2 * n1 * L::PITCH2] : make_float2(0.f, 0.f);
       fft_inreg<N1, false>(v);
-      c[n2 * g.pitch2] = v[0];
+      c[0] = v[0];
 #pragma unroll
       for (int k1 = 1; k1 < N1; ++k1)
-        c[(N2 * k1 + n2) * g.pitch2] = cmul(v[k1], tw128_runtime<false>(n2 * k1 * (128 / N)));
+        c[N2 * k1 * L::PITCH2] = cmul(v[k1], tw128_runtime<false>(n2 * k1 * (128 / N)));
     }
   }
 
@@ -568,51 +612,75 @@ struct CoopForward {
   static FBF_HD void col_step2(const FftParams& p, const FftGeom& g, const char* smem, int tid,
                                int nthreads, int row, int inner0) {
     const float2* mid = reinterpret_cast<const float2*>(smem + g.off_b);
-    const int cols = g.lines2;
     const long long bin_stride = (long long)p.n_rows * p.kc;
-    for (int item = tid; item < cols * N1; item += nthreads) {
-      const int k1 = item / cols, col = item - k1 * cols;
+    for (int item = tid; item < L::COLS * N1; item += nthreads) {
+      const int k1 = item / L::COLS, col = item - k1 * L::COLS;
       const int t = col / KX, kx = col - t * KX;
       const int inner = inner0 + t;
       if (inner >= p.kc) continue;
-      const float2* c = mid + col;
+      const float2* c = mid + col + N2 * k1 * L::PITCH2;
       float2 u[N2];
 #pragma unroll
-      for (int n2 = 0; n2 < N2; ++n2) u[n2] = c[(N2 * k1 + n2) * g.pitch2];
+      for (int n2 = 0; n2 < N2; ++n2) u[n2] = c[n2 * L::PITCH2];
       fft_inreg<N2, false>(u);
       float2* dst = p.spec + ((long long)k1 * KX + kx) * bin_stride + (long long)row * p.kc + inner;
+      const long long step = (long long)(N1 * KX) * bin_stride;
 #pragma unroll
-      for (int k2 = 0; k2 < N2; ++k2) dst[(long long)(N1 * k2 * KX) * bin_stride] = u[k2];
+      for (int k2 = 0; k2 < N2; ++k2) dst[k2 * step] = u[k2];
     }
   }
 };
 
 template <int N, int T>
 struct CoopInverse {
-  static constexpr int N1 = Split<N>::N1, N2 = Split<N>::N2, KX = N / 2 + 1;
+  using L = CoopLayout<N, T>;
+  static constexpr int N1 = L::N1, N2 = L::N2, KX = L::KX;
 
-  // Column step 1: bins of column (t, kx) from global memory, N1-point inverse transform,
-  // twiddle, written to rows k1 + N1*n2 of mid so that step 2 can run in place.
+  struct ColLoad {
+    float2 v[N1];
+    int col;  // -1 when idle
+    int n2;
+  };
+
+  static FBF_HD void col_fetch(const FftParams& p, long long bin_stride, const float2* base, int inner0,
+                               int item, ColLoad& r) {
+    r.col = -1;
+    if (item >= L::COLS * N2) return;
+    const int n2 = item / L::COLS, col = item - n2 * L::COLS;
+    const int t = col / KX, kx = col - t * KX;
+    const bool live = inner0 + t < p.n_inner;
+    const float2* src = base + ((long long)n2 * KX + kx) * bin_stride + t;
+    const long long step = (long long)(N2 * KX) * bin_stride;
+#pragma unroll
+    for (int n1 = 0; n1 < N1; ++n1) r.v[n1] = live ? src[n1 * step] : make_float2(0.f, 0.f);
+    r.col = col;
+    r.n2 = n2;
+  }
+
+  static FBF_HD void col_transform(float2* mid, ColLoad& r) {
+    if (r.col < 0) return;
+    fft_inreg<N1, true>(r.v);
+    float2* c = mid + r.col + N1 * r.n2 * L::PITCH2;
+    c[0] = r.v[0];
+#pragma unroll
+    for (int k1 = 1; k1 < N1; ++k1)
+      c[k1 * L::PITCH2] = cmul(r.v[k1], tw128_runtime<true>(r.n2 * k1 * (128 / N)));
+  }
+
+  // Column step 1: bins of column (t, kx) from global memory (two items in flight per
+  // thread), N1-point inverse transform, twiddle, written to rows k1 + N1*n2 of mid so
+  // that step 2 can run in place.
   static FBF_HD void col_step1(const FftParams& p, const FftGeom& g, char* smem, int tid, int nthreads,
                                int row, int inner0) {
     float2* mid = reinterpret_cast<float2*>(smem + g.off_b);
-    const int cols = g.lines2;
     const long long bin_stride = (long long)p.n_rows * p.kc;
-    for (int item = tid; item < cols * N2; item += nthreads) {
-      const int n2 = item / cols, col = item - n2 * cols;
-      const int t = col / KX, kx = col - t * KX;
-      const bool live = inner0 + t < p.n_inner;
-      const float2* src = p.spec + ((long long)n2 * KX + kx) * bin_stride + (long long)row * p.kc + inner0 + t;
-      float2 v[N1];
-#pragma unroll
-      for (int n1 = 0; n1 < N1; ++n1)
-        v[n1] = live ? src[(long long)(N2 * n1 * KX) * bin_stride] : make_float2(0.f, 0.f);
-      fft_inreg<N1, true>(v);
-      float2* c = mid + col;
-      c[(N1 * n2) * g.pitch2] = v[0];
-#pragma unroll
-      for (int k1 = 1; k1 < N1; ++k1)
-        c[(k1 + N1 * n2) * g.pitch2] = cmul(v[k1], tw128_runtime<true>(n2 * k1 * (128 / N)));
+    const float2* base = p.spec + (long long)row * p.kc + inner0;
+    for (int item = tid; item < L::COLS * N2; item += 2 * nthreads) {
+      ColLoad r0, r1;
+      col_fetch(p, bin_stride, base, inner0, item, r0);
+      col_fetch(p, bin_stride, base, inner0, item + nthreads, r1);
+      col_transform(mid, r0);
+      col_transform(mid, r1);
     }
   }
 
@@ -620,16 +688,15 @@ struct CoopInverse {
   // mid holds the half spectrum along x of real row y.
   static FBF_HD void col_step2(const FftGeom& g, char* smem, int tid, int nthreads) {
     float2* mid = reinterpret_cast<float2*>(smem + g.off_b);
-    const int cols = g.lines2;
-    for (int item = tid; item < cols * N1; item += nthreads) {
-      const int k1 = item / cols, col = item - k1 * cols;
-      float2* c = mid + col;
+    for (int item = tid; item < L::COLS * N1; item += nthreads) {
+      const int k1 = item / L::COLS, col = item - k1 * L::COLS;
+      float2* c = mid + col + k1 * L::PITCH2;
       float2 u[N2];
 #pragma unroll
-      for (int n2 = 0; n2 < N2; ++n2) u[n2] = c[(k1 + N1 * n2) * g.pitch2];
+      for (int n2 = 0; n2 < N2; ++n2) u[n2] = c[N1 * n2 * L::PITCH2];
       fft_inreg<N2, true>(u);
 #pragma unroll
-      for (int k2 = 0; k2 < N2; ++k2) c[(k1 + N1 * k2) * g.pitch2] = u[k2];
+      for (int k2 = 0; k2 < N2; ++k2) c[N1 * k2 * L::PITCH2] = u[k2];
     }
   }
 
@@ -644,8 +711,8 @@ struct CoopInverse {
       const int line = line0 + ll;
       const int t = line / g.hh, j = line - t * g.hh;
       const bool has_b = (j + g.hh) < g.he;
-      const float2* pa = mid + (p.off_y + j) * g.pitch2 + t * KX;
-      const float2* pb = mid + (p.off_y + j + g.hh) * g.pitch2 + t * KX;
+      const float2* pa = mid + (p.off_y + j) * L::PITCH2 + t * KX;
+      const float2* pb = pa + g.hh * L::PITCH2;
       float2 v[N1];
 #pragma unroll
       for (int n1 = 0; n1 < N1; ++n1) {
@@ -656,7 +723,7 @@ struct CoopInverse {
         v[n1] = k <= N / 2 ? tangle_low(a, b) : tangle_high(a, b);
       }
       fft_inreg<N1, true>(v);
-      float2* dst = rb + ll * g.pitch1 + n2;
+      float2* dst = rb + ll * L::PITCH1 + n2;
       dst[0] = v[0];
 #pragma unroll
       for (int k1 = 1; k1 < N1; ++k1)
@@ -680,21 +747,21 @@ struct CoopInverse {
       const int inner = inner0 + t;
       if (inner >= p.n_inner) continue;
       const bool has_b = (j + g.hh) < g.he;
-      const float2* src = rb + ll * g.pitch1 + k1 * (N2 + 1);
+      const float2* src = rb + ll * L::PITCH1 + k1 * (N2 + 1);
       float2 u[N2];
 #pragma unroll
       for (int n2 = 0; n2 < N2; ++n2) u[n2] = src[n2];
       fft_inreg<N2, true>(u);
       const float bias = p.bias ? p.bias[inner] : 0.f;
-      float* da = base + t * tstride + (long long)j * g.we;
+      float* da = base + t * tstride + (long long)j * g.we + (k1 - p.off_x);
       float* db = da + (long long)g.hh * g.we;
 #pragma unroll
       for (int k2 = 0; k2 < N2; ++k2) {
         const int x = k1 + N1 * k2 - p.off_x;
         if (x < 0 || x >= g.we) continue;
         const float va = u[k2].x + bias, vb = u[k2].y + bias;
-        da[x] = p.accumulate ? da[x] + va : va;
-        if (has_b) db[x] = p.accumulate ? db[x] + vb : vb;
+        da[N1 * k2] = p.accumulate ? da[N1 * k2] + va : va;
+        if (has_b) db[N1 * k2] = p.accumulate ? db[N1 * k2] + vb : vb;
       }
     }
   }

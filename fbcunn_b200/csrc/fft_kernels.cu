@@ -68,7 +68,20 @@ fft2d_forward_coop_kernel(const __grid_constant__ FftParams p, const __grid_cons
     const int nl = min(g.chunk, g.lines1 - line0);
     CoopForward<N, T>::row_step1(p, g, smem, tid, nth, row, inner0, line0, nl);
     __syncthreads();
-    CoopForward<N, T>::row_step2(g, smem, tid, nth, line0, nl);
+    // groups of eight lanes hold the eight residues of one line; mirror residues are
+    // neighbours, so one shuffle hands each lane the partner's odd-indexed outputs
+    constexpr int N1 = CoopForward<N, T>::N1, N2 = CoopForward<N, T>::N2;
+    const int items = nl * N1;
+    for (int base = 0; base < items; base += nth) {
+      float2 u[N2], mirror_odd[N2 / 2];
+      const bool active = CoopForward<N, T>::row_step2_fft(g, smem, base + tid, nl, u);
+#pragma unroll
+      for (int i = 0; i < N2 / 2; ++i) {
+        mirror_odd[i].x = __shfl_xor_sync(0xffffffffu, u[2 * i + 1].x, 1);
+        mirror_odd[i].y = __shfl_xor_sync(0xffffffffu, u[2 * i + 1].y, 1);
+      }
+      if (active) CoopForward<N, T>::row_step2_split(g, smem, base + tid, line0, u, mirror_odd);
+    }
     __syncthreads();
   }
   CoopForward<N, T>::col_step1(g, smem, tid, nth);

@@ -31,8 +31,26 @@ void run_forward(const FftParams& p) {
           std::memset(smem.data() + g.off_a, 0xFF, g.off_b - g.off_a);
           for (int tid = 0; tid < nth; ++tid)
             CoopForward<N, T>::row_step1(p, g, smem.data(), tid, nth, row, inner0, line0, nl);
-          for (int tid = 0; tid < nth; ++tid)
-            CoopForward<N, T>::row_step2(g, smem.data(), tid, nth, line0, nl);
+          {  // the device exchanges the transforms of mirror residues by a lane shuffle
+            constexpr int N1 = CoopForward<N, T>::N1, N2 = CoopForward<N, T>::N2;
+            const int items = nl * N1;
+            std::vector<float2> all(static_cast<size_t>(items) * N2);
+            for (int item = 0; item < items; ++item) {
+              float2 u[N2];
+              CoopForward<N, T>::row_step2_fft(g, smem.data(), item, nl, u);
+              std::copy(u, u + N2, all.begin() + static_cast<size_t>(item) * N2);
+            }
+            for (int item = 0; item < items; ++item) {
+              float2 u[N2], mirror_odd[N2 / 2];
+              std::copy(all.begin() + static_cast<size_t>(item) * N2,
+                        all.begin() + static_cast<size_t>(item + 1) * N2, u);
+              const int partner = item ^ 1;
+              for (int i = 0; i < N2 / 2; ++i)
+                mirror_odd[i] = partner < items ? all[static_cast<size_t>(partner) * N2 + 2 * i + 1]
+                                                : make_float2(NAN, NAN);
+              CoopForward<N, T>::row_step2_split(g, smem.data(), item, line0, u, mirror_odd);
+            }
+          }
         }
         for (int tid = 0; tid < nth; ++tid) CoopForward<N, T>::col_step1(g, smem.data(), tid, nth);
         for (int tid = 0; tid < nth; ++tid)
