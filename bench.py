@@ -336,11 +336,8 @@ def run_gpu_arm(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
         from fbcunn_b200 import SpatialConvolutionFBFFT
-        uid = torch.zeros(128, dtype=torch.uint8, device="cuda")
-        if rank == 0:
-            uid.copy_(torch.frombuffer(bytearray(SpatialConvolutionFBFFT.makeUniqueId()), dtype=torch.uint8))
-        dist.broadcast(uid, 0)
-        comm = (bytes(uid.cpu().numpy().tobytes()), rank, world)
+        from fbcunn_b200.sharding import share_unique_id
+        comm = (share_unique_id(dist, SpatialConvolutionFBFFT.makeUniqueId), rank, world)
 
     def barrier():
         torch.cuda.synchronize()
