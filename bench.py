@@ -211,7 +211,7 @@ class ClockSampler:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "50",
                  "-i", str(self.index)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
@@ -357,6 +357,9 @@ def run_gpu_arm(args):
     assert L[0] % world == 0, "global batch must divide over the ranks"
     local_b = L[0] // world
     run = LayerRun(torch, name, L, local_b, rank, comm)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()  # before the warm-up so that short timed regions still get samples
     for _ in range(max(args.warmup, 3)):
         run.step()
     barrier()
@@ -365,9 +368,6 @@ def run_gpu_arm(args):
     lib = capi.lib()
     capi.check(lib.fbfftconv_profile_enable(run.handle(), 1))
     capi.check(lib.fbfftconv_profile_reset(run.handle()))
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
     launches0 = capi.kernel_launches()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()

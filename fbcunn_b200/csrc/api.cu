@@ -10,6 +10,8 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <map>
+#include <mutex>
 #include <string>
 #include <vector>
 
@@ -88,6 +90,15 @@ NcclApi* nccl_api() {
   return &api;
 }
 
+// One NCCL communicator per unique id and process, shared by every handle that names
+// that id (a model has many layers but needs one communicator).
+struct SharedComm {
+  ncclComm_t comm = nullptr;
+  int refs = 0;
+};
+std::mutex g_comm_mutex;
+std::map<std::string, SharedComm> g_comms;
+
 int nccl_fail(NcclApi* api, ncclResult_t r, const char* what) {
   return fail(FBFFTCONV_ERR_COMM, "%s: %s", what,
               api && api->GetErrorString ? api->GetErrorString(r) : "nccl error");
@@ -117,6 +128,7 @@ struct fbfftconv_handle {
   size_t stage_bytes = 0;
   // communicator
   ncclComm_t comm = nullptr;
+  std::string comm_key;
   int rank = 0, nranks = 1;
 
   float2* buf_in() const { return reinterpret_cast<float2*>(ws); }
@@ -247,6 +259,20 @@ int contract(const float2* a, const float2* b, float2* c, int bins, int m, int n
 
 bool valid_fft_size(int n) { return n == 8 || n == 16 || n == 32 || n == 64 || n == 128; }
 
+void release_comm(fbfftconv_handle* h) {
+  if (!h->comm) return;
+  std::lock_guard<std::mutex> lock(g_comm_mutex);
+  auto it = g_comms.find(h->comm_key);
+  if (it != g_comms.end() && --it->second.refs == 0) {
+    if (NcclApi* api = nccl_api()) api->CommDestroy(it->second.comm);
+    g_comms.erase(it);
+  }
+  h->comm = nullptr;
+  h->comm_key.clear();
+  h->rank = 0;
+  h->nranks = 1;
+}
+
 }  // namespace
 
 namespace fbfft {
@@ -331,9 +357,7 @@ int fbfftconv_destroy(fbfftconv_handle* h) {
   if (!h) return FBFFTCONV_OK;
   DeviceGuard g;
   g.enter(h->device);
-  if (h->comm) {
-    if (NcclApi* api = nccl_api()) api->CommDestroy(h->comm);
-  }
+  release_comm(h);
   if (h->ws && h->ws_owned) cudaFree(h->ws);
   if (h->stage) cudaFree(h->stage);
   for (auto& per_pass : h->events)
@@ -726,17 +750,22 @@ int fbfftconv_comm_init(fbfftconv_handle* h, const void* id128, int rank, int nr
   if (!api) return fail(FBFFTCONV_ERR_COMM, "libnccl is not loadable: %s", dlerror());
   DeviceGuard g;
   FBF_CUDA(g.enter(h->device));
-  if (h->comm) {
-    api->CommDestroy(h->comm);
-    h->comm = nullptr;
+  release_comm(h);
+  const std::string key(static_cast<const char*>(id128), sizeof(ncclUniqueId));
+  std::lock_guard<std::mutex> lock(g_comm_mutex);
+  SharedComm& shared = g_comms[key];
+  if (!shared.comm) {
+    ncclUniqueId id;
+    memcpy(&id, id128, sizeof(id));
+    ncclResult_t r = api->CommInitRank(&shared.comm, nranks, id, rank);
+    if (r != ncclSuccess) {
+      g_comms.erase(key);
+      return nccl_fail(api, r, "ncclCommInitRank");
+    }
   }
-  ncclUniqueId id;
-  memcpy(&id, id128, sizeof(id));
-  ncclResult_t r = api->CommInitRank(&h->comm, nranks, id, rank);
-  if (r != ncclSuccess) {
-    h->comm = nullptr;
-    return nccl_fail(api, r, "ncclCommInitRank");
-  }
+  ++shared.refs;
+  h->comm = shared.comm;
+  h->comm_key = key;
   h->rank = rank;
   h->nranks = nranks;
   return FBFFTCONV_OK;
@@ -744,15 +773,9 @@ int fbfftconv_comm_init(fbfftconv_handle* h, const void* id128, int rank, int nr
 
 int fbfftconv_comm_destroy(fbfftconv_handle* h) {
   if (!h || !h->comm) return FBFFTCONV_OK;
-  NcclApi* api = nccl_api();
-  if (api) {
-    DeviceGuard g;
-    g.enter(h->device);
-    api->CommDestroy(h->comm);
-  }
-  h->comm = nullptr;
-  h->nranks = 1;
-  h->rank = 0;
+  DeviceGuard g;
+  g.enter(h->device);
+  release_comm(h);
   return FBFFTCONV_OK;
 }
 
