@@ -455,6 +455,9 @@ def run_gpu_arm(args):
         }
         print(json.dumps(line), flush=True)
     if world > 1:
+        import gc
+        gc.collect()  # handles detach from the communicator before it is shut down
+        lib.fbfftconv_comm_shutdown()
         dist.destroy_process_group()
     return 0
 

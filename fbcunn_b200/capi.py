@@ -69,6 +69,7 @@ _SIGNATURES = {
     "fbfftconv_comm_unique_id": (c_int, [c_void_p]),
     "fbfftconv_comm_init": (c_int, [c_void_p, c_void_p, c_int, c_int]),
     "fbfftconv_comm_destroy": (c_int, [c_void_p]),
+    "fbfftconv_comm_shutdown": (c_int, []),
     "fbfftconv_last_error": (c_char_p, []),
     "fbfftconv_status_string": (c_char_p, [c_int]),
     "fbfftconv_kernel_launches": (c_uint64, []),

@@ -263,10 +263,7 @@ void release_comm(fbfftconv_handle* h) {
   if (!h->comm) return;
   std::lock_guard<std::mutex> lock(g_comm_mutex);
   auto it = g_comms.find(h->comm_key);
-  if (it != g_comms.end() && --it->second.refs == 0) {
-    if (NcclApi* api = nccl_api()) api->CommDestroy(it->second.comm);
-    g_comms.erase(it);
-  }
+  if (it != g_comms.end()) --it->second.refs;  // the communicator itself stays: an id cannot be used twice
   h->comm = nullptr;
   h->comm_key.clear();
   h->rank = 0;
@@ -769,6 +766,21 @@ int fbfftconv_comm_init(fbfftconv_handle* h, const void* id128, int rank, int nr
   h->rank = rank;
   h->nranks = nranks;
   return FBFFTCONV_OK;
+}
+
+int fbfftconv_comm_shutdown(void) {
+  std::lock_guard<std::mutex> lock(g_comm_mutex);
+  NcclApi* api = nccl_api();
+  for (auto it = g_comms.begin(); it != g_comms.end();) {
+    if (it->second.refs > 0) {
+      ++it;
+      continue;
+    }
+    if (api) api->CommDestroy(it->second.comm);
+    it = g_comms.erase(it);
+  }
+  return g_comms.empty() ? FBFFTCONV_OK
+                         : fail(FBFFTCONV_ERR_COMM, "%zu communicator(s) still attached to handles", g_comms.size());
 }
 
 int fbfftconv_comm_destroy(fbfftconv_handle* h) {

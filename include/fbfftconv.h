@@ -179,11 +179,14 @@ int fbfftconv_acc_grad_parameters_bias_noalloc(const float* grad_output, float* 
  * Replaces the gather / add / broadcast of nn.DataParallel
  * (fbcunn/DataParallel.lua:105-131) by one NCCL all-reduce over NVLink.  Rank 0
  * makes an id, every rank gets the same 128 bytes (by any side channel) and calls
- * fbfftconv_comm_init.  Handles that name the same id share one communicator, which is
- * destroyed with the last of them.  libnccl is loaded at run time on the first call. */
+ * fbfftconv_comm_init.  Handles that name the same id share one communicator; it stays
+ * alive (an id cannot be used twice) until fbfftconv_comm_shutdown, which destroys every
+ * communicator no handle is attached to.  fbfftconv_comm_destroy detaches one handle.
+ * libnccl is loaded at run time on the first call. */
 int fbfftconv_comm_unique_id(void* id128);
 int fbfftconv_comm_init(fbfftconv_handle* h, const void* id128, int rank, int nranks);
 int fbfftconv_comm_destroy(fbfftconv_handle* h);
+int fbfftconv_comm_shutdown(void);
 
 /* ---- per-kernel timing ---------------------------------------------------------
  * With profiling enabled every kernel (and collective) a pass enqueues is bracketed
