@@ -252,9 +252,20 @@ int contract(const float2* a, const float2* b, float2* c, int bins, int m, int n
   p.alpha = alpha;
   p.conj_a = conj_a;
   p.conj_b = conj_b;
-  (void)simt;  // the CUDA-core kernel is the only contraction built so far
-  FBF_CUDA(launch_contract_simt(p, s));
+  if (!simt && contract_tc_supported(p)) {
+    FBF_CUDA(launch_contract_tc(p, s));
+  } else {
+    FBF_CUDA(launch_contract_simt(p, s));
+  }
   return FBFFTCONV_OK;
+}
+
+// Contractions with a tiny column count or depth are bandwidth-bound streams: the CUDA-core
+// kernels (one of them shaped for <= 4 columns) serve them; everything else goes to the
+// tensor cores.
+bool thin_contraction(int m, int n, int k) {
+  (void)m;
+  return n <= 4 || k < 8;
 }
 
 bool valid_fft_size(int n) { return n == 8 || n == 16 || n == 32 || n == 64 || n == 128; }
@@ -396,7 +407,7 @@ int fbfftconv_update_output(fbfftconv_handle* h, const float* input, const float
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const fbfftconv_desc& d = h->d;
   const int B = d.batch, P = d.n_input_plane, F = d.n_output_plane;
-  const bool simt = d.flags & FBFFTCONV_CONTRACT_SIMT;
+  const bool simt = (d.flags & FBFFTCONV_CONTRACT_SIMT) || thin_contraction(B, F, P);
   const int pass = FBFFTCONV_PASS_UPDATE_OUTPUT;
   // I^[bin][b][p], W^[bin][f][p]
   {
@@ -430,7 +441,7 @@ int fbfftconv_update_grad_input(fbfftconv_handle* h, const float* grad_output, c
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const fbfftconv_desc& d = h->d;
   const int B = d.batch, P = d.n_input_plane, F = d.n_output_plane;
-  const bool simt = d.flags & FBFFTCONV_CONTRACT_SIMT;
+  const bool simt = (d.flags & FBFFTCONV_CONTRACT_SIMT) || thin_contraction(B, P, F);
   const int pass = FBFFTCONV_PASS_UPDATE_GRAD_INPUT;
   // O'^[bin][b][f], W^[bin][p][f] (weight planes transposed on the fly)
   {
@@ -466,7 +477,7 @@ int fbfftconv_acc_grad_parameters(fbfftconv_handle* h, const float* input, const
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const fbfftconv_desc& d = h->d;
   const int B = d.batch, P = d.n_input_plane, F = d.n_output_plane;
-  const bool simt = d.flags & FBFFTCONV_CONTRACT_SIMT;
+  const bool simt = (d.flags & FBFFTCONV_CONTRACT_SIMT) || thin_contraction(F, P, B);
   const int accumulate = (d.flags & FBFFTCONV_ACCUMULATE_GRADS) ? 1 : 0;
   const int pass = FBFFTCONV_PASS_ACC_GRAD_PARAMETERS;
   // O'^[bin][f][b], I^[bin][p][b]: the batch is the contraction index here
@@ -692,6 +703,8 @@ int fbfftconv_acc_grad_parameters_bias(const float* grad_output, float* grad_bia
                             static_cast<cudaStream_t>(stream)));
   return FBFFTCONV_OK;
 }
+
+int fbfftconv_tensor_core_status(int reset) { return contract_tc_error(reset != 0); }
 
 // ---- per-kernel timing ---------------------------------------------------------
 

@@ -29,6 +29,12 @@ struct ContractParams {
   int conj_a, conj_b;
 };
 cudaError_t launch_contract_simt(const ContractParams& p, cudaStream_t stream);
+// Tensor-core (tcgen05, 3xTF32) contraction.  contract_tc_error returns the first
+// non-zero code a block of that kernel has raised (a bounded wait that ran out) since the
+// last reset; it synchronises with the device.
+bool contract_tc_supported(const ContractParams& p);
+cudaError_t launch_contract_tc(const ContractParams& p, cudaStream_t stream);
+int contract_tc_error(bool reset);
 
 cudaError_t launch_bias_add(float* out, const float* bias, int batch, int planes, int hw,
                             cudaStream_t stream);

@@ -148,6 +148,11 @@ int fbfftconv_ifft2d(const void* spectrum, float* real, const float* bias, int d
 int fbfftconv_transpose_mm(const void* a, const void* b, void* c, int bins, int m, int n, int k,
                            float alpha, int conj_a, int conj_b, int use_simt,
                            fbfftconv_stream stream);
+/* The tensor-core contraction bounds every wait on the device; a block whose wait runs out
+ * stops, frees its tensor memory and records a non-zero code.  This call waits for the
+ * device and returns the first such code since the last reset (0 = none, -1 = the query
+ * itself failed). */
+int fbfftconv_tensor_core_status(int reset);
 /* Replaces updateOutputBiasFFI (fbcunn/FFTCDefs.lua:4, src/ConvolutionBias.cu:39-51). */
 int fbfftconv_update_output_bias(float* output, const float* bias, int batch, int planes, int h,
                                  int w, fbfftconv_stream stream);

@@ -136,7 +136,7 @@ def test_ifft2d_crop_bias_and_round_trip(N):
 def test_transpose_mm(use_simt, conj_a, conj_b):
     rng = np.random.default_rng(3)
     for (bins, m, n, k) in [(5, 7, 9, 3), (3, 64, 64, 8), (2, 130, 70, 21), (1, 1, 1, 1), (4, 16, 128, 128),
-                            (3, 130, 3, 96), (2, 96, 4, 128)]:
+                            (3, 130, 3, 96), (2, 96, 4, 128), (3, 128, 384, 384), (2, 300, 200, 77)]:
         kp, npad = (k + 3) // 4 * 4, (n + 3) // 4 * 4
         a = np.zeros((bins, m, kp), np.complex64)
         b = np.zeros((bins, n, kp), np.complex64)
@@ -152,7 +152,11 @@ def test_transpose_mm(use_simt, conj_a, conj_b):
         b64 = b.astype(np.complex128).conj() if conj_b else b.astype(np.complex128)
         ref = 0.25 * np.einsum("zmk,znk->zmn", a64, b64)
         got = c.cpu().numpy()[:, :, :n]
-        assert np.abs(got - ref).max() <= 2e-6 * np.abs(ref).max(), (bins, m, n, k)
+        # exact-fp32 CUDA-core kernel: 2e-6; tensor cores with the 3xTF32 split (each product
+        # good to about 2^-21): 1e-5, still ten times inside the 1e-4 bar of the passes
+        tol = 2e-6 if use_simt else 1e-5
+        assert capi.lib().fbfftconv_tensor_core_status(1) == 0, "a bounded wait ran out on the device"
+        assert np.abs(got - ref).max() <= tol * np.abs(ref).max(), (bins, m, n, k)
 
 
 def test_bias_kernels():
