@@ -312,10 +312,20 @@ def kernel_table(L, B, prof, pk):
         avg_s = ms / n / 1e3
         row = {"pass": PASSES[pi], "kernel": sname, "launches": n, "avg_us": 1e6 * avg_s, "total_ms": ms,
                "gbs": by / avg_s / 1e9 if avg_s > 0 else None}
+        if row["gbs"] is not None:
+            row["frac_hbm"] = row["gbs"] / pk["hbm_gbs"]
         if fl:
             row["tflops"] = fl / avg_s / 1e12 if avg_s > 0 else None
+            if row["tflops"] is not None:
+                row["frac_tensor_3xtf32"] = row["tflops"] / tensor_peak_3xtf32(pk)
         rows.append(row)
     return rows
+
+
+def tensor_peak_3xtf32(pk):
+    """Algorithmic TFLOP/s the 3xTF32 contraction can reach: dense TF32 is taken as half the
+    measured bf16 rate and every product costs three MMAs."""
+    return pk["bf16_tflops"] / 2.0 / 3.0
 
 
 def run_gpu_arm(args):
@@ -381,19 +391,32 @@ def run_gpu_arm(args):
     clocks = sampler.stop() if rank == 0 else None
     prof = read_profile(run.handle())
     capi.check(lib.fbfftconv_profile_enable(run.handle(), 0))
+    device_status = int(lib.fbfftconv_tensor_core_status(0))
+    if device_status != 0:
+        raise SystemExit(f"tensor-core contraction reported device status {device_status}")
     ms_per_step = elapsed_ms / args.steps
     value = 3.0 * conv_flops(L) / (ms_per_step / 1e3) / 1e12
 
     kernels = kernel_table(L, local_b, prof, pk)
     top = max((k for k in kernels if k["kernel"] != "allreduce"), key=lambda k: k["total_ms"])
-    tensor_bound = False  # the fp32 CUDA-core contraction is compared with HBM like the transforms
     by, fl = stage_algorithmic(L, local_b, PASSES.index(top["pass"]), top["kernel"])
-    achieved = by / (top["avg_us"] / 1e6) / 1e9
-    roofline = {"bound": "hbm", "kernel": f'{top["kernel"]} of {top["pass"]}', "achieved": achieved,
-                "peak": pk["hbm_gbs"], "peak_source": pk["source"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"],
-                "traffic": None, "algorithmic_bytes_per_launch": by, "avg_launch_us": top["avg_us"],
-                "share_of_step": top["total_ms"] / elapsed_ms}
-    del tensor_bound
+    secs = top["avg_us"] / 1e6
+    # the contraction is held against the tensor roofline where its intensity is above the
+    # ridge of (3xTF32 peak) / (HBM peak), otherwise against HBM like the transforms
+    ridge = tensor_peak_3xtf32(pk) * 1e12 / (pk["hbm_gbs"] * 1e9)
+    if fl and fl / by > ridge:
+        achieved = fl / secs / 1e12
+        roofline = {"bound": "tensor", "kernel": f'{top["kernel"]} of {top["pass"]}', "achieved": achieved,
+                    "peak": tensor_peak_3xtf32(pk), "peak_source": pk["source"] + " bf16 / 2 (TF32) / 3 (3xTF32)",
+                    "unit": "TFLOP/s", "frac": achieved / tensor_peak_3xtf32(pk), "traffic": None,
+                    "algorithmic_flops_per_launch": fl}
+    else:
+        achieved = by / secs / 1e9
+        roofline = {"bound": "hbm", "kernel": f'{top["kernel"]} of {top["pass"]}', "achieved": achieved,
+                    "peak": pk["hbm_gbs"], "peak_source": pk["source"], "unit": "GB/s",
+                    "frac": achieved / pk["hbm_gbs"], "traffic": None, "algorithmic_bytes_per_launch": by}
+    roofline["avg_launch_us"] = top["avg_us"]
+    roofline["share_of_step"] = top["total_ms"] / elapsed_ms
 
     # ---- e2e: host buffers through the *_host entry points ----------------------
     e2e = measure_e2e(torch, lib, run, L, local_b, world, barrier, max_over_ranks,

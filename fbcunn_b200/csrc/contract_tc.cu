@@ -20,7 +20,7 @@
 //   warp 0      TMA producer: raw fp32 tiles of A (128 rows) and B (64 rows), 32 floats
 //               (16 complex k) per stage
 //   warp 1      allocates tensor memory; one lane issues the MMAs
-//   warps 2..5  converters (split, rotate, write the 128-byte-swizzled K-major operand
+//   warps 2..9  converters (split, rotate, write the 128-byte-swizzled K-major operand
 //               tiles), then the epilogue (tcgen05.ld, scale, store)
 // Every wait on an mbarrier is bounded; on a time-out the block raises a flag, stops
 // issuing work, waits (bounded) for copies in flight, frees its tensor memory and
@@ -41,8 +41,9 @@ constexpr int UMMA_N = 2 * BNC;    // real accumulator columns
 constexpr int KB_FLOATS = 32;      // floats of K per stage: one 128-byte swizzle row
 constexpr int RAW_STAGES = 3;
 constexpr int CONV_STAGES = 2;
-constexpr int THREADS = 192;
-constexpr int CONVERTER_THREADS = 128;
+constexpr int CONVERTER_WARPS = 8;
+constexpr int CONVERTER_THREADS = 32 * CONVERTER_WARPS;
+constexpr int THREADS = 64 + CONVERTER_THREADS;
 
 constexpr int RAW_A_BYTES = BM * KB_FLOATS * 4;     // 16 KB
 constexpr int RAW_B_BYTES = BNC * KB_FLOATS * 4;    //  8 KB
@@ -206,10 +207,10 @@ contract_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   if (threadIdx.x == 0) {
     for (int i = 0; i < RAW_STAGES; ++i) {
       mbar_init(&full_raw[i], 1);
-      mbar_init(&empty_raw[i], 4);
+      mbar_init(&empty_raw[i], CONVERTER_WARPS);
     }
     for (int i = 0; i < CONV_STAGES; ++i) {
-      mbar_init(&full_conv[i], 4);
+      mbar_init(&full_conv[i], CONVERTER_WARPS);
       mbar_init(&empty_conv[i], 1);
     }
     mbar_init(accum_full, 1);
@@ -269,7 +270,7 @@ contract_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     }
   } else {
     // ---------------- converters, then epilogue ----------------
-    const int ct = threadIdx.x - 64;  // 0..127
+    const int ct = threadIdx.x - 64;  // 0..CONVERTER_THREADS-1
     bool ok = true;
     for (int kb = 0; kb < kblocks && ok; ++kb) {
       const int s = kb % RAW_STAGES, cs = kb % CONV_STAGES;
@@ -323,12 +324,15 @@ contract_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld below needs the whole warp
     if (ok) {
       tc_fence_after_sync();
-      // tensor-memory lanes 32*(warp%4) .. +31 belong to this warp; lane = tile row
+      // tensor-memory lanes 32*(warp%4) .. +31 belong to this warp; lane = tile row.  The
+      // warps that share a quarter split the accumulator columns between them.
       const int quarter = warp & 3;
+      const int share = (warp - 2) >> 2;
+      constexpr int kColBlocks = UMMA_N / 32, kShares = CONVERTER_WARPS / 4;
       const int row = m0 + quarter * 32 + lane;
       float2* crow = p.c + ((long long)bin * p.m + row) * p.ldc + n0;
 #pragma unroll 1
-      for (int cb = 0; cb < UMMA_N / 32; ++cb) {
+      for (int cb = share * (kColBlocks / kShares); cb < (share + 1) * (kColBlocks / kShares); ++cb) {
         float v[32];
         tmem_load_32cols(tmem_base + (uint32_t(quarter * 32) << 16) + cb * 32, v);
         if (row < p.m) {
