@@ -23,6 +23,7 @@ ERR_COMM = 5
 
 ACCUMULATE_GRADS = 1
 CONTRACT_SIMT = 2
+BIN_MAJOR_ONLY = 4
 
 
 class Desc(ctypes.Structure):
@@ -58,7 +59,7 @@ _SIGNATURES = {
     "fbfftconv_acc_grad_parameters_host": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p]),
     "fbfftconv_spectrum_bytes": (c_size_t, [c_int, c_int, c_int]),
     "fbfftconv_fft2d": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
-    "fbfftconv_ifft2d": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "fbfftconv_ifft2d": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "fbfftconv_transpose_mm": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p]),
     "fbfftconv_tensor_core_status": (c_int, [c_int]),
     "fbfftconv_update_output_bias": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),

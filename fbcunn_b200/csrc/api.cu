@@ -119,6 +119,7 @@ struct fbfftconv_handle {
   int device;
   int N, bins;
   int oH, oW;
+  bool plane_major = false;  // <= 4 input planes at a cooperative transform size: see contract_stream.cu
   // frequency buffers, each sized for the largest use among the three passes
   size_t bytes_in, bytes_out, bytes_w, bytes_small, bytes_total;
   char* ws = nullptr;
@@ -194,8 +195,25 @@ struct DeviceGuard {
   }
 };
 
+// layout: 0 = [bin][d1][d2], 1 = [bin][d2][d1], 2 = plane-major [d1][d2][bin]
+void set_spectrum_layout(FftParams& p, int fft_size, bool plane_major) {
+  const long long bins = (long long)(fft_size / 2 + 1) * fft_size;
+  if (plane_major) {
+    p.kc = p.n_inner;
+    p.spec_bin = 1;
+    p.spec_row = (long long)p.n_inner * bins;
+    p.spec_inner = bins;
+  } else {
+    p.kc = pad4(p.n_inner);
+    p.spec_bin = (long long)p.n_rows * p.kc;
+    p.spec_row = p.kc;
+    p.spec_inner = 1;
+  }
+}
+
 FftParams forward_params(const float* real, float2* spec, int d1, int d2, int h, int w, int pad_u,
-                         int pad_l, bool transposed) {
+                         int pad_l, int layout, int fft_size) {
+  const bool transposed = layout == 1;
   FftParams p{};
   p.real_in = real;
   p.spec = spec;
@@ -214,12 +232,12 @@ FftParams forward_params(const float* real, float2* spec, int d1, int d2, int h,
     p.real_row_stride = 1;
     p.real_inner_stride = d2;
   }
-  p.kc = pad4(p.n_inner);
+  set_spectrum_layout(p, fft_size, layout == 2);
   return p;
 }
 
 FftParams inverse_params(const float2* spec, float* real, const float* bias, int d1, int d2, int h,
-                         int w, int off_y, int off_x, int accumulate) {
+                         int w, int off_y, int off_x, int accumulate, bool plane_major, int fft_size) {
   FftParams p{};
   p.real_out = real;
   p.spec = const_cast<float2*>(spec);
@@ -230,10 +248,10 @@ FftParams inverse_params(const float2* spec, float* real, const float* bias, int
   p.off_x = off_x;
   p.n_rows = d1;
   p.n_inner = d2;
-  p.kc = pad4(d2);
   p.real_row_stride = d2;
   p.real_inner_stride = 1;
   p.accumulate = accumulate;
+  set_spectrum_layout(p, fft_size, plane_major);
   return p;
 }
 
@@ -348,6 +366,7 @@ int fbfftconv_create(const fbfftconv_desc* desc, fbfftconv_handle** out) {
   h->device = device;
   h->N = N;
   h->bins = (N / 2 + 1) * N;
+  h->plane_major = d.n_input_plane <= 4 && N >= 64 && !(d.flags & FBFFTCONV_BIN_MAJOR_ONLY);
   h->oH = oH;
   h->oW = oW;
   const size_t B = d.batch, P = d.n_input_plane, F = d.n_output_plane, bins = h->bins;
@@ -409,24 +428,29 @@ int fbfftconv_update_output(fbfftconv_handle* h, const float* input, const float
   const int B = d.batch, P = d.n_input_plane, F = d.n_output_plane;
   const bool simt = (d.flags & FBFFTCONV_CONTRACT_SIMT) || thin_contraction(B, F, P);
   const int pass = FBFFTCONV_PASS_UPDATE_OUTPUT;
-  // I^[bin][b][p], W^[bin][f][p]
+  const bool pm = h->plane_major;
+  const float norm = 1.0f / (float)(h->N * h->N);
+  // I^[bin][b][p], W^[bin][f][p]   (plane-major: I^[b][p][bin], W^[f][p][bin])
   {
     StageTimer t(h, pass, FBFFTCONV_STAGE_FFT_A, s);
-    FBF_CUDA(launch_forward(forward_params(input, h->buf_in(), B, P, d.input_h, d.input_w, d.pad_h, d.pad_w, false), h->N, s));
+    FBF_CUDA(launch_forward(forward_params(input, h->buf_in(), B, P, d.input_h, d.input_w, d.pad_h, d.pad_w, pm ? 2 : 0, h->N), h->N, s));
   }
   {
     StageTimer t(h, pass, FBFFTCONV_STAGE_FFT_B, s);
-    FBF_CUDA(launch_forward(forward_params(weight, h->buf_w(), F, P, d.kernel_h, d.kernel_w, 0, 0, false), h->N, s));
+    FBF_CUDA(launch_forward(forward_params(weight, h->buf_w(), F, P, d.kernel_h, d.kernel_w, 0, 0, pm ? 2 : 0, h->N), h->N, s));
   }
-  // O^[bin][b][f] = 1/N^2 sum_p I^[b][p] conj(W^[f][p])
+  // O^[b][f] = 1/N^2 sum_p I^[b][p] conj(W^[f][p]) per bin
   {
     StageTimer t(h, pass, FBFFTCONV_STAGE_CONTRACT, s);
-    FBF_TRY(contract(h->buf_in(), h->buf_w(), h->buf_out(), h->bins, B, F, P,
-                     1.0f / (float)(h->N * h->N), 0, 1, simt, s));
+    if (pm) {
+      FBF_CUDA(launch_stream_expand(h->buf_in(), h->buf_w(), h->buf_out(), B, F, P, h->bins, norm, s));
+    } else {
+      FBF_TRY(contract(h->buf_in(), h->buf_w(), h->buf_out(), h->bins, B, F, P, norm, 0, 1, simt, s));
+    }
   }
   {
     StageTimer t(h, pass, FBFFTCONV_STAGE_IFFT, s);
-    FBF_CUDA(launch_inverse(inverse_params(h->buf_out(), output, bias, B, F, h->oH, h->oW, 0, 0, 0), h->N, s));
+    FBF_CUDA(launch_inverse(inverse_params(h->buf_out(), output, bias, B, F, h->oH, h->oW, 0, 0, 0, pm, h->N), h->N, s));
   }
   return FBFFTCONV_OK;
 }
@@ -443,25 +467,30 @@ int fbfftconv_update_grad_input(fbfftconv_handle* h, const float* grad_output, c
   const int B = d.batch, P = d.n_input_plane, F = d.n_output_plane;
   const bool simt = (d.flags & FBFFTCONV_CONTRACT_SIMT) || thin_contraction(B, P, F);
   const int pass = FBFFTCONV_PASS_UPDATE_GRAD_INPUT;
+  const bool pm = h->plane_major;
+  const float norm = 1.0f / (float)(h->N * h->N);
   // O'^[bin][b][f], W^[bin][p][f] (weight planes transposed on the fly)
   {
     StageTimer t(h, pass, FBFFTCONV_STAGE_FFT_A, s);
-    FBF_CUDA(launch_forward(forward_params(grad_output, h->buf_out(), B, F, h->oH, h->oW, 0, 0, false), h->N, s));
+    FBF_CUDA(launch_forward(forward_params(grad_output, h->buf_out(), B, F, h->oH, h->oW, 0, 0, pm ? 2 : 0, h->N), h->N, s));
   }
   {
     StageTimer t(h, pass, FBFFTCONV_STAGE_FFT_B, s);
-    FBF_CUDA(launch_forward(forward_params(weight, h->buf_w(), F, P, d.kernel_h, d.kernel_w, 0, 0, true), h->N, s));
+    FBF_CUDA(launch_forward(forward_params(weight, h->buf_w(), F, P, d.kernel_h, d.kernel_w, 0, 0, pm ? 2 : 1, h->N), h->N, s));
   }
   // I'^[bin][b][p] = 1/N^2 sum_f O'^[b][f] W^[p][f]
   {
     StageTimer t(h, pass, FBFFTCONV_STAGE_CONTRACT, s);
-    FBF_TRY(contract(h->buf_out(), h->buf_w(), h->buf_in(), h->bins, B, P, F,
-                     1.0f / (float)(h->N * h->N), 0, 0, simt, s));
+    if (pm) {  // I'^[b][p] = sum_f O'^[b][f] W^[f][p]
+      FBF_CUDA(launch_stream_reduce(h->buf_out(), h->buf_w(), h->buf_in(), B, F, P, F, 1, false, h->bins, norm, s));
+    } else {
+      FBF_TRY(contract(h->buf_out(), h->buf_w(), h->buf_in(), h->bins, B, P, F, norm, 0, 0, simt, s));
+    }
   }
   {
     StageTimer t(h, pass, FBFFTCONV_STAGE_IFFT, s);
     FBF_CUDA(launch_inverse(inverse_params(h->buf_in(), grad_input, nullptr, B, P, d.input_h, d.input_w,
-                                           d.pad_h, d.pad_w, 0), h->N, s));
+                                           d.pad_h, d.pad_w, 0, pm, h->N), h->N, s));
   }
   return FBFFTCONV_OK;
 }
@@ -480,14 +509,15 @@ int fbfftconv_acc_grad_parameters(fbfftconv_handle* h, const float* input, const
   const bool simt = (d.flags & FBFFTCONV_CONTRACT_SIMT) || thin_contraction(F, P, B);
   const int accumulate = (d.flags & FBFFTCONV_ACCUMULATE_GRADS) ? 1 : 0;
   const int pass = FBFFTCONV_PASS_ACC_GRAD_PARAMETERS;
+  const bool pm = h->plane_major;
   // O'^[bin][f][b], I^[bin][p][b]: the batch is the contraction index here
   {
     StageTimer t(h, pass, FBFFTCONV_STAGE_FFT_A, s);
-    FBF_CUDA(launch_forward(forward_params(grad_output, h->buf_out(), B, F, h->oH, h->oW, 0, 0, true), h->N, s));
+    FBF_CUDA(launch_forward(forward_params(grad_output, h->buf_out(), B, F, h->oH, h->oW, 0, 0, pm ? 2 : 1, h->N), h->N, s));
   }
   {
     StageTimer t(h, pass, FBFFTCONV_STAGE_FFT_B, s);
-    FBF_CUDA(launch_forward(forward_params(input, h->buf_in(), B, P, d.input_h, d.input_w, d.pad_h, d.pad_w, true), h->N, s));
+    FBF_CUDA(launch_forward(forward_params(input, h->buf_in(), B, P, d.input_h, d.input_w, d.pad_h, d.pad_w, pm ? 2 : 1, h->N), h->N, s));
   }
   NcclApi* api = h->comm ? nccl_api() : nullptr;
   if (h->comm && !api) return fail(FBFFTCONV_ERR_COMM, "libnccl is not loadable");
@@ -495,34 +525,40 @@ int fbfftconv_acc_grad_parameters(fbfftconv_handle* h, const float* input, const
     StageTimer t(h, pass, FBFFTCONV_STAGE_BIAS, s);
     // bin (0,0) of O'^[bin][f][b] is the plain sum of gradOutput plane (b, f): its real
     // parts, summed over b, are the bias gradient (src/ConvolutionBias.cu:61-97).
+    // (plane-major: element (b, f, bin 0) sits at ((b*F + f) * bins) complex values)
     const float* dc = reinterpret_cast<const float*>(h->buf_out());
-    const long long ld = 2LL * pad4(B);
+    const long long ld = pm ? 2LL * h->bins : 2LL * pad4(B);
+    const long long dc_step = pm ? 2LL * F * h->bins : 2;
     float* tmp = h->small() + (size_t)B * F;
     if (h->comm) {
-      FBF_CUDA(launch_row_sum(dc, tmp, F, B, ld, 2, scale, 0, s));
+      FBF_CUDA(launch_row_sum(dc, tmp, F, B, ld, dc_step, scale, 0, s));
       ncclResult_t r = api->AllReduce(tmp, tmp, (size_t)F, ncclFloat, ncclSum, h->comm, s);
       if (r != ncclSuccess) return nccl_fail(api, r, "ncclAllReduce(gradBias)");
       FBF_CUDA(launch_row_sum(tmp, grad_bias, F, 1, 1, 1, 1.0f, accumulate, s));
     } else {
-      FBF_CUDA(launch_row_sum(dc, grad_bias, F, B, ld, 2, scale, accumulate, s));
+      FBF_CUDA(launch_row_sum(dc, grad_bias, F, B, ld, dc_step, scale, accumulate, s));
     }
   }
   // W'^[bin][f][p] = scale/N^2 sum_b conj(O'^[f][b]) I^[p][b]
   {
     StageTimer t(h, pass, FBFFTCONV_STAGE_CONTRACT, s);
-    FBF_TRY(contract(h->buf_out(), h->buf_in(), h->buf_w(), h->bins, F, P, B,
-                     scale / (float)(h->N * h->N), 1, 0, simt, s));
+    const float norm = scale / (float)(h->N * h->N);
+    if (pm) {  // W'^[f][p] = sum_b conj(O'^[b][f]) I^[b][p]
+      FBF_CUDA(launch_stream_reduce(h->buf_out(), h->buf_in(), h->buf_w(), F, B, P, 1, F, true, h->bins, norm, s));
+    } else {
+      FBF_TRY(contract(h->buf_out(), h->buf_in(), h->buf_w(), h->bins, F, P, B, norm, 1, 0, simt, s));
+    }
   }
   if (h->comm) {
     StageTimer t(h, pass, FBFFTCONV_STAGE_ALLREDUCE, s);
-    const size_t count = (size_t)h->bins * F * pad4(P) * 2;
+    const size_t count = (size_t)h->bins * F * (pm ? P : pad4(P)) * 2;
     ncclResult_t r = api->AllReduce(h->buf_w(), h->buf_w(), count, ncclFloat, ncclSum, h->comm, s);
     if (r != ncclSuccess) return nccl_fail(api, r, "ncclAllReduce(gradWeight spectrum)");
   }
   {
     StageTimer t(h, pass, FBFFTCONV_STAGE_IFFT, s);
     FBF_CUDA(launch_inverse(inverse_params(h->buf_w(), grad_weight, nullptr, F, P, d.kernel_h, d.kernel_w,
-                                           0, 0, accumulate), h->N, s));
+                                           0, 0, accumulate, pm, h->N), h->N, s));
   }
   return FBFFTCONV_OK;
 }
@@ -657,20 +693,20 @@ int fbfftconv_fft2d(const float* real, void* spectrum, int d1, int d2, int h, in
   if (d1 <= 0 || d2 <= 0 || h <= 0 || w <= 0 || pad_u < 0 || pad_l < 0 || h + pad_u > fft_size ||
       w + pad_l > fft_size || d1 > 65535 || d2 > 65535)
     return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "plane of %dx%d at (%d,%d) does not fit %d", h, w, pad_u, pad_l, fft_size);
-  FBF_CUDA(launch_forward(forward_params(real, static_cast<float2*>(spectrum), d1, d2, h, w, pad_u, pad_l, transposed != 0),
+  FBF_CUDA(launch_forward(forward_params(real, static_cast<float2*>(spectrum), d1, d2, h, w, pad_u, pad_l, transposed, fft_size),
                           fft_size, static_cast<cudaStream_t>(stream)));
   return FBFFTCONV_OK;
 }
 
 int fbfftconv_ifft2d(const void* spectrum, float* real, const float* bias, int d1, int d2, int h,
-                     int w, int fft_size, int off_y, int off_x, int accumulate,
+                     int w, int fft_size, int off_y, int off_x, int accumulate, int plane_major,
                      fbfftconv_stream stream) {
   if (!real || !spectrum) return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "null argument");
   if (!valid_fft_size(fft_size)) return fail(FBFFTCONV_ERR_UNSUPPORTED_SIZE, "transform size %d not in {8,16,32,64,128}", fft_size);
   if (d1 <= 0 || d2 <= 0 || h <= 0 || w <= 0 || off_y < 0 || off_x < 0 || h + off_y > fft_size ||
       w + off_x > fft_size || d1 > 65535 || d2 > 65535)
     return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "window of %dx%d at (%d,%d) does not fit %d", h, w, off_y, off_x, fft_size);
-  FBF_CUDA(launch_inverse(inverse_params(static_cast<const float2*>(spectrum), real, bias, d1, d2, h, w, off_y, off_x, accumulate != 0),
+  FBF_CUDA(launch_inverse(inverse_params(static_cast<const float2*>(spectrum), real, bias, d1, d2, h, w, off_y, off_x, accumulate != 0, plane_major != 0, fft_size),
                           fft_size, static_cast<cudaStream_t>(stream)));
   return FBFFTCONV_OK;
 }

@@ -50,7 +50,7 @@ plane_sum_kernel(const float* __restrict__ grad_out, float* scratch, int batch, 
 
 // grad_bias[f] (=|+=) scale * sum_b src[f * ld + b * step]
 __global__ void __launch_bounds__(128)
-row_sum_kernel(const float* __restrict__ src, float* grad_bias, int batch, long long ld, int step,
+row_sum_kernel(const float* __restrict__ src, float* grad_bias, int batch, long long ld, long long step,
                float scale, int accumulate) {
   const int f = blockIdx.x;
   float v = 0.f;
@@ -79,7 +79,7 @@ cudaError_t launch_bias_grad(const float* grad_out, float* grad_bias, float* scr
   return cudaGetLastError();
 }
 
-cudaError_t launch_row_sum(const float* src, float* dst, int rows, int count, long long ld, int step,
+cudaError_t launch_row_sum(const float* src, float* dst, int rows, int count, long long ld, long long step,
                            float scale, int accumulate, cudaStream_t stream) {
   row_sum_kernel<<<rows, 128, 0, stream>>>(src, dst, count, ld, step, scale, accumulate);
   count_launch();

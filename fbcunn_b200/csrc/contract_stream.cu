@@ -1,0 +1,150 @@
+// Streaming contraction for layers with at most four input planes (sm_100a).
+//
+// When one dimension of the per-bin product is that thin (the first layer of a network:
+// three colour planes), the contraction is a bandwidth-bound stream over the large
+// spectrum, not a matrix product.  The spectra are then kept plane-major,
+// [plane][bin] with the bins contiguous, which is also the layout the FFT kernels of the
+// large transform sizes read and write with full coalescing; a thread owns two
+// neighbouring bins (one 16-byte access) and walks over planes.
+//
+// Stands where the reference calls transposeMMFFI on its plane-major buffers
+// (fbcunn/SpatialConvolutionFBFFT.lua:157-164, :244-251, :337-344; src/MM.cu:54-73).
+#include "kernels.h"
+
+namespace fbfft {
+
+namespace {
+
+constexpr int THREADS = 256;
+constexpr int PMAX = 4;
+
+struct C2 {  // two complex values
+  float2 a, b;
+};
+__device__ __forceinline__ C2 ld2(const float2* p) {
+  const float4 v = *reinterpret_cast<const float4*>(p);
+  return C2{make_float2(v.x, v.y), make_float2(v.z, v.w)};
+}
+__device__ __forceinline__ void st2(float2* p, const C2& v, float alpha) {
+  *reinterpret_cast<float4*>(p) = make_float4(alpha * v.a.x, alpha * v.a.y, alpha * v.b.x, alpha * v.b.y);
+}
+// acc += x * y, or conj(x) * y, or x * conj(y)
+template <int CONJ>  // 0 none, 1 conj x, 2 conj y
+__device__ __forceinline__ void mac1(float2& acc, float2 x, float2 y) {
+  const float sx = CONJ == 1 ? -1.f : 1.f, sy = CONJ == 2 ? -1.f : 1.f;
+  acc.x = fmaf(x.x, y.x, acc.x);
+  acc.x = fmaf(-sx * sy * x.y, y.y, acc.x);
+  acc.y = fmaf(sy * x.x, y.y, acc.y);
+  acc.y = fmaf(sx * x.y, y.x, acc.y);
+}
+template <int CONJ>
+__device__ __forceinline__ void mac2(C2& acc, const C2& x, const C2& y) {
+  mac1<CONJ>(acc.a, x.a, y.a);
+  mac1<CONJ>(acc.b, x.b, y.b);
+}
+
+// Z[u][v][bin] = alpha * sum_{p<P} X[u][p][bin] * conj(Y[v][p][bin])
+// block: TU rows u, a chunk of columns v, 512 bins.
+template <int TU>
+__global__ void __launch_bounds__(THREADS)
+stream_expand_kernel(const float2* __restrict__ X, const float2* __restrict__ Y, float2* __restrict__ Z, int U,
+                     int V, int P, int v_per_block, long long bins, float alpha) {
+  const long long bin = ((long long)blockIdx.x * THREADS + threadIdx.x) * 2;
+  if (bin >= bins) return;
+  const int u0 = blockIdx.y * TU;
+  const int v0 = blockIdx.z * v_per_block;
+  const int v1 = min(V, v0 + v_per_block);
+  C2 x[TU][PMAX];
+#pragma unroll
+  for (int i = 0; i < TU; ++i)
+#pragma unroll
+    for (int p = 0; p < PMAX; ++p)
+      x[i][p] = (u0 + i < U && p < P) ? ld2(X + ((long long)(u0 + i) * P + p) * bins + bin)
+                                      : C2{make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+  for (int v = v0; v < v1; ++v) {
+    C2 y[PMAX];
+#pragma unroll
+    for (int p = 0; p < PMAX; ++p)
+      y[p] = p < P ? ld2(Y + ((long long)v * P + p) * bins + bin) : C2{make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+#pragma unroll
+    for (int i = 0; i < TU; ++i) {
+      if (u0 + i >= U) break;
+      C2 acc{make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+#pragma unroll
+      for (int p = 0; p < PMAX; ++p) mac2<2>(acc, x[i][p], y[p]);
+      st2(Z + ((long long)(u0 + i) * V + v) * bins + bin, acc, alpha);
+    }
+  }
+}
+
+// Z[u][p][bin] = alpha * sum_{w<W} opX(X[u*xs_u + w*xs_w][bin]) * Y[w][p][bin],  p < P <= 4
+// block: TU rows u, 512 bins; the loop over w is the long one.
+template <int TU, bool CONJX>
+__global__ void __launch_bounds__(THREADS)
+stream_reduce_kernel(const float2* __restrict__ X, const float2* __restrict__ Y, float2* __restrict__ Z, int U,
+                     int W, int P, long long xs_u, long long xs_w, long long bins, float alpha) {
+  const long long bin = ((long long)blockIdx.x * THREADS + threadIdx.x) * 2;
+  if (bin >= bins) return;
+  const int u0 = blockIdx.y * TU;
+  C2 acc[TU][PMAX];
+#pragma unroll
+  for (int i = 0; i < TU; ++i)
+#pragma unroll
+    for (int p = 0; p < PMAX; ++p) acc[i][p] = C2{make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+#pragma unroll 2
+  for (int w = 0; w < W; ++w) {
+    C2 y[PMAX], x[TU];
+#pragma unroll
+    for (int p = 0; p < PMAX; ++p)
+      y[p] = p < P ? ld2(Y + ((long long)w * P + p) * bins + bin) : C2{make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+#pragma unroll
+    for (int i = 0; i < TU; ++i)
+      x[i] = u0 + i < U ? ld2(X + ((u0 + i) * xs_u + w * xs_w) * bins + bin)
+                        : C2{make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+#pragma unroll
+    for (int i = 0; i < TU; ++i)
+#pragma unroll
+      for (int p = 0; p < PMAX; ++p) mac2<CONJX ? 1 : 0>(acc[i][p], x[i], y[p]);
+  }
+#pragma unroll
+  for (int i = 0; i < TU; ++i) {
+    if (u0 + i >= U) break;
+#pragma unroll
+    for (int p = 0; p < PMAX; ++p)
+      if (p < P) st2(Z + ((long long)(u0 + i) * P + p) * bins + bin, acc[i][p], alpha);
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_stream_expand(const float2* x, const float2* y, float2* z, int U, int V, int P, long long bins,
+                                 float alpha, cudaStream_t stream) {
+  if (P < 1 || P > PMAX || (bins & 1)) return cudaErrorInvalidValue;
+  constexpr int TU = 4;
+  const int bin_blocks = (int)((bins / 2 + THREADS - 1) / THREADS);
+  int v_chunks = 1;
+  while (v_chunks < 8 && (long long)bin_blocks * ((U + TU - 1) / TU) * v_chunks < 148 * 8 && V / (v_chunks * 2) >= 8)
+    v_chunks *= 2;
+  const int v_per_block = (V + v_chunks - 1) / v_chunks;
+  dim3 grid(bin_blocks, (U + TU - 1) / TU, (V + v_per_block - 1) / v_per_block);
+  if (grid.y > 65535 || grid.z > 65535) return cudaErrorInvalidValue;
+  stream_expand_kernel<TU><<<grid, THREADS, 0, stream>>>(x, y, z, U, V, P, v_per_block, bins, alpha);
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t launch_stream_reduce(const float2* x, const float2* y, float2* z, int U, int W, int P, long long xs_u,
+                                 long long xs_w, bool conj_x, long long bins, float alpha, cudaStream_t stream) {
+  if (P < 1 || P > PMAX || (bins & 1)) return cudaErrorInvalidValue;
+  constexpr int TU = 2;
+  dim3 grid((unsigned)((bins / 2 + THREADS - 1) / THREADS), (U + TU - 1) / TU);
+  if (grid.y > 65535) return cudaErrorInvalidValue;
+  if (conj_x)
+    stream_reduce_kernel<TU, true><<<grid, THREADS, 0, stream>>>(x, y, z, U, W, P, xs_u, xs_w, bins, alpha);
+  else
+    stream_reduce_kernel<TU, false><<<grid, THREADS, 0, stream>>>(x, y, z, U, W, P, xs_u, xs_w, bins, alpha);
+  count_launch();
+  return cudaGetLastError();
+}
+
+}  // namespace fbfft

@@ -265,7 +265,10 @@ static inline FftGeom inverse_geom(int N, int T, int oh, int ow) {
 struct FftParams {
   const float* real_in;   // forward input
   float* real_out;        // inverse output
-  float2* spec;           // [bins][n_rows][kc]
+  float2* spec;           // element (bin, row, inner) at bin*spec_bin + row*spec_row + inner*spec_inner:
+                          //   bin-major   [bins][n_rows][kc]:      spec_bin = n_rows*kc, spec_row = kc, spec_inner = 1
+                          //   plane-major [n_rows][n_inner][bins]: spec_bin = 1, spec_row = n_inner*bins, spec_inner = bins
+  long long spec_bin, spec_row, spec_inner;
   const float* bias;      // inverse only: added per inner index, may be null
   int h, w;               // extent of the real planes
   int off_y, off_x;       // forward: placement offset; inverse: crop origin
@@ -354,8 +357,8 @@ struct Forward {
     const int kx = line / T, t = line - kx * T;
     const int inner = inner0 + t;
     if (inner >= p.kc) return;
-    const long long bin_stride = (long long)p.n_rows * p.kc;
-    float2* dst = p.spec + (long long)kx * bin_stride + (long long)row * p.kc + inner;
+    const long long bin_stride = p.spec_bin;
+    float2* dst = p.spec + (long long)kx * bin_stride + row * p.spec_row + inner * p.spec_inner;
     const int pitch = g.pitch2;
     const int he = g.he;
     float2 u[N];
@@ -377,8 +380,8 @@ struct Inverse {
     const int kx = line / T, t = line - kx * T;
     const int inner = inner0 + t;
     const bool live = inner < p.n_inner;
-    const long long bin_stride = (long long)p.n_rows * p.kc;
-    const float2* src = p.spec + (long long)kx * bin_stride + (long long)row * p.kc + inner;
+    const long long bin_stride = p.spec_bin;
+    const float2* src = p.spec + (long long)kx * bin_stride + row * p.spec_row + inner * p.spec_inner;
     const int pitch = g.pitch2;
     const int y0 = p.off_y, y1 = p.off_y + g.he;
     float2 u[N];
@@ -612,7 +615,7 @@ struct CoopForward {
   static FBF_HD void col_step2(const FftParams& p, const FftGeom& g, const char* smem, int tid,
                                int nthreads, int row, int inner0) {
     const float2* mid = reinterpret_cast<const float2*>(smem + g.off_b);
-    const long long bin_stride = (long long)p.n_rows * p.kc;
+    const long long bin_stride = p.spec_bin;
     for (int item = tid; item < L::COLS * N1; item += nthreads) {
       const int k1 = item / L::COLS, col = item - k1 * L::COLS;
       const int t = col / KX, kx = col - t * KX;
@@ -623,7 +626,7 @@ struct CoopForward {
 #pragma unroll
       for (int n2 = 0; n2 < N2; ++n2) u[n2] = c[n2 * L::PITCH2];
       fft_inreg<N2, false>(u);
-      float2* dst = p.spec + ((long long)k1 * KX + kx) * bin_stride + (long long)row * p.kc + inner;
+      float2* dst = p.spec + ((long long)k1 * KX + kx) * bin_stride + row * p.spec_row + inner * p.spec_inner;
       const long long step = (long long)(N1 * KX) * bin_stride;
 #pragma unroll
       for (int k2 = 0; k2 < N2; ++k2) dst[k2 * step] = u[k2];
@@ -649,7 +652,7 @@ struct CoopInverse {
     const int n2 = item / L::COLS, col = item - n2 * L::COLS;
     const int t = col / KX, kx = col - t * KX;
     const bool live = inner0 + t < p.n_inner;
-    const float2* src = base + ((long long)n2 * KX + kx) * bin_stride + t;
+    const float2* src = base + ((long long)n2 * KX + kx) * bin_stride + t * p.spec_inner;
     const long long step = (long long)(N2 * KX) * bin_stride;
 #pragma unroll
     for (int n1 = 0; n1 < N1; ++n1) r.v[n1] = live ? src[n1 * step] : make_float2(0.f, 0.f);
@@ -673,8 +676,8 @@ struct CoopInverse {
   static FBF_HD void col_step1(const FftParams& p, const FftGeom& g, char* smem, int tid, int nthreads,
                                int row, int inner0) {
     float2* mid = reinterpret_cast<float2*>(smem + g.off_b);
-    const long long bin_stride = (long long)p.n_rows * p.kc;
-    const float2* base = p.spec + (long long)row * p.kc + inner0;
+    const long long bin_stride = p.spec_bin;
+    const float2* base = p.spec + row * p.spec_row + inner0 * p.spec_inner;
     for (int item = tid; item < L::COLS * N2; item += 2 * nthreads) {
       ColLoad r0, r1;
       col_fetch(p, bin_stride, base, inner0, item, r0);

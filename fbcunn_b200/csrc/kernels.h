@@ -36,12 +36,20 @@ bool contract_tc_supported(const ContractParams& p);
 cudaError_t launch_contract_tc(const ContractParams& p, cudaStream_t stream);
 int contract_tc_error(bool reset);
 
+// Plane-major ([plane][bin]) streaming contractions for <= 4 input planes (contract_stream.cu):
+//   expand: z[u][v] = alpha * sum_p x[u][p] * conj(y[v][p])
+//   reduce: z[u][p] = alpha * sum_w op(x[u*xs_u + w*xs_w]) * y[w][p]
+cudaError_t launch_stream_expand(const float2* x, const float2* y, float2* z, int U, int V, int P, long long bins,
+                                 float alpha, cudaStream_t stream);
+cudaError_t launch_stream_reduce(const float2* x, const float2* y, float2* z, int U, int W, int P, long long xs_u,
+                                 long long xs_w, bool conj_x, long long bins, float alpha, cudaStream_t stream);
+
 cudaError_t launch_bias_add(float* out, const float* bias, int batch, int planes, int hw,
                             cudaStream_t stream);
 cudaError_t launch_bias_grad(const float* grad_out, float* grad_bias, float* scratch, int batch,
                              int planes, int hw, float scale, int accumulate, cudaStream_t stream);
 // dst[r] (=|+=) scale * sum_{i<count} src[r*ld + i*step]
-cudaError_t launch_row_sum(const float* src, float* dst, int rows, int count, long long ld, int step,
+cudaError_t launch_row_sum(const float* src, float* dst, int rows, int count, long long ld, long long step,
                            float scale, int accumulate, cudaStream_t stream);
 
 // Records `message` as the calling thread's last error (what fbfftconv_last_error

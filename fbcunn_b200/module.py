@@ -83,7 +83,7 @@ class SpatialConvolutionFBFFT:
 
         self.device = torch.device(device)
         self._accumulate = bool(accumulate)
-        assert contraction in ("auto", "simt")
+        assert contraction in ("auto", "simt", "bin_major")
         self._contraction = contraction
         shape_w = (self.nOutputPlane, self.nInputPlane, self.kH, self.kW)
         self.weight = torch.empty(shape_w, dtype=torch.float32, device=self.device)
@@ -223,7 +223,8 @@ class SpatialConvolutionFBFFT:
             return self._handle
         self.cleanupBuffers()
         flags = (capi.ACCUMULATE_GRADS if self._accumulate else 0) | \
-                (capi.CONTRACT_SIMT if self._contraction == "simt" else 0)
+                (capi.CONTRACT_SIMT if self._contraction == "simt" else 0) | \
+                (capi.BIN_MAJOR_ONLY if self._contraction == "bin_major" else 0)
         desc = capi.Desc(B, self.nInputPlane, self.nOutputPlane, iH, iW, self.kH, self.kW,
                          self.dH, self.dW, self.padUp, self.padLeft,
                          self.device.index if self.device.index is not None else torch.cuda.current_device(),
@@ -275,7 +276,7 @@ class FFTWrapper:
         assert time.is_cuda and time.dim() == 4 and time.is_contiguous() and time.dtype == torch.float32
         d1, d2, h, w = time.shape
         capi.check(capi.lib().fbfftconv_ifft2d(_ptr(frequency), _ptr(time), _ptr(bias), d1, d2, h, w, fft_size,
-                                               self.padUp, self.padLeft, int(accumulate), _stream(time.device)))
+                                               self.padUp, self.padLeft, int(accumulate), 0, _stream(time.device)))
         return time
 
     @staticmethod

@@ -50,7 +50,10 @@ enum {
    * fbcunn/SpatialConvolutionFBFFT.lua:337-349, src/ConvolutionBias.cu:95. */
   FBFFTCONV_ACCUMULATE_GRADS = 1,
   /* contraction on the CUDA cores in plain fp32 instead of the tensor cores */
-  FBFFTCONV_CONTRACT_SIMT = 2
+  FBFFTCONV_CONTRACT_SIMT = 2,
+  /* keep the bin-major frequency layout even for layers with <= 4 input planes, which by
+   * default use plane-major buffers and a streaming contraction at transform sizes 64/128 */
+  FBFFTCONV_BIN_MAJOR_ONLY = 4
 };
 
 /* Constructor arguments of nn.SpatialConvolutionFBFFT
@@ -130,15 +133,16 @@ size_t fbfftconv_spectrum_bytes(int fft_size, int rows, int inner);
 /* Replaces FFTWrapper_fft for the 2-D batched case (src/fft/FFTWrapperLua.cpp:209-272,
  * src/fft/FBFFTHost.cpp:39-116): real (d1, d2, h, w) placed at (pad_u, pad_l) of an
  * N x N zero square -> half spectrum.  transposed == 0 writes [bin][d1][d2],
- * transposed != 0 writes [bin][d2][d1]. */
+ * 1 writes [bin][d2][d1], 2 writes plane-major [d1][d2][bin] (no padding of d2). */
 int fbfftconv_fft2d(const float* real, void* spectrum, int d1, int d2, int h, int w, int fft_size,
                     int pad_u, int pad_l, int transposed, fbfftconv_stream stream);
 /* Replaces FFTWrapper_ffti (src/fft/FFTWrapperLua.cpp:209-272): un-normalised inverse
  * of spectrum [bin][d1][d2], cropped to the h x w window whose corner is (off_y, off_x).
  * bias (d2 values, may be NULL) is added to every element of plane (., j);
- * accumulate != 0 adds into `real` instead of overwriting. */
+ * accumulate != 0 adds into `real` instead of overwriting; plane_major != 0 reads
+ * [d1][d2][bin] instead of [bin][d1][d2]. */
 int fbfftconv_ifft2d(const void* spectrum, float* real, const float* bias, int d1, int d2, int h,
-                     int w, int fft_size, int off_y, int off_x, int accumulate,
+                     int w, int fft_size, int off_y, int off_x, int accumulate, int plane_major,
                      fbfftconv_stream stream);
 /* Replaces transposeMMFFI (fbcunn/FFTCDefs.lua:7-14, src/MM.cu:54-73) on bin-major
  * operands: for every bin  C[m][n] = alpha * sum_k opA(A[m][k]) * opB(B[n][k]),

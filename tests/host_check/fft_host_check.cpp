@@ -135,29 +135,47 @@ int dispatch(bool inverse, const FftParams& p, int N, int T, int oh, int ow) {
 
 }  // namespace
 
+namespace {
+void set_layout(FftParams& p, int N, int plane_major) {
+  const long long bins = (long long)(N / 2 + 1) * N;
+  if (plane_major) {
+    p.kc = p.n_inner;
+    p.spec_bin = 1;
+    p.spec_row = p.n_inner * bins;
+    p.spec_inner = bins;
+  } else {
+    p.spec_bin = (long long)p.n_rows * p.kc;
+    p.spec_row = p.kc;
+    p.spec_inner = 1;
+  }
+}
+}  // namespace
+
 extern "C" {
 
 int hostcheck_fft_forward(const float* real, float* spec, int N, int T, int h, int w, int pad_u,
                           int pad_l, int n_rows, int n_inner, int kc, long long row_stride,
-                          long long inner_stride) {
+                          long long inner_stride, int plane_major) {
   FftParams p{};
   p.real_in = real;
   p.spec = reinterpret_cast<float2*>(spec);
   p.h = h; p.w = w; p.off_y = pad_u; p.off_x = pad_l;
   p.n_rows = n_rows; p.n_inner = n_inner; p.kc = kc;
+  set_layout(p, N, plane_major);
   p.real_row_stride = row_stride; p.real_inner_stride = inner_stride;
   return dispatch(false, p, N, T, 0, 0);
 }
 
 int hostcheck_fft_inverse(const float* spec, float* real, const float* bias, int N, int T, int oh,
                           int ow, int off_y, int off_x, int n_rows, int n_inner, int kc,
-                          long long row_stride, long long inner_stride, int accumulate) {
+                          long long row_stride, long long inner_stride, int accumulate, int plane_major) {
   FftParams p{};
   p.real_out = real;
   p.spec = reinterpret_cast<float2*>(const_cast<float*>(spec));
   p.bias = bias;
   p.h = oh; p.w = ow; p.off_y = off_y; p.off_x = off_x;
   p.n_rows = n_rows; p.n_inner = n_inner; p.kc = kc;
+  set_layout(p, N, plane_major);
   p.real_row_stride = row_stride; p.real_inner_stride = inner_stride;
   p.accumulate = accumulate;
   return dispatch(true, p, N, T, oh, ow);

@@ -101,7 +101,7 @@ def test_substeps_reject_bad_arguments(lib):
     one = ctypes.c_void_p(16)
     assert lib.fbfftconv_fft2d(one, one, 1, 1, 4, 4, 12, 0, 0, 0, None) == capi.ERR_UNSUPPORTED_SIZE
     assert lib.fbfftconv_fft2d(one, one, 1, 1, 9, 4, 8, 0, 0, 0, None) == capi.ERR_INVALID_ARGUMENT
-    assert lib.fbfftconv_ifft2d(one, one, None, 1, 1, 4, 4, 8, 5, 0, 0, None) == capi.ERR_INVALID_ARGUMENT
+    assert lib.fbfftconv_ifft2d(one, one, None, 1, 1, 4, 4, 8, 5, 0, 0, 0, None) == capi.ERR_INVALID_ARGUMENT
     assert lib.fbfftconv_transpose_mm(one, one, one, 0, 1, 1, 1, 1.0, 0, 0, 0, None) == capi.ERR_INVALID_ARGUMENT
     assert lib.fbfftconv_status_string(capi.ERR_NOMEM) == b"out of device memory"
 

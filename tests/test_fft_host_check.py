@@ -52,7 +52,7 @@ def test_forward(hc, N, T):
             kc = (inner + 3) // 4 * 4
             spec = np.full(((N // 2 + 1) * N, rows, kc, 2), np.nan, np.float32)
             rc = hc.hostcheck_fft_forward(x.ctypes.data_as(ctypes.c_void_p), spec.ctypes.data_as(ctypes.c_void_p),
-                                          N, T, h, w, pu, pl, rows, inner, kc, LL(rs), LL(is_))
+                                          N, T, h, w, pu, pl, rows, inner, kc, LL(rs), LL(is_), 0)
             assert rc == 0
             ref = _bin_major(spectral.rfft2_padded(x, N, N, pu, pl))
             if transposed:
@@ -80,7 +80,7 @@ def test_inverse(hc, N, T):
         out = np.full((rows, inner, oh, ow), np.nan, np.float32)
         rc = hc.hostcheck_fft_inverse(spec.ctypes.data_as(ctypes.c_void_p), out.ctypes.data_as(ctypes.c_void_p),
                                       bias.ctypes.data_as(ctypes.c_void_p), N, T, oh, ow, oy, ox, rows, inner, kc,
-                                      LL(inner), LL(1), 0)
+                                      LL(inner), LL(1), 0, 0)
         assert rc == 0
         # un-normalised inverse (src/fft/FFTWrapperLua.cpp:235-237), cropped, bias added
         ref = spectral.irfft2_unnormalised(np.fft.rfft2(full), N)[:, :, oy:oy + oh, ox:ox + ow] + bias[None, :, None, None]
@@ -88,5 +88,26 @@ def test_inverse(hc, N, T):
         init = rng.standard_normal((rows, inner, oh, ow)).astype(np.float32)
         acc = init.copy()
         hc.hostcheck_fft_inverse(spec.ctypes.data_as(ctypes.c_void_p), acc.ctypes.data_as(ctypes.c_void_p), None,
-                                 N, T, oh, ow, oy, ox, rows, inner, kc, LL(inner), LL(1), 1)
+                                 N, T, oh, ow, oy, ox, rows, inner, kc, LL(inner), LL(1), 1, 0)
         assert np.abs(acc - (ref - bias[None, :, None, None] + init)).max() <= 3e-6 * np.abs(ref).max()
+
+
+@pytest.mark.parametrize("N,T", [(64, 1), (64, 4), (128, 1), (16, 1), (32, 2)])
+def test_plane_major_layout(hc, N, T):
+    """Spectrum stored [row][inner][bin] (bins contiguous): forward then inverse."""
+    rng = np.random.default_rng(N + T)
+    d1, d2, h, w, pu, pl = 3, 5, N - 6, N - 9, 1, 2
+    x = rng.standard_normal((d1, d2, h, w)).astype(np.float32)
+    bins = (N // 2 + 1) * N
+    spec = np.full((d1, d2, bins, 2), np.nan, np.float32)
+    rc = hc.hostcheck_fft_forward(x.ctypes.data_as(ctypes.c_void_p), spec.ctypes.data_as(ctypes.c_void_p),
+                                  N, T, h, w, pu, pl, d1, d2, d2, LL(d2), LL(1), 1)
+    assert rc == 0
+    ref = spectral.rfft2_padded(x, N, N, pu, pl).reshape(d1, d2, bins)   # bin = ky*(N/2+1) + kx
+    got = spec[..., 0] + 1j * spec[..., 1]
+    assert np.abs(got - ref).max() <= 3e-6 * np.abs(ref).max()
+    out = np.full((d1, d2, h, w), np.nan, np.float32)
+    rc = hc.hostcheck_fft_inverse(spec.ctypes.data_as(ctypes.c_void_p), out.ctypes.data_as(ctypes.c_void_p), None,
+                                  N, T, h, w, pu, pl, d1, d2, d2, LL(d2), LL(1), 0, 1)
+    assert rc == 0
+    assert np.abs(out / (N * N) - x).max() <= 5e-6 * np.abs(x).max()

@@ -224,7 +224,8 @@ REGRESSION_SHAPES = [
     (1, 3, 16, 3, 3, 8, 8, 0, 0), (64, 16, 16, 3, 3, 16, 16, 1, 1), (1, 128, 128, 3, 3, 32, 32, 0, 0),
     (2, 3, 5, 8, 8, 11, 11, 0, 0), (2, 2, 3, 13, 14, 20, 17, 0, 0), (1, 2, 2, 3, 3, 128, 128, 0, 0),
     (3, 5, 6, 9, 9, 64, 64, 0, 0), (2, 3, 96, 11, 11, 128, 128, 0, 0), (2, 5, 3, 3, 3, 33, 40, 2, 2),
-    (2, 4, 4, 3, 3, 126, 126, 1, 1),
+    (2, 4, 4, 3, 3, 126, 126, 1, 1), (2, 3, 5, 9, 9, 64, 64, 0, 0), (3, 1, 2, 5, 5, 40, 50, 2, 1),
+    (5, 2, 7, 3, 5, 70, 33, 0, 2),
 ]
 
 
@@ -234,6 +235,18 @@ def test_regression_shapes(shape):
     s = oracle.Shape(B, P, F, iH, iW, kH, kW, padH, padW)
     x, w, go, b = _data(s, hash(shape) % 10000, bias=True)
     _check_three_passes(s, x, w, go, b, scale=0.7)
+
+
+def test_thin_layers_in_both_frequency_layouts():
+    """Layers with <= 4 input planes use plane-major buffers and the streaming contraction at
+    transform sizes 64 / 128; the bin-major path must give the same result."""
+    s = oracle.Shape(6, 3, 10, 60, 57, 7, 4, 1, 2)
+    x, w, go, b = _data(s, 4242, bias=True)
+    a = _check_three_passes(s, x, w, go, b, scale=1.3)
+    c = _check_three_passes(s, x, w, go, b, scale=1.3, contraction="bin_major")
+    for name in ("output", "gradInput", "gradWeight", "gradBias"):
+        ta, tc = getattr(a, name), getattr(c, name)
+        assert float((ta - tc).abs().max()) <= 2e-5 * float(tc.abs().max()), name
 
 
 def test_random_sweep():
