@@ -49,6 +49,24 @@ FBF_HD float2 cmul(float2 a, float2 b) {
   return make_float2(a.x * b.x - a.y * b.y, a.x * b.y + a.y * b.x);
 }
 
+// Asynchronous 4-byte global -> shared copy: no register staging, so a thread keeps as
+// many in flight as it issues; async_copy_wait() before the barrier that publishes the
+// data.  The host harness copies synchronously.
+FBF_HD void async_copy4(float* smem_dst, const float* gmem_src) {
+#if defined(__CUDA_ARCH__)
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((unsigned)__cvta_generic_to_shared(smem_dst)),
+               "l"(gmem_src)
+               : "memory");
+#else
+  *smem_dst = *gmem_src;
+#endif
+}
+FBF_HD void async_copy_wait() {
+#if defined(__CUDA_ARCH__)
+  asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
+#endif
+}
+
 // (cos, sin)(2 pi i / 128) as literals: with a compile-time index the switch folds
 // into immediates.
 FBF_HD float2 tw128_literal(int i) {
@@ -311,17 +329,15 @@ struct Forward {
       const bool va = x >= 0 && ya >= 0 && ya < p.h;
       const bool vb = x >= 0 && yb >= 0 && yb < p.h;
       const int oa = ya * p.w + x, ob = yb * p.w + x;
-      float2* dst = ra + xx * g.pitch1 + j * T;
+      float* dst = reinterpret_cast<float*>(ra + xx * g.pitch1 + j * T);
       for (int t = part; t < T; t += ts) {
-        float a = 0.f, b = 0.f;
-        if (inner0 + t < p.n_inner) {
-          const float* plane = base + t * tstride;
-          if (va) a = plane[oa];
-          if (vb) b = plane[ob];
-        }
-        dst[t] = make_float2(a, b);
+        const bool live = inner0 + t < p.n_inner;
+        const float* plane = base + t * tstride;
+        if (live && va) async_copy4(dst + 2 * t, plane + oa); else dst[2 * t] = 0.f;
+        if (live && vb) async_copy4(dst + 2 * t + 1, plane + ob); else dst[2 * t + 1] = 0.f;
       }
     }
+    async_copy_wait();
   }
 
   // Phase 1a: a line into registers.
