@@ -633,8 +633,10 @@ struct CoopForward {
     const float2* mid = reinterpret_cast<const float2*>(smem + g.off_b);
     const long long bin_stride = p.spec_bin;
     for (int item = tid; item < L::COLS * N1; item += nthreads) {
-      const int k1 = item / L::COLS, col = item - k1 * L::COLS;
-      const int t = col / KX, kx = col - t * KX;
+      // neighbouring lanes take the T planes of one bin, so that their 8-byte stores share a line
+      const int k1 = item / L::COLS, ci = item - k1 * L::COLS;
+      const int kx = ci / T, t = ci - kx * T;
+      const int col = t * KX + kx;
       const int inner = inner0 + t;
       if (inner >= p.kc) continue;
       const float2* c = mid + col + N2 * k1 * L::PITCH2;
@@ -665,8 +667,10 @@ struct CoopInverse {
                                int item, ColLoad& r) {
     r.col = -1;
     if (item >= L::COLS * N2) return;
-    const int n2 = item / L::COLS, col = item - n2 * L::COLS;
-    const int t = col / KX, kx = col - t * KX;
+    // neighbouring lanes take the T planes of one bin: their 8-byte loads share a line
+    const int n2 = item / L::COLS, ci = item - n2 * L::COLS;
+    const int kx = ci / T, t = ci - kx * T;
+    const int col = t * KX + kx;
     const bool live = inner0 + t < p.n_inner;
     const float2* src = base + ((long long)n2 * KX + kx) * bin_stride + t * p.spec_inner;
     const long long step = (long long)(N2 * KX) * bin_stride;

@@ -57,17 +57,57 @@ fft2d_inverse_kernel(const __grid_constant__ FftParams p, const __grid_constant_
   Inverse<N, T>::store(p, g, smem, tid, blockDim.x, row, inner0);
 }
 
+__device__ __forceinline__ void prefetch_l2(const void* p) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
+
+#ifdef FBF_PHASE_TIMING
+// Debug builds only: clock cycles spent between phase boundaries, summed over blocks
+// (thread 0 of each block), read back through fbfft_debug_phase_clocks().
+__device__ unsigned long long g_phase_clocks[16];
+#define FBF_PHASE_BEGIN() long long fbf_t0 = clock64()
+#define FBF_PHASE_MARK(i)                                                   \
+  do {                                                                      \
+    if (threadIdx.x == 0) {                                                 \
+      const long long fbf_t1 = clock64();                                   \
+      atomicAdd(&g_phase_clocks[i], (unsigned long long)(fbf_t1 - fbf_t0)); \
+      fbf_t0 = fbf_t1;                                                      \
+    }                                                                       \
+  } while (0)
+#else
+#define FBF_PHASE_BEGIN()
+#define FBF_PHASE_MARK(i)
+#endif
+
 template <int N, int T>
 __global__ void __launch_bounds__(FBF_COOP_THREADS, 2)
 fft2d_forward_coop_kernel(const __grid_constant__ FftParams p, const __grid_constant__ FftGeom g) {
   extern __shared__ __align__(16) char smem[];
   const int tid = threadIdx.x, nth = blockDim.x;
-  const int row = blockIdx.y;
-  const int inner0 = blockIdx.x * T;
+  const int tiles_x = (p.kc + T - 1) / T;
+  const int total = tiles_x * p.n_rows;
+  // persistent blocks: tile w, then w + gridDim.x, ...; the real planes of the next tile are
+  // pulled into L2 while this one is transformed
+  for (int w = blockIdx.x; w < total; w += gridDim.x) {
+  const int row = w / tiles_x;
+  const int inner0 = (w - row * tiles_x) * T;
+  if (w + (int)gridDim.x < total) {
+    const int wn = w + gridDim.x;
+    const int rown = wn / tiles_x, innern = (wn - rown * tiles_x) * T;
+    const long long plane_bytes = (long long)p.h * p.w * 4;
+    for (int t = 0; t < T; ++t) {
+      if (innern + t >= p.n_inner) break;
+      const char* src = reinterpret_cast<const char*>(p.real_in) +
+                        (rown * p.real_row_stride + (innern + t) * p.real_inner_stride) * plane_bytes;
+      for (long long off = (long long)tid * 128; off < plane_bytes; off += (long long)nth * 128) prefetch_l2(src + off);
+    }
+  }
+  FBF_PHASE_BEGIN();
   for (int line0 = 0; line0 < g.lines1; line0 += g.chunk) {
     const int nl = min(g.chunk, g.lines1 - line0);
     CoopForward<N, T>::row_step1(p, g, smem, tid, nth, row, inner0, line0, nl);
     __syncthreads();
+    FBF_PHASE_MARK(0);
     // groups of eight lanes hold the eight residues of one line; mirror residues are
     // neighbours, so one shuffle hands each lane the partner's odd-indexed outputs
     constexpr int N1 = CoopForward<N, T>::N1, N2 = CoopForward<N, T>::N2;
@@ -83,10 +123,15 @@ fft2d_forward_coop_kernel(const __grid_constant__ FftParams p, const __grid_cons
       if (active) CoopForward<N, T>::row_step2_split(g, smem, base + tid, line0, u, mirror_odd);
     }
     __syncthreads();
+    FBF_PHASE_MARK(1);
   }
   CoopForward<N, T>::col_step1(g, smem, tid, nth);
   __syncthreads();
+  FBF_PHASE_MARK(2);
   CoopForward<N, T>::col_step2(p, g, smem, tid, nth, row, inner0);
+  FBF_PHASE_MARK(3);
+  __syncthreads();  // the buffers are reused by the next tile
+  }
 }
 
 template <int N, int T>
@@ -94,18 +139,37 @@ __global__ void __launch_bounds__(FBF_COOP_THREADS, 2)
 fft2d_inverse_coop_kernel(const __grid_constant__ FftParams p, const __grid_constant__ FftGeom g) {
   extern __shared__ __align__(16) char smem[];
   const int tid = threadIdx.x, nth = blockDim.x;
-  const int row = blockIdx.y;
-  const int inner0 = blockIdx.x * T;
+  const int tiles_x = (p.n_inner + T - 1) / T;
+  const int total = tiles_x * p.n_rows;
+  for (int w = blockIdx.x; w < total; w += gridDim.x) {
+  const int row = w / tiles_x;
+  const int inner0 = (w - row * tiles_x) * T;
+  if (p.spec_bin == 1 && w + (int)gridDim.x < total) {  // plane-major: the next tile's spectra are contiguous
+    const int wn = w + gridDim.x;
+    const int rown = wn / tiles_x, innern = (wn - rown * tiles_x) * T;
+    const long long plane_bytes = (long long)(N / 2 + 1) * N * 8;
+    for (int t = 0; t < T; ++t) {
+      if (innern + t >= p.n_inner) break;
+      const char* src = reinterpret_cast<const char*>(p.spec + rown * p.spec_row + (innern + t) * p.spec_inner);
+      for (long long off = (long long)tid * 128; off < plane_bytes; off += (long long)nth * 128) prefetch_l2(src + off);
+    }
+  }
+  FBF_PHASE_BEGIN();
   CoopInverse<N, T>::col_step1(p, g, smem, tid, nth, row, inner0);
   __syncthreads();
+  FBF_PHASE_MARK(8);
   CoopInverse<N, T>::col_step2(g, smem, tid, nth);
   __syncthreads();
+  FBF_PHASE_MARK(9);
   for (int line0 = 0; line0 < g.lines1; line0 += g.chunk) {
     const int nl = min(g.chunk, g.lines1 - line0);
     CoopInverse<N, T>::row_step1(p, g, smem, tid, nth, line0, nl);
     __syncthreads();
+    FBF_PHASE_MARK(10);
     CoopInverse<N, T>::row_step2(p, g, smem, tid, nth, row, inner0, line0, nl);
     __syncthreads();
+    FBF_PHASE_MARK(11);
+  }
   }
 }
 
@@ -139,6 +203,18 @@ int pick_tile(int N, GeomFn geom) {
   return best_any;
 }
 
+// Blocks of a persistent cooperative kernel: as many as are resident at once.
+int persistent_blocks(long long tiles, int smem_bytes) {
+  static int sms = [] {
+    int dev = 0, n = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    return n > 0 ? n : 148;
+  }();
+  const int per_sm = smem_bytes <= kSmemTwoBlocks ? 2 : 1;
+  const long long resident = (long long)sms * per_sm;
+  return (int)(tiles < resident ? tiles : resident);
+}
+
 template <int N, int T>
 cudaError_t run_forward(const FftParams& p, cudaStream_t stream) {
   if constexpr (!tile_allowed(N, T)) {
@@ -155,6 +231,7 @@ cudaError_t run_forward(const FftParams& p, cudaStream_t stream) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, g.smem_bytes);
     if (e != cudaSuccess) return e;
     dim3 grid((p.kc + T - 1) / T, p.n_rows);
+    if constexpr (N > 32) grid = dim3(persistent_blocks((long long)grid.x * grid.y, g.smem_bytes), 1);
     kernel<<<grid, g.threads, g.smem_bytes, stream>>>(p, g);
     count_launch();
     return cudaGetLastError();
@@ -177,6 +254,7 @@ cudaError_t run_inverse(const FftParams& p, cudaStream_t stream) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, g.smem_bytes);
     if (e != cudaSuccess) return e;
     dim3 grid((p.n_inner + T - 1) / T, p.n_rows);
+    if constexpr (N > 32) grid = dim3(persistent_blocks((long long)grid.x * grid.y, g.smem_bytes), 1);
     kernel<<<grid, g.threads, g.smem_bytes, stream>>>(p, g);
     count_launch();
     return cudaGetLastError();
@@ -231,3 +309,13 @@ cudaError_t launch_inverse(const FftParams& p, int N, cudaStream_t stream) {
 }
 
 }  // namespace fbfft
+
+#ifdef FBF_PHASE_TIMING
+extern "C" void fbfft_debug_phase_clocks(unsigned long long* out, int reset) {
+  cudaMemcpyFromSymbol(out, fbfft::g_phase_clocks, sizeof(fbfft::g_phase_clocks));
+  if (reset) {
+    unsigned long long zero[16] = {};
+    cudaMemcpyToSymbol(fbfft::g_phase_clocks, zero, sizeof(zero));
+  }
+}
+#endif
