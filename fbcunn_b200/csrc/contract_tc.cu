@@ -28,6 +28,7 @@
 #include <cuda.h>
 
 #include <cstdint>
+#include <cstdlib>
 
 #include "kernels.h"
 
@@ -356,6 +357,8 @@ contract_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   }
 }
 
+#include "contract_tc_wide.inc"
+
 // ---- host side -----------------------------------------------------------------
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -374,12 +377,13 @@ EncodeTiledFn encode_fn() {
 }
 
 // [bins][rows][k_floats] fp32, box {32 floats, box_rows, 1}; out-of-range elements read as zero.
-bool make_map(CUtensorMap* map, const void* base, int k_floats, int rows, int bins, int box_rows) {
+bool make_map(CUtensorMap* map, const void* base, int k_floats, int rows, int bins, int box_rows,
+              int box_floats = KB_FLOATS) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   const cuuint64_t dims[3] = {(cuuint64_t)k_floats, (cuuint64_t)rows, (cuuint64_t)bins};
   const cuuint64_t strides[2] = {(cuuint64_t)k_floats * 4, (cuuint64_t)k_floats * 4 * (cuuint64_t)rows};
-  const cuuint32_t box[3] = {(cuuint32_t)KB_FLOATS, (cuuint32_t)box_rows, 1};
+  const cuuint32_t box[3] = {(cuuint32_t)box_floats, (cuuint32_t)box_rows, 1};
   const cuuint32_t elem[3] = {1, 1, 1};
   return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), dims, strides, box, elem,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -394,8 +398,43 @@ bool contract_tc_supported(const ContractParams& p) {
          (p.lda & 3) == 0 && (p.ldb & 3) == 0 && (p.ldc & 3) == 0;
 }
 
+// Wide persistent kernel for shapes with at least 96 complex columns.
+cudaError_t launch_contract_tc_wide(const ContractParams& p, cudaStream_t stream) {
+  using namespace wide;
+  CUtensorMap map_a, map_b;
+  if (!make_map(&map_a, p.a, 2 * p.lda, p.m, p.bins, WBM, WKB) ||
+      !make_map(&map_b, p.b, 2 * p.ldb, p.n, p.bins, WBNC, WKB))
+    return cudaErrorInvalidValue;
+  WideParams t;
+  t.c = p.c;
+  t.m = p.m;
+  t.n = p.n;
+  t.ldc = p.ldc;
+  t.k_floats = 2 * p.lda;
+  t.m_tiles = (p.m + WBM - 1) / WBM;
+  t.n_tiles = (p.ldc + WBNC - 1) / WBNC;
+  const long long total = (long long)t.m_tiles * t.n_tiles * p.bins;
+  if (total > 0x7fffffff) return cudaErrorInvalidValue;
+  t.total_tiles = (int)total;
+  t.alpha = p.alpha;
+  const float sa = p.conj_a ? -1.f : 1.f, sb = p.conj_b ? -1.f : 1.f;
+  t.s_b1_im = -sa * sb;
+  t.s_b2_re = sb;
+  t.s_b2_im = sa;
+  cudaError_t e = cudaFuncSetAttribute(contract_tc_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, W_SMEM_BYTES);
+  if (e != cudaSuccess) return e;
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int grid = (int)(total < sms ? total : sms);
+  contract_tc_wide_kernel<<<grid, W_THREADS, W_SMEM_BYTES, stream>>>(map_a, map_b, t);
+  count_launch();
+  return cudaGetLastError();
+}
+
 cudaError_t launch_contract_tc(const ContractParams& p, cudaStream_t stream) {
   if (!contract_tc_supported(p)) return cudaErrorInvalidValue;
+  static const bool narrow_only = getenv("FBFFTCONV_TC_NARROW") != nullptr;  // tuning aid
+  if (!narrow_only && p.ldc >= 96) return launch_contract_tc_wide(p, stream);
   CUtensorMap map_a, map_b;
   if (!make_map(&map_a, p.a, 2 * p.lda, p.m, p.bins, BM) || !make_map(&map_b, p.b, 2 * p.ldb, p.n, p.bins, BNC))
     return cudaErrorInvalidValue;
