@@ -322,6 +322,21 @@ def kernel_table(L, B, prof, pk):
     return rows
 
 
+def captured_traffic(layer, top, L, local_b):
+    """DRAM bytes per launch of the dominant kernel from the committed ncu capture
+    (profiles/dram_traffic.json), scaled by the planes this launch processes; None where no
+    capture of that kernel on that layer exists."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "dram_traffic.json")) as f:
+            table = json.load(f)
+        entry = table[layer][f'{top["kernel"]}:{top["pass"]}']
+    except (OSError, KeyError, ValueError):
+        return None
+    if entry["unit"] == "launch":
+        return float(entry["bytes_per_unit"]) if local_b == L[0] else None
+    return float(entry["bytes_per_unit"]) * local_b * L[2]  # planes (b, f) in this launch
+
+
 def tensor_peak_3xtf32(pk):
     """Algorithmic TFLOP/s the 3xTF32 contraction can reach: dense TF32 is taken as half the
     measured bf16 rate and every product costs three MMAs."""
@@ -415,6 +430,7 @@ def run_gpu_arm(args):
         roofline = {"bound": "hbm", "kernel": f'{top["kernel"]} of {top["pass"]}', "achieved": achieved,
                     "peak": pk["hbm_gbs"], "peak_source": pk["source"], "unit": "GB/s",
                     "frac": achieved / pk["hbm_gbs"], "traffic": None, "algorithmic_bytes_per_launch": by}
+    roofline["traffic"] = captured_traffic(name, top, L, local_b)
     roofline["avg_launch_us"] = top["avg_us"]
     roofline["share_of_step"] = top["total_ms"] / elapsed_ms
 
