@@ -24,6 +24,7 @@ ERR_COMM = 5
 ACCUMULATE_GRADS = 1
 CONTRACT_SIMT = 2
 BIN_MAJOR_ONLY = 4
+ALLREDUCE_SPATIAL = 8
 
 
 class Desc(ctypes.Structure):

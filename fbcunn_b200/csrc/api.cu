@@ -373,8 +373,11 @@ int fbfftconv_create(const fbfftconv_desc* desc, fbfftconv_handle** out) {
   auto mx = [](size_t a, size_t b) { return a > b ? a : b; };
   h->bytes_in = align256(bins * mx(B * pad4(P), P * pad4(B)) * sizeof(float2));
   h->bytes_out = align256(bins * mx(B * pad4(F), F * pad4(B)) * sizeof(float2));
-  h->bytes_w = align256(bins * mx(F * pad4(P), P * pad4(F)) * sizeof(float2));
+  // (+ F floats behind the gradWeight spectrum: the bias gradient rides in the same all-reduce)
+  h->bytes_w = align256(bins * mx(F * pad4(P), P * pad4(F)) * sizeof(float2) + F * sizeof(float));
   h->bytes_small = align256((B * F + F) * sizeof(float));
+  if (d.flags & FBFFTCONV_ALLREDUCE_SPATIAL)  // local gradWeight + gradBias, summed across ranks
+    h->bytes_small += align256((F * P * d.kernel_h * d.kernel_w + F) * sizeof(float));
   h->bytes_total = h->bytes_in + h->bytes_out + h->bytes_w + h->bytes_small;
   *out = h;
   return FBFFTCONV_OK;
@@ -521,24 +524,13 @@ int fbfftconv_acc_grad_parameters(fbfftconv_handle* h, const float* input, const
   }
   NcclApi* api = h->comm ? nccl_api() : nullptr;
   if (h->comm && !api) return fail(FBFFTCONV_ERR_COMM, "libnccl is not loadable");
-  if (grad_bias) {
-    StageTimer t(h, pass, FBFFTCONV_STAGE_BIAS, s);
-    // bin (0,0) of O'^[bin][f][b] is the plain sum of gradOutput plane (b, f): its real
-    // parts, summed over b, are the bias gradient (src/ConvolutionBias.cu:61-97).
-    // (plane-major: element (b, f, bin 0) sits at ((b*F + f) * bins) complex values)
-    const float* dc = reinterpret_cast<const float*>(h->buf_out());
-    const long long ld = pm ? 2LL * h->bins : 2LL * pad4(B);
-    const long long dc_step = pm ? 2LL * F * h->bins : 2;
-    float* tmp = h->small() + (size_t)B * F;
-    if (h->comm) {
-      FBF_CUDA(launch_row_sum(dc, tmp, F, B, ld, dc_step, scale, 0, s));
-      ncclResult_t r = api->AllReduce(tmp, tmp, (size_t)F, ncclFloat, ncclSum, h->comm, s);
-      if (r != ncclSuccess) return nccl_fail(api, r, "ncclAllReduce(gradBias)");
-      FBF_CUDA(launch_row_sum(tmp, grad_bias, F, 1, 1, 1, 1.0f, accumulate, s));
-    } else {
-      FBF_CUDA(launch_row_sum(dc, grad_bias, F, B, ld, dc_step, scale, accumulate, s));
-    }
-  }
+  const bool spatial = h->comm && (d.flags & FBFFTCONV_ALLREDUCE_SPATIAL);
+  const size_t spec_floats = (size_t)h->bins * F * (pm ? P : pad4(P)) * 2;
+  const size_t n_weight = (size_t)F * P * d.kernel_h * d.kernel_w;
+  // Across ranks the bias gradient travels behind whatever the weight gradient is summed
+  // as: behind its spectrum, or behind the local spatial gradient.
+  float* local_w = h->small() + align256(((size_t)B * F + F) * sizeof(float)) / sizeof(float);
+  float* bias_part = spatial ? local_w + n_weight : reinterpret_cast<float*>(h->buf_w()) + spec_floats;
   // W'^[bin][f][p] = scale/N^2 sum_b conj(O'^[f][b]) I^[p][b]
   {
     StageTimer t(h, pass, FBFFTCONV_STAGE_CONTRACT, s);
@@ -549,16 +541,39 @@ int fbfftconv_acc_grad_parameters(fbfftconv_handle* h, const float* input, const
       FBF_TRY(contract(h->buf_out(), h->buf_in(), h->buf_w(), h->bins, F, P, B, norm, 1, 0, simt, s));
     }
   }
-  if (h->comm) {
+  if (grad_bias) {
+    StageTimer t(h, pass, FBFFTCONV_STAGE_BIAS, s);
+    // bin (0,0) of O'^[bin][f][b] is the plain sum of gradOutput plane (b, f): its real
+    // parts, summed over b, are the bias gradient (src/ConvolutionBias.cu:61-97).
+    // (plane-major: element (b, f, bin 0) sits at ((b*F + f) * bins) complex values)
+    const float* dc = reinterpret_cast<const float*>(h->buf_out());
+    const long long ld = pm ? 2LL * h->bins : 2LL * pad4(B);
+    const long long dc_step = pm ? 2LL * F * h->bins : 2;
+    if (h->comm)
+      FBF_CUDA(launch_row_sum(dc, bias_part, F, B, ld, dc_step, scale, 0, s));
+    else
+      FBF_CUDA(launch_row_sum(dc, grad_bias, F, B, ld, dc_step, scale, accumulate, s));
+  }
+  const size_t bias_floats = grad_bias ? (size_t)F : 0;
+  if (h->comm && !spatial) {
     StageTimer t(h, pass, FBFFTCONV_STAGE_ALLREDUCE, s);
-    const size_t count = (size_t)h->bins * F * (pm ? P : pad4(P)) * 2;
-    ncclResult_t r = api->AllReduce(h->buf_w(), h->buf_w(), count, ncclFloat, ncclSum, h->comm, s);
+    ncclResult_t r = api->AllReduce(h->buf_w(), h->buf_w(), spec_floats + bias_floats, ncclFloat, ncclSum, h->comm, s);
     if (r != ncclSuccess) return nccl_fail(api, r, "ncclAllReduce(gradWeight spectrum)");
   }
   {
     StageTimer t(h, pass, FBFFTCONV_STAGE_IFFT, s);
-    FBF_CUDA(launch_inverse(inverse_params(h->buf_w(), grad_weight, nullptr, F, P, d.kernel_h, d.kernel_w,
-                                           0, 0, accumulate, pm, h->N), h->N, s));
+    FBF_CUDA(launch_inverse(inverse_params(h->buf_w(), spatial ? local_w : grad_weight, nullptr, F, P, d.kernel_h,
+                                           d.kernel_w, 0, 0, spatial ? 0 : accumulate, pm, h->N), h->N, s));
+  }
+  if (spatial) {
+    StageTimer t(h, pass, FBFFTCONV_STAGE_ALLREDUCE, s);
+    ncclResult_t r = api->AllReduce(local_w, local_w, n_weight + bias_floats, ncclFloat, ncclSum, h->comm, s);
+    if (r != ncclSuccess) return nccl_fail(api, r, "ncclAllReduce(gradWeight)");
+    FBF_CUDA(launch_copy_or_add(local_w, grad_weight, (long long)n_weight, accumulate, s));
+  }
+  if (h->comm && grad_bias) {
+    StageTimer t(h, pass, FBFFTCONV_STAGE_BIAS, s);
+    FBF_CUDA(launch_copy_or_add(bias_part, grad_bias, F, accumulate, s));
   }
   return FBFFTCONV_OK;
 }

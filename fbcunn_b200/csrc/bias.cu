@@ -59,7 +59,22 @@ row_sum_kernel(const float* __restrict__ src, float* grad_bias, int batch, long 
   if (threadIdx.x == 0) grad_bias[f] = accumulate ? grad_bias[f] + scale * v : scale * v;
 }
 
+__global__ void __launch_bounds__(256)
+copy_or_add_kernel(const float* __restrict__ src, float* dst, long long n, int accumulate) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    dst[i] = accumulate ? dst[i] + src[i] : src[i];
+}
+
 }  // namespace
+
+cudaError_t launch_copy_or_add(const float* src, float* dst, long long n, int accumulate, cudaStream_t stream) {
+  if (n <= 0) return cudaSuccess;
+  const long long want = (n + 255) / 256;
+  const int blocks = (int)(want < 148 * 8 ? want : 148 * 8);
+  copy_or_add_kernel<<<blocks, 256, 0, stream>>>(src, dst, n, accumulate);
+  count_launch();
+  return cudaGetLastError();
+}
 
 cudaError_t launch_bias_add(float* out, const float* bias, int batch, int planes, int hw,
                             cudaStream_t stream) {

@@ -136,13 +136,23 @@ cudaError_t launch_stream_expand(const float2* x, const float2* y, float2* z, in
 cudaError_t launch_stream_reduce(const float2* x, const float2* y, float2* z, int U, int W, int P, long long xs_u,
                                  long long xs_w, bool conj_x, long long bins, float alpha, cudaStream_t stream) {
   if (P < 1 || P > PMAX || (bins & 1)) return cudaErrorInvalidValue;
-  constexpr int TU = 2;
-  dim3 grid((unsigned)((bins / 2 + THREADS - 1) / THREADS), (U + TU - 1) / TU);
+  const unsigned bin_blocks = (unsigned)((bins / 2 + THREADS - 1) / THREADS);
+  // two rows per block halve the re-reads of Y; with few rows (a small batch shard) one row
+  // per block keeps every SM busy instead
+  const bool pair = (long long)bin_blocks * ((U + 1) / 2) >= 2 * 148;
+  dim3 grid(bin_blocks, pair ? (U + 1) / 2 : U);
   if (grid.y > 65535) return cudaErrorInvalidValue;
-  if (conj_x)
-    stream_reduce_kernel<TU, true><<<grid, THREADS, 0, stream>>>(x, y, z, U, W, P, xs_u, xs_w, bins, alpha);
-  else
-    stream_reduce_kernel<TU, false><<<grid, THREADS, 0, stream>>>(x, y, z, U, W, P, xs_u, xs_w, bins, alpha);
+  if (pair) {
+    if (conj_x)
+      stream_reduce_kernel<2, true><<<grid, THREADS, 0, stream>>>(x, y, z, U, W, P, xs_u, xs_w, bins, alpha);
+    else
+      stream_reduce_kernel<2, false><<<grid, THREADS, 0, stream>>>(x, y, z, U, W, P, xs_u, xs_w, bins, alpha);
+  } else {
+    if (conj_x)
+      stream_reduce_kernel<1, true><<<grid, THREADS, 0, stream>>>(x, y, z, U, W, P, xs_u, xs_w, bins, alpha);
+    else
+      stream_reduce_kernel<1, false><<<grid, THREADS, 0, stream>>>(x, y, z, U, W, P, xs_u, xs_w, bins, alpha);
+  }
   count_launch();
   return cudaGetLastError();
 }

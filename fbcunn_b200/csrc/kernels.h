@@ -49,6 +49,8 @@ cudaError_t launch_bias_add(float* out, const float* bias, int batch, int planes
 cudaError_t launch_bias_grad(const float* grad_out, float* grad_bias, float* scratch, int batch,
                              int planes, int hw, float scale, int accumulate, cudaStream_t stream);
 // dst[r] (=|+=) scale * sum_{i<count} src[r*ld + i*step]
+// dst[i] = src[i], or dst[i] += src[i]
+cudaError_t launch_copy_or_add(const float* src, float* dst, long long n, int accumulate, cudaStream_t stream);
 cudaError_t launch_row_sum(const float* src, float* dst, int rows, int count, long long ld, long long step,
                            float scale, int accumulate, cudaStream_t stream);
 

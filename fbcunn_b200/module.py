@@ -52,7 +52,7 @@ class SpatialConvolutionFBFFT:
 
     def __init__(self, nInputPlane, nOutputPlane, kW, kH, dW=1, dH=1, padLeft=0, padUp=0,
                  memoryReusePolicy=None, numCudaStreams=None, *, device="cuda", accumulate=False,
-                 contraction: str = "auto"):
+                 contraction: str = "auto", allreduce: str = "spectrum"):
         for v in (nInputPlane, nOutputPlane, kW, kH, dW, dH, padLeft, padUp):
             assert _is_number(v), "constructor arguments must be numbers"
         assert memoryReusePolicy is None or isinstance(memoryReusePolicy, (str, list, tuple))
@@ -85,6 +85,10 @@ class SpatialConvolutionFBFFT:
         self._accumulate = bool(accumulate)
         assert contraction in ("auto", "simt", "bin_major")
         self._contraction = contraction
+        # where accGradParameters sums across ranks once a communicator is attached: the
+        # gradWeight spectrum before the inverse transform, or gradWeight itself after it
+        assert allreduce in ("spectrum", "spatial")
+        self._allreduce = allreduce
         shape_w = (self.nOutputPlane, self.nInputPlane, self.kH, self.kW)
         self.weight = torch.empty(shape_w, dtype=torch.float32, device=self.device)
         self.bias = torch.empty(self.nOutputPlane, dtype=torch.float32, device=self.device)
@@ -224,7 +228,8 @@ class SpatialConvolutionFBFFT:
         self.cleanupBuffers()
         flags = (capi.ACCUMULATE_GRADS if self._accumulate else 0) | \
                 (capi.CONTRACT_SIMT if self._contraction == "simt" else 0) | \
-                (capi.BIN_MAJOR_ONLY if self._contraction == "bin_major" else 0)
+                (capi.BIN_MAJOR_ONLY if self._contraction == "bin_major" else 0) | \
+                (capi.ALLREDUCE_SPATIAL if self._allreduce == "spatial" else 0)
         desc = capi.Desc(B, self.nInputPlane, self.nOutputPlane, iH, iW, self.kH, self.kW,
                          self.dH, self.dW, self.padUp, self.padLeft,
                          self.device.index if self.device.index is not None else torch.cuda.current_device(),

@@ -53,7 +53,12 @@ enum {
   FBFFTCONV_CONTRACT_SIMT = 2,
   /* keep the bin-major frequency layout even for layers with <= 4 input planes, which by
    * default use plane-major buffers and a streaming contraction at transform sizes 64/128 */
-  FBFFTCONV_BIN_MAJOR_ONLY = 4
+  FBFFTCONV_BIN_MAJOR_ONLY = 4,
+  /* with a communicator attached, sum gradWeight across ranks after the inverse transform
+   * (F*P*kH*kW floats) instead of summing its spectrum before it (F*P*bins complex
+   * values).  The transform is linear, so both orders give the same gradient; the
+   * default is the frequency-domain sum. */
+  FBFFTCONV_ALLREDUCE_SPATIAL = 8
 };
 
 /* Constructor arguments of nn.SpatialConvolutionFBFFT
