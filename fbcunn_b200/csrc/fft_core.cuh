@@ -61,6 +61,20 @@ FBF_HD void async_copy4(float* smem_dst, const float* gmem_src) {
   *smem_dst = *gmem_src;
 #endif
 }
+// 16-byte variant: both addresses 16-byte aligned.
+FBF_HD void async_copy16(float* smem_dst, const float* gmem_src) {
+#if defined(__CUDA_ARCH__)
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(smem_dst)),
+               "l"(gmem_src)
+               : "memory");
+#else
+  for (int i = 0; i < 4; ++i) smem_dst[i] = gmem_src[i];
+#endif
+}
+// Four floats moved as one 16-byte access.
+struct alignas(16) Quad {
+  float a, b, c, d;
+};
 FBF_HD void async_copy_wait() {
 #if defined(__CUDA_ARCH__)
   asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
@@ -197,9 +211,9 @@ static inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
 
 // Smallest pitch >= n (in float2 units) such that groups of T consecutive planes
 // of neighbouring lines fall on different banks.
-static inline int plane_pitch(int n, int T) {
-  if (T >= 16) return round_up(n, 16);
-  int p = round_up(n, 16) + T;
+constexpr int plane_pitch(int n, int T) {
+  if (T >= 16) return (n + 15) / 16 * 16;
+  int p = (n + 15) / 16 * 16 + T;
   while (p - 16 >= n) p -= 16;
   return p;
 }
@@ -209,7 +223,7 @@ struct FftGeom {
   int he, we;      // forward: extent of the data inside the N x N square (offset included);
                    // inverse: the crop window
   int hh;          // row pairs: rows (j, j + hh) share one complex line
-  int pitch1;      // line pitch of the row buffer
+  int pitch1;      // cooperative: line pitch of the row buffer; thread-per-line: pitch of a staged real plane (floats)
   int pitch2;      // row pitch of the column buffer ("mid")
   int lines1;      // hh * T
   int lines2;      // (N/2 + 1) * T
@@ -225,12 +239,24 @@ static inline bool cooperative(int N) { return N > 32; }
 #endif
 static inline int coop_threads() { return FBF_COOP_THREADS; }
 
-// Thread-per-line kernels (N <= 32): region A = row buffer [x][line1], region B = column
-// buffer [y][kx*T + t]; they alias (a thread takes its whole line into registers before
-// the barrier that precedes the first write of the other region).
+// Thread-per-line kernels (N <= 32): region A = the T real planes as they lie in global
+// memory (pitch1 floats apart), region B = column buffer [y][kx*T + t]; they alias (a thread
+// takes its whole line into registers before the barrier that precedes the first write of the
+// other region).
 // Cooperative kernels (N > 32): region A = one chunk of row lines
 // [line][k1*(N2+1) + n2], region B = column buffer [y or slot][t*(N/2+1) + kx].
-static inline FftGeom make_geom(int N, int T, int he, int we, bool inverse) {
+// Pitch (floats) of one staged real plane of n elements: a multiple of 4 (16-byte copies)
+// with room for the 0..3 floats by which a plane is shifted to share the 16-byte phase of
+// its global address, and an odd number of 16-byte units so that neighbouring planes start
+// in different banks.
+static inline int stage_pitch(int n) {
+  int p = round_up(n + 3, 4);
+  if (((p >> 2) & 1) == 0) p += 4;
+  return p;
+}
+
+// `plane_elems`: elements of one real plane as it lies in global memory.
+static inline FftGeom make_geom(int N, int T, int he, int we, int plane_elems, bool inverse) {
   FftGeom g;
   g.N = N;
   g.T = T;
@@ -241,17 +267,14 @@ static inline FftGeom make_geom(int N, int T, int he, int we, bool inverse) {
   g.lines2 = (N / 2 + 1) * T;
   g.off_a = 0;
   if (!cooperative(N)) {
-    g.pitch1 = g.lines1 | 1;
+    g.pitch1 = stage_pitch(plane_elems);
     g.pitch2 = plane_pitch(g.lines2, T);
     g.chunk = g.lines1;
-    const int bytes_a = (inverse ? 0 : we * g.pitch1 * 8);
-    const int stage = inverse ? T * ((he * we) | 1) * 4 : 0;
-    int bytes_b = he * g.pitch2 * 8;
-    if (stage > bytes_b) bytes_b = stage;
+    const int bytes_a = T * g.pitch1 * 4;
+    const int bytes_b = he * g.pitch2 * 8;
     g.off_b = 0;
     g.smem_bytes = bytes_a > bytes_b ? bytes_a : bytes_b;
-    const int need = g.lines1 > g.lines2 ? g.lines1 : g.lines2;
-    g.threads = round_up(need < 64 ? 64 : need, 32);
+    g.threads = round_up(g.lines2 < 64 ? 64 : g.lines2, 32);
   } else {
     const int n1 = N == 64 ? 8 : 8, n2 = N / n1;
     g.pitch1 = (n1 * (n2 + 1)) | 1;    // = CoopLayout::PITCH1 (odd: neighbouring lines, different banks)
@@ -267,10 +290,10 @@ static inline FftGeom make_geom(int N, int T, int he, int we, bool inverse) {
 }
 
 static inline FftGeom forward_geom(int N, int T, int h, int w, int pad_u, int pad_l) {
-  return make_geom(N, T, h + pad_u, w + pad_l, false);
+  return make_geom(N, T, h + pad_u, w + pad_l, h * w, false);
 }
 static inline FftGeom inverse_geom(int N, int T, int oh, int ow) {
-  return make_geom(N, T, oh, ow, true);
+  return make_geom(N, T, oh, ow, oh * ow, true);
 }
 
 // ---------------------------------------------------------------------------
@@ -304,49 +327,70 @@ struct LineRegs {
 
 // ===========================================================================
 // Thread-per-line kernels, N <= 32.  Block (tile, row): planes inner0 .. inner0+T-1.
+//
+// These kernels are bound by instruction issue, not by arithmetic, so the layout is
+// chosen for cheap addressing: the real planes are staged in shared memory exactly as
+// they lie in global memory (16-byte copies), each plane shifted by the 0..3 floats
+// that give it the 16-byte phase of its global address, and every shared-memory pitch
+// that an unrolled loop walks is a compile-time constant.
 // ===========================================================================
 template <int N, int T>
+struct TileLayout {
+  static constexpr int KX = N / 2 + 1;
+  static constexpr int LINES2 = KX * T;
+  static constexpr int PITCH2 = plane_pitch(LINES2, T);  // row pitch of mid (float2)
+};
+
+// 16-byte phase of a float address, in floats.
+FBF_HD int phase16(const float* ptr) { return (int)((reinterpret_cast<uintptr_t>(ptr) >> 2) & 3); }
+
+template <int N, int T>
 struct Forward {
-  // Phase 0: real planes -> row buffer, rows (j, j+hh) packed as (re, im).
+  using L = TileLayout<N, T>;
+
+  static FBF_HD const float* plane_ptr(const FftParams& p, int row, int inner) {
+    return p.real_in + (row * p.real_row_stride + inner * p.real_inner_stride) * ((long long)p.h * p.w);
+  }
+
+  // Phase 0: real planes -> stage, plane t at stage + t*pitch1 + phase16(plane); warps take planes.
   static FBF_HD void load(const FftParams& p, const FftGeom& g, char* smem, int tid, int nthreads,
                           int row, int inner0) {
-    float2* ra = reinterpret_cast<float2*>(smem + g.off_a);
-    const int per_plane = g.hh * g.we;
-    // split the T planes over `ts` thread groups so that small planes still use the block
-    int ts = 1;
-    while (ts < T && per_plane * ts * 2 <= nthreads) ts *= 2;
-    const int items = per_plane * ts;
-    const long long plane_elems = (long long)p.h * p.w;
-    const float* base = p.real_in + (row * p.real_row_stride + inner0 * p.real_inner_stride) * plane_elems;
-    const long long tstride = p.real_inner_stride * plane_elems;
-    for (int i = tid; i < items; i += nthreads) {
-      const int part = i / per_plane;
-      const int r = i - part * per_plane;
-      const int j = r / g.we;
-      const int xx = r - j * g.we;
-      const int x = xx - p.off_x;
-      const int ya = j - p.off_y, yb = j + g.hh - p.off_y;
-      const bool va = x >= 0 && ya >= 0 && ya < p.h;
-      const bool vb = x >= 0 && yb >= 0 && yb < p.h;
-      const int oa = ya * p.w + x, ob = yb * p.w + x;
-      float* dst = reinterpret_cast<float*>(ra + xx * g.pitch1 + j * T);
-      for (int t = part; t < T; t += ts) {
-        const bool live = inner0 + t < p.n_inner;
-        const float* plane = base + t * tstride;
-        if (live && va) async_copy4(dst + 2 * t, plane + oa); else dst[2 * t] = 0.f;
-        if (live && vb) async_copy4(dst + 2 * t + 1, plane + ob); else dst[2 * t + 1] = 0.f;
-      }
+    float* stage = reinterpret_cast<float*>(smem + g.off_a);
+    const int hw = p.h * p.w;
+    const int warp = tid >> 5, lane = tid & 31, nwarps = nthreads >> 5;
+    for (int t = warp; t < T; t += nwarps) {
+      if (inner0 + t >= p.n_inner) break;
+      const float* src = plane_ptr(p, row, inner0 + t);
+      const int shift = phase16(src);
+      float* dst = stage + t * g.pitch1 + shift;
+      int head = (4 - shift) & 3;
+      if (head > hw) head = hw;
+      const int chunks = (hw - head) >> 2;
+      const int tail0 = head + 4 * chunks;
+      for (int c = lane; c < chunks; c += 32) async_copy16(dst + head + 4 * c, src + head + 4 * c);
+      if (lane < head) async_copy4(dst + lane, src + lane);
+      if (lane < hw - tail0) async_copy4(dst + tail0 + lane, src + tail0 + lane);
     }
     async_copy_wait();
   }
 
-  // Phase 1a: a line into registers.
-  static FBF_HD void row_fetch(const FftGeom& g, const char* smem, int line, LineRegs<N>& regs) {
+  // Phase 1a: rows (j, j+hh) of plane t into registers as (re, im), zero outside the plane.
+  static FBF_HD void row_fetch(const FftParams& p, const FftGeom& g, const char* smem, int line, int row,
+                               int inner0, LineRegs<N>& regs) {
     if (line >= g.lines1) return;
-    const float2* ra = reinterpret_cast<const float2*>(smem + g.off_a);
+    const float* stage = reinterpret_cast<const float*>(smem + g.off_a);
+    const int j = line / T, t = line - j * T;
+    const bool live = inner0 + t < p.n_inner;
+    const float* sp = stage + t * g.pitch1 + phase16(plane_ptr(p, row, inner0 + t));
+    const int ya = j - p.off_y, yb = ya + g.hh;
+    const bool va = live && (unsigned)ya < (unsigned)p.h, vb = live && (unsigned)yb < (unsigned)p.h;
+    const float* pa = sp + ya * p.w - p.off_x;
+    const float* pb = pa + g.hh * p.w;
 #pragma unroll
-    for (int xx = 0; xx < N; ++xx)
-      regs.v[xx] = xx < g.we ? ra[xx * g.pitch1 + line] : make_float2(0.f, 0.f);
+    for (int x = 0; x < N; ++x) {
+      const bool px = (unsigned)(x - p.off_x) < (unsigned)p.w;
+      regs.v[x] = make_float2(va && px ? pa[x] : 0.f, vb && px ? pb[x] : 0.f);
+    }
   }
 
   // Phase 1b: transform along x, split the row pair, write mid[y][kx*T + t].
@@ -355,59 +399,71 @@ struct Forward {
     float2* mid = reinterpret_cast<float2*>(smem + g.off_b);
     const int j = line / T, t = line - j * T;
     const bool has_b = (j + g.hh) < g.he;
+    float2* ma = mid + j * L::PITCH2 + t;
+    float2* mb = ma + g.hh * L::PITCH2;
     fft_inreg<N, false>(regs.v);
 #pragma unroll
     for (int k = 0; k <= N / 2; ++k) {
       float2 a, b;
       untangle_pair(regs.v[k], regs.v[(N - k) % N], a, b);
-      mid[j * g.pitch2 + k * T + t] = a;
-      if (has_b) mid[(j + g.hh) * g.pitch2 + k * T + t] = b;
+      ma[k * T] = a;
+      if (has_b) mb[k * T] = b;
     }
   }
 
   // Phase 2: transform along y for line2 = kx*T + t and write the spectrum.
   static FBF_HD void col_pass(const FftParams& p, const FftGeom& g, char* smem, int line, int row,
                               int inner0) {
-    if (line >= g.lines2) return;
+    if (line >= L::LINES2) return;
     const float2* mid = reinterpret_cast<const float2*>(smem + g.off_b) + line;
     const int kx = line / T, t = line - kx * T;
     const int inner = inner0 + t;
     if (inner >= p.kc) return;
-    const long long bin_stride = p.spec_bin;
-    float2* dst = p.spec + (long long)kx * bin_stride + row * p.spec_row + inner * p.spec_inner;
-    const int pitch = g.pitch2;
     const int he = g.he;
     float2 u[N];
 #pragma unroll
-    for (int y = 0; y < N; ++y) u[y] = y < he ? mid[y * pitch] : make_float2(0.f, 0.f);
+    for (int y = 0; y < N; ++y) u[y] = y < he ? mid[y * L::PITCH2] : make_float2(0.f, 0.f);
     fft_inreg<N, false>(u);
+    float2* dst = p.spec + (long long)kx * p.spec_bin + row * p.spec_row + inner * p.spec_inner;
+    const long long step = (long long)L::KX * p.spec_bin;
 #pragma unroll
-    for (int ky = 0; ky < N; ++ky) dst[(long long)(ky * (N / 2 + 1)) * bin_stride] = u[ky];
+    for (int ky = 0; ky < N; ++ky) {
+      *dst = u[ky];
+      dst += step;
+    }
   }
 };
 
 template <int N, int T>
 struct Inverse {
+  using L = TileLayout<N, T>;
+
+  static FBF_HD float* plane_ptr(const FftParams& p, const FftGeom& g, int row, int inner) {
+    return p.real_out + (row * p.real_row_stride + inner * p.real_inner_stride) * ((long long)g.he * g.we);
+  }
+
   // Phase 1: inverse transform along y of line2 = kx*T + t, keep the crop rows.
   static FBF_HD void col_pass(const FftParams& p, const FftGeom& g, char* smem, int line, int row,
                               int inner0) {
-    if (line >= g.lines2) return;
-    float2* mid = reinterpret_cast<float2*>(smem + g.off_b) + line;
+    if (line >= L::LINES2) return;
     const int kx = line / T, t = line - kx * T;
     const int inner = inner0 + t;
     const bool live = inner < p.n_inner;
-    const long long bin_stride = p.spec_bin;
-    const float2* src = p.spec + (long long)kx * bin_stride + row * p.spec_row + inner * p.spec_inner;
-    const int pitch = g.pitch2;
-    const int y0 = p.off_y, y1 = p.off_y + g.he;
+    const float2* src = p.spec + (long long)kx * p.spec_bin + row * p.spec_row + inner * p.spec_inner;
+    const long long step = (long long)L::KX * p.spec_bin;
     float2 u[N];
 #pragma unroll
-    for (int ky = 0; ky < N; ++ky)
-      u[ky] = live ? src[(long long)(ky * (N / 2 + 1)) * bin_stride] : make_float2(0.f, 0.f);
+    for (int ky = 0; ky < N; ++ky) {
+      u[ky] = live ? *src : make_float2(0.f, 0.f);
+      src += step;
+    }
     fft_inreg<N, true>(u);
+    // row y of the square lands in row y - off_y of mid
+    float2* mid = reinterpret_cast<float2*>(smem + g.off_b) + line - p.off_y * L::PITCH2;
+    const unsigned he = (unsigned)g.he;
 #pragma unroll
     for (int y = 0; y < N; ++y)
-      if (y >= y0 && y < y1) mid[(y - y0) * pitch] = u[y];
+      if ((unsigned)(y - p.off_y) < he) mid[y * L::PITCH2] = u[y];
   }
 
   // Phase 2a: gather the two half spectra of rows (j, j+hh) into one complex line.
@@ -416,8 +472,8 @@ struct Inverse {
     const float2* mid = reinterpret_cast<const float2*>(smem + g.off_b);
     const int j = line / T, t = line - j * T;
     const bool has_b = (j + g.hh) < g.he;
-    const float2* pa = mid + j * g.pitch2 + t;
-    const float2* pb = mid + (j + g.hh) * g.pitch2 + t;
+    const float2* pa = mid + j * L::PITCH2 + t;
+    const float2* pb = pa + g.hh * L::PITCH2;
 #pragma unroll
     for (int k = 0; k <= N / 2; ++k) {
       const float2 a = pa[k * T];
@@ -427,45 +483,57 @@ struct Inverse {
     }
   }
 
-  // Phase 2b: inverse transform along x, stage the crop columns as real rows.
-  static FBF_HD void row_pass(const FftParams& p, const FftGeom& g, char* smem, int line,
-                              LineRegs<N>& regs) {
+  // Phase 2b: inverse transform along x, stage the crop columns as real rows, plane t at
+  // stage + t*pitch1 + phase16(its destination).
+  static FBF_HD void row_pass(const FftParams& p, const FftGeom& g, char* smem, int line, int row,
+                              int inner0, LineRegs<N>& regs) {
     if (line >= g.lines1) return;
-    float* stage = reinterpret_cast<float*>(smem + g.off_b);
+    float* stage = reinterpret_cast<float*>(smem + g.off_a);
     const int j = line / T, t = line - j * T;
     const bool has_b = (j + g.hh) < g.he;
-    const int plane_pitch_f = (g.he * g.we) | 1;
-    float* sa = stage + t * plane_pitch_f + j * g.we;
-    float* sb = stage + t * plane_pitch_f + (j + g.hh) * g.we;
-    const int x0 = p.off_x, x1 = p.off_x + g.we;
+    float* sa = stage + t * g.pitch1 + phase16(plane_ptr(p, g, row, inner0 + t)) + j * g.we - p.off_x;
+    float* sb = sa + g.hh * g.we;
+    const unsigned we = (unsigned)g.we;
     fft_inreg<N, true>(regs.v);
 #pragma unroll
     for (int x = 0; x < N; ++x) {
-      if (x >= x0 && x < x1) {
-        sa[x - x0] = regs.v[x].x;
-        if (has_b) sb[x - x0] = regs.v[x].y;
+      if ((unsigned)(x - p.off_x) < we) {
+        sa[x] = regs.v[x].x;
+        if (has_b) sb[x] = regs.v[x].y;
       }
     }
   }
 
-  // Phase 3: staged planes -> global, bias added per plane.
+  static FBF_HD float finish(const FftParams& p, float v, float bias, const float* dst) {
+    return p.accumulate ? *dst + (v + bias) : v + bias;
+  }
+
+  // Phase 3: staged planes -> global in 16-byte pieces, bias added per plane; warps take planes.
   static FBF_HD void store(const FftParams& p, const FftGeom& g, const char* smem, int tid,
                            int nthreads, int row, int inner0) {
-    const float* stage = reinterpret_cast<const float*>(smem + g.off_b);
+    const float* stage = reinterpret_cast<const float*>(smem + g.off_a);
     const int per_plane = g.he * g.we;
-    const int plane_pitch_f = per_plane | 1;
-    float* base = p.real_out + (row * p.real_row_stride + inner0 * p.real_inner_stride) * (long long)per_plane;
-    const long long tstride = p.real_inner_stride * (long long)per_plane;
-    for (int t = 0; t < T; ++t) {
+    const int warp = tid >> 5, lane = tid & 31, nwarps = nthreads >> 5;
+    for (int t = warp; t < T; t += nwarps) {
       const int inner = inner0 + t;
       if (inner >= p.n_inner) break;
       const float bias = p.bias ? p.bias[inner] : 0.f;
-      const float* src = stage + t * plane_pitch_f;
-      float* dst = base + t * tstride;
-      for (int r = tid; r < per_plane; r += nthreads) {
-        const float v = src[r] + bias;
-        dst[r] = p.accumulate ? (dst[r] + v) : v;
+      float* dst = plane_ptr(p, g, row, inner);
+      const int shift = phase16(dst);
+      const float* src = stage + t * g.pitch1 + shift;
+      int head = (4 - shift) & 3;
+      if (head > per_plane) head = per_plane;
+      const int chunks = (per_plane - head) >> 2;
+      const int tail0 = head + 4 * chunks;
+      for (int c = lane; c < chunks; c += 32) {
+        const Quad s4 = *reinterpret_cast<const Quad*>(src + head + 4 * c);
+        float* d4 = dst + head + 4 * c;
+        const Quad q{finish(p, s4.a, bias, d4), finish(p, s4.b, bias, d4 + 1), finish(p, s4.c, bias, d4 + 2),
+                     finish(p, s4.d, bias, d4 + 3)};
+        *reinterpret_cast<Quad*>(d4) = q;
       }
+      if (lane < head) dst[lane] = finish(p, src[lane], bias, dst + lane);
+      if (lane < per_plane - tail0) dst[tail0 + lane] = finish(p, src[tail0 + lane], bias, dst + tail0 + lane);
     }
   }
 };

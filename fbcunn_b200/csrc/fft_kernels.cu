@@ -33,8 +33,8 @@ fft2d_forward_kernel(const __grid_constant__ FftParams p, const __grid_constant_
   Forward<N, T>::load(p, g, smem, tid, blockDim.x, row, inner0);
   __syncthreads();
   LineRegs<N> regs;
-  Forward<N, T>::row_fetch(g, smem, tid, regs);
-  if (N <= 32) __syncthreads();  // the column buffer aliases the row buffer
+  Forward<N, T>::row_fetch(p, g, smem, tid, row, inner0, regs);
+  __syncthreads();  // the column buffer aliases the staged planes
   Forward<N, T>::row_pass(g, smem, tid, regs);
   __syncthreads();
   Forward<N, T>::col_pass(p, g, smem, tid, row, inner0);
@@ -52,7 +52,7 @@ fft2d_inverse_kernel(const __grid_constant__ FftParams p, const __grid_constant_
   LineRegs<N> regs;
   Inverse<N, T>::row_fetch(g, smem, tid, regs);
   __syncthreads();  // the staged output aliases the column buffer
-  Inverse<N, T>::row_pass(p, g, smem, tid, regs);
+  Inverse<N, T>::row_pass(p, g, smem, tid, row, inner0, regs);
   __syncthreads();
   Inverse<N, T>::store(p, g, smem, tid, blockDim.x, row, inner0);
 }

@@ -59,7 +59,7 @@ void run_forward(const FftParams& p) {
         for (int tid = 0; tid < g.threads; ++tid)
           Forward<N, T>::load(p, g, smem.data(), tid, g.threads, row, inner0);
         for (int tid = 0; tid < g.threads; ++tid)
-          Forward<N, T>::row_fetch(g, smem.data(), tid, regs[tid]);
+          Forward<N, T>::row_fetch(p, g, smem.data(), tid, row, inner0, regs[tid]);
         std::memset(smem.data(), 0xFF, smem.size());  // aliasing: the row buffer is dead now
         for (int tid = 0; tid < g.threads; ++tid)
           Forward<N, T>::row_pass(g, smem.data(), tid, regs[tid]);
@@ -100,7 +100,7 @@ void run_inverse(const FftParams& p, int oh, int ow) {
           Inverse<N, T>::row_fetch(g, smem.data(), tid, regs[tid]);
         std::memset(smem.data() + g.off_b, 0xFF, smem.size() - g.off_b);  // mid is dead now
         for (int tid = 0; tid < g.threads; ++tid)
-          Inverse<N, T>::row_pass(p, g, smem.data(), tid, regs[tid]);
+          Inverse<N, T>::row_pass(p, g, smem.data(), tid, row, inner0, regs[tid]);
         for (int tid = 0; tid < g.threads; ++tid)
           Inverse<N, T>::store(p, g, smem.data(), tid, g.threads, row, inner0);
       }
