@@ -223,6 +223,7 @@ struct FftGeom {
   int he, we;      // forward: extent of the data inside the N x N square (offset included);
                    // inverse: the crop window
   int hh;          // row pairs: rows (j, j + hh) share one complex line
+  int hh_magic;    // ceil(2^16 / hh): line / hh == (line * hh_magic) >> 16 for line < 512, hh <= 64
   int pitch1;      // cooperative: line pitch of the row buffer; thread-per-line: pitch of a staged real plane (floats)
   int pitch2;      // row pitch of the column buffer ("mid")
   int lines1;      // hh * T
@@ -237,6 +238,7 @@ static inline bool cooperative(int N) { return N > 32; }
 #ifndef FBF_COOP_THREADS
 #define FBF_COOP_THREADS 256
 #endif
+static_assert(FBF_COOP_THREADS % 32 == 0, "whole warps, and a multiple of every N2");
 static inline int coop_threads() { return FBF_COOP_THREADS; }
 
 // Thread-per-line kernels (N <= 32): region A = the T real planes as they lie in global
@@ -263,6 +265,7 @@ static inline FftGeom make_geom(int N, int T, int he, int we, int plane_elems, b
   g.he = he;
   g.we = we;
   g.hh = (he + 1) / 2;
+  g.hh_magic = (65536 + g.hh - 1) / g.hh;
   g.lines1 = g.hh * T;
   g.lines2 = (N / 2 + 1) * T;
   g.off_a = 0;
@@ -341,6 +344,10 @@ struct TileLayout {
   static constexpr int PITCH2 = plane_pitch(LINES2, T);  // row pitch of mid (float2)
 };
 
+// log2 of the lanes that copy one plane of n floats together (3 floats of head and tail
+// need at most 3 lanes).
+FBF_HD int copy_group_shift(int n) { return n <= 64 ? 3 : n <= 192 ? 4 : 5; }
+
 // 16-byte phase of a float address, in floats.
 FBF_HD int phase16(const float* ptr) { return (int)((reinterpret_cast<uintptr_t>(ptr) >> 2) & 3); }
 
@@ -357,8 +364,11 @@ struct Forward {
                           int row, int inner0) {
     float* stage = reinterpret_cast<float*>(smem + g.off_a);
     const int hw = p.h * p.w;
-    const int warp = tid >> 5, lane = tid & 31, nwarps = nthreads >> 5;
-    for (int t = warp; t < T; t += nwarps) {
+    // small planes: a warp splits into groups of 8 or 16 lanes that take one plane each
+    const int lp_shift = copy_group_shift(hw);
+    const int lanes = 1 << lp_shift, lane = tid & (lanes - 1);
+    const int group = tid >> lp_shift, ngroups = nthreads >> lp_shift;
+    for (int t = group; t < T; t += ngroups) {
       if (inner0 + t >= p.n_inner) break;
       const float* src = plane_ptr(p, row, inner0 + t);
       const int shift = phase16(src);
@@ -367,7 +377,7 @@ struct Forward {
       if (head > hw) head = hw;
       const int chunks = (hw - head) >> 2;
       const int tail0 = head + 4 * chunks;
-      for (int c = lane; c < chunks; c += 32) async_copy16(dst + head + 4 * c, src + head + 4 * c);
+      for (int c = lane; c < chunks; c += lanes) async_copy16(dst + head + 4 * c, src + head + 4 * c);
       if (lane < head) async_copy4(dst + lane, src + lane);
       if (lane < hw - tail0) async_copy4(dst + tail0 + lane, src + tail0 + lane);
     }
@@ -424,13 +434,11 @@ struct Forward {
 #pragma unroll
     for (int y = 0; y < N; ++y) u[y] = y < he ? mid[y * L::PITCH2] : make_float2(0.f, 0.f);
     fft_inreg<N, false>(u);
-    float2* dst = p.spec + (long long)kx * p.spec_bin + row * p.spec_row + inner * p.spec_inner;
-    const long long step = (long long)L::KX * p.spec_bin;
+    // 32-bit offsets inside the row: the launcher refuses spectra of 2^31 elements or more
+    float2* dst = p.spec + ((long long)kx * p.spec_bin + row * p.spec_row + inner * p.spec_inner);
+    const int step = L::KX * (int)p.spec_bin;
 #pragma unroll
-    for (int ky = 0; ky < N; ++ky) {
-      *dst = u[ky];
-      dst += step;
-    }
+    for (int ky = 0; ky < N; ++ky) dst[ky * step] = u[ky];
   }
 };
 
@@ -449,14 +457,11 @@ struct Inverse {
     const int kx = line / T, t = line - kx * T;
     const int inner = inner0 + t;
     const bool live = inner < p.n_inner;
-    const float2* src = p.spec + (long long)kx * p.spec_bin + row * p.spec_row + inner * p.spec_inner;
-    const long long step = (long long)L::KX * p.spec_bin;
+    const float2* src = p.spec + ((long long)kx * p.spec_bin + row * p.spec_row + inner * p.spec_inner);
+    const int step = L::KX * (int)p.spec_bin;
     float2 u[N];
 #pragma unroll
-    for (int ky = 0; ky < N; ++ky) {
-      u[ky] = live ? *src : make_float2(0.f, 0.f);
-      src += step;
-    }
+    for (int ky = 0; ky < N; ++ky) u[ky] = live ? src[ky * step] : make_float2(0.f, 0.f);
     fft_inreg<N, true>(u);
     // row y of the square lands in row y - off_y of mid
     float2* mid = reinterpret_cast<float2*>(smem + g.off_b) + line - p.off_y * L::PITCH2;
@@ -513,8 +518,10 @@ struct Inverse {
                            int nthreads, int row, int inner0) {
     const float* stage = reinterpret_cast<const float*>(smem + g.off_a);
     const int per_plane = g.he * g.we;
-    const int warp = tid >> 5, lane = tid & 31, nwarps = nthreads >> 5;
-    for (int t = warp; t < T; t += nwarps) {
+    const int lp_shift = copy_group_shift(per_plane);
+    const int lanes = 1 << lp_shift, lane = tid & (lanes - 1);
+    const int group = tid >> lp_shift, ngroups = nthreads >> lp_shift;
+    for (int t = group; t < T; t += ngroups) {
       const int inner = inner0 + t;
       if (inner >= p.n_inner) break;
       const float bias = p.bias ? p.bias[inner] : 0.f;
@@ -525,7 +532,7 @@ struct Inverse {
       if (head > per_plane) head = per_plane;
       const int chunks = (per_plane - head) >> 2;
       const int tail0 = head + 4 * chunks;
-      for (int c = lane; c < chunks; c += 32) {
+      for (int c = lane; c < chunks; c += lanes) {
         const Quad s4 = *reinterpret_cast<const Quad*>(src + head + 4 * c);
         float* d4 = dst + head + 4 * c;
         const Quad q{finish(p, s4.a, bias, d4), finish(p, s4.b, bias, d4 + 1), finish(p, s4.c, bias, d4 + 2),
@@ -559,6 +566,18 @@ FBF_HD int coop_residue_of_lane(int p) {
   return p == 0 ? 0 : p == 1 ? 4 : p == 2 ? 1 : p == 3 ? 7 : p == 4 ? 2 : p == 5 ? 6 : p == 6 ? 3 : 5;
 }
 
+// line = t * hh + j of a tile of T planes, without an integer division.
+template <int T>
+FBF_HD void coop_split_line(const FftGeom& g, int line, int& t, int& j) {
+  if (T == 1) {
+    t = 0;
+    j = line;
+  } else {
+    t = (line * g.hh_magic) >> 16;
+    j = line - t * g.hh;
+  }
+}
+
 template <int N, int T>
 struct CoopForward {
   using L = CoopLayout<N, T>;
@@ -576,7 +595,8 @@ struct CoopForward {
     if (item >= nl * N2) return;
     const int ll = item / N2, n2 = item - ll * N2;
     const int line = line0 + ll;
-    const int t = line / g.hh, j = line - t * g.hh;
+    int t, j;
+    coop_split_line<T>(g, line, t, j);
     const bool live = inner0 + t < p.n_inner;
     const float* plane = base + t * tstride;
     const int ya = j - p.off_y, yb = j + g.hh - p.off_y;
@@ -597,7 +617,7 @@ struct CoopForward {
     r.n2 = n2;
   }
 
-  static FBF_HD void row_transform(float2* rb, RowLoad& r) {
+  static FBF_HD void row_transform(float2* rb, RowLoad& r, const float2 (&tw)[N1]) {
     if (r.slot < 0) return;
 #ifdef FBF_EXP_NOFFT
     {
@@ -611,8 +631,7 @@ struct CoopForward {
     float2* dst = rb + r.slot;
     dst[0] = r.v[0];
 #pragma unroll
-    for (int k1 = 1; k1 < N1; ++k1)
-      dst[k1 * (N2 + 1)] = cmul(r.v[k1], tw128_runtime<false>(r.n2 * k1 * (128 / N)));
+    for (int k1 = 1; k1 < N1; ++k1) dst[k1 * (N2 + 1)] = cmul(r.v[k1], tw[k1]);
   }
 
   // Row step 1 for lines [line0, line0 + nl): straight from global memory (N2
@@ -624,12 +643,16 @@ struct CoopForward {
     const long long plane_elems = (long long)p.h * p.w;
     const float* base = p.real_in + (row * p.real_row_stride + inner0 * p.real_inner_stride) * plane_elems;
     const long long tstride = p.real_inner_stride * plane_elems;
+    // the block size is a multiple of N2, so a thread meets the same n2 in all its items
+    float2 tw[N1];
+#pragma unroll
+    for (int k1 = 0; k1 < N1; ++k1) tw[k1] = tw128_runtime<false>((tid % N2) * k1 * (128 / N));
     for (int item = tid; item < nl * N2; item += 2 * nthreads) {
       RowLoad r0, r1;
       row_fetch(p, g, base, tstride, inner0, line0, nl, item, r0);
       row_fetch(p, g, base, tstride, inner0, line0, nl, item + nthreads, r1);
-      row_transform(rb, r0);
-      row_transform(rb, r1);
+      row_transform(rb, r0, tw);
+      row_transform(rb, r1, tw);
     }
   }
 
@@ -655,7 +678,8 @@ struct CoopForward {
     float2* mid = reinterpret_cast<float2*>(smem + g.off_b);
     const int ll = item / N1, k1 = coop_residue_of_lane(item % N1);
     const int line = line0 + ll;
-    const int t = line / g.hh, j = line - t * g.hh;
+    int t, j;
+    coop_split_line<T>(g, line, t, j);
     const bool has_b = (j + g.hh) < g.he;
     float2* ma = mid + j * L::PITCH2 + t * KX;
     float2* mb = mid + (j + g.hh) * L::PITCH2 + t * KX;
@@ -708,10 +732,15 @@ struct CoopForward {
   }
 
   // Column step 2: item (col, k1) reads rows {N2*k1 + n2} and writes bins ky = k1 + N1*k2.
+  // PM: the spectrum is plane-major (bins contiguous), every stride a compile-time constant;
+  // otherwise offsets are 32-bit (the launcher refuses spectra of 2^31 elements or more).
+  template <bool PM>
   static FBF_HD void col_step2(const FftParams& p, const FftGeom& g, const char* smem, int tid,
                                int nthreads, int row, int inner0) {
     const float2* mid = reinterpret_cast<const float2*>(smem + g.off_b);
-    const long long bin_stride = p.spec_bin;
+    const int bin_stride = PM ? 1 : (int)p.spec_bin;
+    const int inner_stride = PM ? N * KX : (int)p.spec_inner;
+    float2* base = p.spec + row * p.spec_row;
     for (int item = tid; item < L::COLS * N1; item += nthreads) {
       // neighbouring lanes take the T planes of one bin, so that their 8-byte stores share a line
       const int k1 = item / L::COLS, ci = item - k1 * L::COLS;
@@ -724,8 +753,8 @@ struct CoopForward {
 #pragma unroll
       for (int n2 = 0; n2 < N2; ++n2) u[n2] = c[n2 * L::PITCH2];
       fft_inreg<N2, false>(u);
-      float2* dst = p.spec + ((long long)k1 * KX + kx) * bin_stride + row * p.spec_row + inner * p.spec_inner;
-      const long long step = (long long)(N1 * KX) * bin_stride;
+      float2* dst = base + ((k1 * KX + kx) * bin_stride + inner * inner_stride);
+      const int step = (N1 * KX) * bin_stride;
 #pragma unroll
       for (int k2 = 0; k2 < N2; ++k2) dst[k2 * step] = u[k2];
     }
@@ -743,8 +772,8 @@ struct CoopInverse {
     int n2;
   };
 
-  static FBF_HD void col_fetch(const FftParams& p, long long bin_stride, const float2* base, int inner0,
-                               int item, ColLoad& r) {
+  template <bool PM>
+  static FBF_HD void col_fetch(const FftParams& p, const float2* base, int inner0, int item, ColLoad& r) {
     r.col = -1;
     if (item >= L::COLS * N2) return;
     // neighbouring lanes take the T planes of one bin: their 8-byte loads share a line
@@ -752,8 +781,10 @@ struct CoopInverse {
     const int kx = ci / T, t = ci - kx * T;
     const int col = t * KX + kx;
     const bool live = inner0 + t < p.n_inner;
-    const float2* src = base + ((long long)n2 * KX + kx) * bin_stride + t * p.spec_inner;
-    const long long step = (long long)(N2 * KX) * bin_stride;
+    const int bin_stride = PM ? 1 : (int)p.spec_bin;
+    const int inner_stride = PM ? N * KX : (int)p.spec_inner;
+    const float2* src = base + ((n2 * KX + kx) * bin_stride + t * inner_stride);
+    const int step = (N2 * KX) * bin_stride;
 #pragma unroll
     for (int n1 = 0; n1 < N1; ++n1) r.v[n1] = live ? src[n1 * step] : make_float2(0.f, 0.f);
     r.col = col;
@@ -773,15 +804,16 @@ struct CoopInverse {
   // Column step 1: bins of column (t, kx) from global memory (two items in flight per
   // thread), N1-point inverse transform, twiddle, written to rows k1 + N1*n2 of mid so
   // that step 2 can run in place.
+  // PM: plane-major spectrum, compile-time strides; otherwise 32-bit offsets (see CoopForward::col_step2).
+  template <bool PM>
   static FBF_HD void col_step1(const FftParams& p, const FftGeom& g, char* smem, int tid, int nthreads,
                                int row, int inner0) {
     float2* mid = reinterpret_cast<float2*>(smem + g.off_b);
-    const long long bin_stride = p.spec_bin;
-    const float2* base = p.spec + row * p.spec_row + inner0 * p.spec_inner;
+    const float2* base = p.spec + (row * p.spec_row + inner0 * p.spec_inner);
     for (int item = tid; item < L::COLS * N2; item += 2 * nthreads) {
       ColLoad r0, r1;
-      col_fetch(p, bin_stride, base, inner0, item, r0);
-      col_fetch(p, bin_stride, base, inner0, item + nthreads, r1);
+      col_fetch<PM>(p, base, inner0, item, r0);
+      col_fetch<PM>(p, base, inner0, item + nthreads, r1);
       col_transform(mid, r0);
       col_transform(mid, r1);
     }
@@ -809,10 +841,15 @@ struct CoopInverse {
                                int line0, int nl) {
     float2* rb = reinterpret_cast<float2*>(smem + g.off_a);
     const float2* mid = reinterpret_cast<const float2*>(smem + g.off_b);
+    // the block size is a multiple of N2, so a thread meets the same n2 in all its items
+    float2 tw[N1];
+#pragma unroll
+    for (int k1 = 0; k1 < N1; ++k1) tw[k1] = tw128_runtime<true>((tid % N2) * k1 * (128 / N));
     for (int item = tid; item < nl * N2; item += nthreads) {
       const int ll = item / N2, n2 = item - ll * N2;
       const int line = line0 + ll;
-      const int t = line / g.hh, j = line - t * g.hh;
+      int t, j;
+    coop_split_line<T>(g, line, t, j);
       const bool has_b = (j + g.hh) < g.he;
       const float2* pa = mid + (p.off_y + j) * L::PITCH2 + t * KX;
       const float2* pb = pa + g.hh * L::PITCH2;
@@ -829,8 +866,7 @@ struct CoopInverse {
       float2* dst = rb + ll * L::PITCH1 + n2;
       dst[0] = v[0];
 #pragma unroll
-      for (int k1 = 1; k1 < N1; ++k1)
-        dst[k1 * (N2 + 1)] = cmul(v[k1], tw128_runtime<true>(n2 * k1 * (128 / N)));
+      for (int k1 = 1; k1 < N1; ++k1) dst[k1 * (N2 + 1)] = cmul(v[k1], tw[k1]);
     }
   }
 
@@ -846,7 +882,8 @@ struct CoopInverse {
     for (int item = tid; item < nl * N1; item += nthreads) {
       const int ll = item / N1, k1 = item - ll * N1;
       const int line = line0 + ll;
-      const int t = line / g.hh, j = line - t * g.hh;
+      int t, j;
+    coop_split_line<T>(g, line, t, j);
       const int inner = inner0 + t;
       if (inner >= p.n_inner) continue;
       const bool has_b = (j + g.hh) < g.he;

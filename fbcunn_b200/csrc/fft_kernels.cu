@@ -128,7 +128,10 @@ fft2d_forward_coop_kernel(const __grid_constant__ FftParams p, const __grid_cons
   CoopForward<N, T>::col_step1(g, smem, tid, nth);
   __syncthreads();
   FBF_PHASE_MARK(2);
-  CoopForward<N, T>::col_step2(p, g, smem, tid, nth, row, inner0);
+  if (p.spec_bin == 1 && p.spec_inner == (N / 2 + 1) * N)
+    CoopForward<N, T>::template col_step2<true>(p, g, smem, tid, nth, row, inner0);
+  else
+    CoopForward<N, T>::template col_step2<false>(p, g, smem, tid, nth, row, inner0);
   FBF_PHASE_MARK(3);
   __syncthreads();  // the buffers are reused by the next tile
   }
@@ -155,7 +158,10 @@ fft2d_inverse_coop_kernel(const __grid_constant__ FftParams p, const __grid_cons
     }
   }
   FBF_PHASE_BEGIN();
-  CoopInverse<N, T>::col_step1(p, g, smem, tid, nth, row, inner0);
+  if (p.spec_bin == 1 && p.spec_inner == (N / 2 + 1) * N)
+    CoopInverse<N, T>::template col_step1<true>(p, g, smem, tid, nth, row, inner0);
+  else
+    CoopInverse<N, T>::template col_step1<false>(p, g, smem, tid, nth, row, inner0);
   __syncthreads();
   FBF_PHASE_MARK(8);
   CoopInverse<N, T>::col_step2(g, smem, tid, nth);
@@ -296,15 +302,21 @@ int pick_inverse_tile(int N, int oh, int ow) {
   return pick_tile(N, [&](int T) { return inverse_geom(N, T, oh, ow); });
 }
 
+// The kernels address the spectrum with 32-bit element offsets.
+bool spectrum_fits(const FftParams& p, int N) {
+  const long long bins = (long long)(N / 2 + 1) * N;
+  return bins * p.n_rows * p.kc < (1LL << 31);
+}
+
 cudaError_t launch_forward(const FftParams& p, int N, cudaStream_t stream) {
   const int T = pick_forward_tile(N, p.h, p.w, p.off_y, p.off_x);
-  if (T == 0 || p.n_rows > 65535) return cudaErrorInvalidConfiguration;
+  if (T == 0 || p.n_rows > 65535 || !spectrum_fits(p, N)) return cudaErrorInvalidConfiguration;
   return dispatch(false, p, N, T, stream);
 }
 
 cudaError_t launch_inverse(const FftParams& p, int N, cudaStream_t stream) {
   const int T = pick_inverse_tile(N, p.h, p.w);
-  if (T == 0 || p.n_rows > 65535) return cudaErrorInvalidConfiguration;
+  if (T == 0 || p.n_rows > 65535 || !spectrum_fits(p, N)) return cudaErrorInvalidConfiguration;
   return dispatch(true, p, N, T, stream);
 }
 

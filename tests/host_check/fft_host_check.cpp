@@ -54,7 +54,10 @@ void run_forward(const FftParams& p) {
         }
         for (int tid = 0; tid < nth; ++tid) CoopForward<N, T>::col_step1(g, smem.data(), tid, nth);
         for (int tid = 0; tid < nth; ++tid)
-          CoopForward<N, T>::col_step2(p, g, smem.data(), tid, nth, row, inner0);
+          if (p.spec_bin == 1 && p.spec_inner == (N / 2 + 1) * N)
+            CoopForward<N, T>::template col_step2<true>(p, g, smem.data(), tid, nth, row, inner0);
+          else
+            CoopForward<N, T>::template col_step2<false>(p, g, smem.data(), tid, nth, row, inner0);
       } else {
         for (int tid = 0; tid < g.threads; ++tid)
           Forward<N, T>::load(p, g, smem.data(), tid, g.threads, row, inner0);
@@ -83,7 +86,10 @@ void run_inverse(const FftParams& p, int oh, int ow) {
       if constexpr (N > 32) {
         const int nth = g.threads;
         for (int tid = 0; tid < nth; ++tid)
-          CoopInverse<N, T>::col_step1(p, g, smem.data(), tid, nth, row, inner0);
+          if (p.spec_bin == 1 && p.spec_inner == (N / 2 + 1) * N)
+            CoopInverse<N, T>::template col_step1<true>(p, g, smem.data(), tid, nth, row, inner0);
+          else
+            CoopInverse<N, T>::template col_step1<false>(p, g, smem.data(), tid, nth, row, inner0);
         for (int tid = 0; tid < nth; ++tid) CoopInverse<N, T>::col_step2(g, smem.data(), tid, nth);
         for (int line0 = 0; line0 < g.lines1; line0 += g.chunk) {
           const int nl = std::min(g.chunk, g.lines1 - line0);
