@@ -183,6 +183,28 @@ struct TcParams {
   float s_b2_re, s_b2_im;  // sb, sa
 };
 
+// One accumulator block -- 32 rows (one per lane) x 32 floats in registers -- to global memory
+// through a 4 KB shared staging tile, so that a store instruction writes four 128-byte row
+// segments instead of 32 scattered 16-byte pieces.  Chunks are XOR-swizzled by the row:
+// both the row-per-lane writes and the row-segment reads are free of bank conflicts.
+// `c_block` = C + element (first row, first complex column) of the block.
+__device__ __forceinline__ void store_block_coalesced(char* stage, const float (&v)[32], float alpha, int lane,
+                                                      float2* c_block, int ldc, int rows_valid, int cols_valid) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+    *reinterpret_cast<float4*>(stage + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+        make_float4(alpha * v[4 * j], alpha * v[4 * j + 1], alpha * v[4 * j + 2], alpha * v[4 * j + 3]);
+  __syncwarp();
+  const int ch = lane & 7, rsub = lane >> 3;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r = i * 4 + rsub;
+    const float4 x = *reinterpret_cast<const float4*>(stage + r * 128 + ((ch ^ (r & 7)) << 4));
+    if (r < rows_valid && ch * 2 < cols_valid) *reinterpret_cast<float4*>(c_block + (long long)r * ldc + ch * 2) = x;
+  }
+  __syncwarp();
+}
+
 __global__ void __launch_bounds__(THREADS, 1)
 contract_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                    const __grid_constant__ TcParams p) {
@@ -330,22 +352,15 @@ contract_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       const int quarter = warp & 3;
       const int share = (warp - 2) >> 2;
       constexpr int kColBlocks = UMMA_N / 32, kShares = CONVERTER_WARPS / 4;
-      const int row = m0 + quarter * 32 + lane;
-      float2* crow = p.c + ((long long)bin * p.m + row) * p.ldc + n0;
+      const int row0 = m0 + quarter * 32;
+      float2* cblock = p.c + ((long long)bin * p.m + row0) * p.ldc + n0;
+      // every load has landed and every MMA has read its operands: the raw stages are free
+      char* stage = raw + (warp - 2) * 4096;
 #pragma unroll 1
       for (int cb = share * (kColBlocks / kShares); cb < (share + 1) * (kColBlocks / kShares); ++cb) {
         float v[32];
         tmem_load_32cols(tmem_base + (uint32_t(quarter * 32) << 16) + cb * 32, v);
-        if (row < p.m) {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const int ncol = n0 + cb * 16 + j * 2;  // complex column of this float4
-            if (ncol < p.ldc)
-              *reinterpret_cast<float4*>(crow + cb * 16 + j * 2) =
-                  make_float4(p.alpha * v[4 * j], p.alpha * v[4 * j + 1], p.alpha * v[4 * j + 2],
-                              p.alpha * v[4 * j + 3]);
-          }
-        }
+        store_block_coalesced(stage, v, p.alpha, lane, cblock + cb * 16, p.ldc, p.m - row0, p.ldc - (n0 + cb * 16));
       }
     }
   }
