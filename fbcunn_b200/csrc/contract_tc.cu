@@ -56,6 +56,8 @@ constexpr int SMEM_TILES = CONV_STAGES * CONV_STAGE_BYTES + RAW_STAGES * RAW_STA
 constexpr int SMEM_BYTES = SMEM_TILES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 
 constexpr uint32_t kSpinLimit = 1u << 21;  // polls of ~0.1 us each: a fraction of a second
+constexpr uint32_t kWaitHintNs = 2000;     // one suspended wait
+constexpr uint32_t kWaitLimit = 1u << 18;  // suspended waits before giving up: about half a second
 
 __device__ int g_tc_error = 0;  // sticky: first non-zero code of any block
 
@@ -84,13 +86,26 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// One bounded hardware wait: the thread is suspended until the phase completes or about
+// `hint_ns` have passed, whichever comes first (no issue slots are spent meanwhile).
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
 // Bounded wait.  Returns false (and raises the block's abort flag) on a time-out or
 // when another role has already given up.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code) {
-  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
-    if (mbar_test(bar, parity)) return true;
+  if (mbar_test(bar, parity)) return true;
+  for (uint32_t spin = 0; spin < kWaitLimit; ++spin) {
+    if (mbar_try_wait(bar, parity, kWaitHintNs)) return true;
     if (*abort_flag) return false;
-    if (spin > 64) __nanosleep(20);
   }
   *abort_flag = code;
   atomicCAS(&g_tc_error, 0, code);
