@@ -166,6 +166,29 @@ __device__ __forceinline__ void tmem_load_32cols(uint32_t taddr, float (&v)[32])
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+__device__ __forceinline__ void tmem_load_16cols_nowait(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+// 16 complex values of one accumulator row whose real parts sit in columns [re_col, re_col+16)
+// and imaginary parts in [im_col, im_col+16): interleaved (re, im) as they lie in C.
+__device__ __forceinline__ void tmem_load_16complex(uint32_t re_addr, uint32_t im_addr, float (&v)[32]) {
+  uint32_t re[16], im[16];
+  tmem_load_16cols_nowait(re_addr, re);
+  tmem_load_16cols_nowait(im_addr, im);
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    v[2 * i] = __uint_as_float(re[i]);
+    v[2 * i + 1] = __uint_as_float(im[i]);
+  }
+}
+
 // K-major operand tile with 128-byte rows, 128-byte swizzle, 8-row groups 1024 bytes
 // apart: start address, LBO = 1, SBO = 64 (both in 16-byte units), version 1, layout 2.
 __device__ __forceinline__ uint64_t operand_desc(uint32_t smem_addr) {
