@@ -182,7 +182,7 @@ def run_reference_arm(args):
     return 0
 
 
-def workload_config(name, L, gpus, allreduce="spectrum"):
+def workload_config(name, L, gpus, allreduce="spectrum", reuse="none"):
     B, P, F, iH, iW, kH, kW, pH, pW, _ = L
     return {
         "workload": f"{name}: batch {B} x {P} planes x {iH}x{iW}, {F} filters {kH}x{kW}, pad {pH}, stride 1, "
@@ -191,6 +191,7 @@ def workload_config(name, L, gpus, allreduce="spectrum"):
         + ("gradWeight spectrum" if allreduce == "spectrum" else "spatial gradWeight") + " all-reduced (NCCL)"
         if gpus > 1 else "single GPU",
         "l2": "per-step working set exceeds the 126 MB L2; per-pass rows in `layers` are timed after an L2 flush",
+        "memory_reuse": reuse,
     }
 
 
@@ -259,7 +260,7 @@ def gen(torch, shape, seed, kind="normal", bound=1.0):
 class LayerRun:
     """Device tensors and a native handle for one layer at a local batch."""
 
-    def __init__(self, torch, name, L, local_batch, rank, comm=None, allreduce="spectrum"):
+    def __init__(self, torch, name, L, local_batch, rank, comm=None, allreduce="spectrum", reuse="none"):
         from fbcunn_b200 import SpatialConvolutionFBFFT
         self.torch, self.name, self.L, self.B = torch, name, L, local_batch
         _, P, F, iH, iW, kH, kW, pH, pW, has_bias = L
@@ -268,7 +269,7 @@ class LayerRun:
         bound = 1.0 / (kH * kW * P) ** 0.5
         self.x = gen(torch, (local_batch, P, iH, iW), 1000 * cfg + 10 * rank)
         self.go = gen(torch, (local_batch, F, oH, oW), 1000 * cfg + 10 * rank + 1)
-        self.m = SpatialConvolutionFBFFT(P, F, kW, kH, 1, 1, pW, pH, allreduce=allreduce)
+        self.m = SpatialConvolutionFBFFT(P, F, kW, kH, 1, 1, pW, pH, reuse, allreduce=allreduce)
         self.m.weight.copy_(gen(torch, (F, P, kH, kW), 1000 * cfg + 2, "uniform", bound))
         if has_bias:
             self.m.bias.copy_(gen(torch, (F,), 1000 * cfg + 3, "uniform", 0.01))
@@ -382,7 +383,7 @@ def run_gpu_arm(args):
     name, L = args.layer, LAYERS[args.layer]
     assert L[0] % world == 0, "global batch must divide over the ranks"
     local_b = L[0] // world
-    run = LayerRun(torch, name, L, local_b, rank, comm, args.allreduce)
+    run = LayerRun(torch, name, L, local_b, rank, comm, args.allreduce, args.reuse)
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()  # before the warm-up so that short timed regions still get samples
@@ -490,7 +491,7 @@ def run_gpu_arm(args):
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": workload_config(name, L, world, args.allreduce), "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
+            "config": workload_config(name, L, world, args.allreduce, args.reuse), "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
             "gpu_launches": int(launches), "clocks": clocks, "kernels": kernels, "layers": layers,
         }
         print(json.dumps(line), flush=True)
@@ -551,6 +552,9 @@ def main():
     ap.add_argument("--allreduce", default="spectrum", choices=["spectrum", "spatial"],
                     help="N > 1: sum the gradWeight spectrum before the inverse FFT (default, as the reference "
                          "data-parallel path is specified) or gradWeight after it")
+    ap.add_argument("--reuse", default="none", choices=["none", "all"],
+                    help="memoryReusePolicy of the timed module: 'all' lets the backward passes take over spectra "
+                         "of the earlier passes of the step (not the default, which recomputes everything)")
     ap.add_argument("--no-layers", action="store_true", help="skip the per-layer / per-pass table")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()

@@ -25,6 +25,9 @@ ACCUMULATE_GRADS = 1
 CONTRACT_SIMT = 2
 BIN_MAJOR_ONLY = 4
 ALLREDUCE_SPATIAL = 8
+REUSE_INPUT = 16
+REUSE_OUTPUT = 32
+REUSE_WEIGHT = 64
 
 
 class Desc(ctypes.Structure):

@@ -121,7 +121,9 @@ struct fbfftconv_handle {
   int oH, oW;
   bool plane_major = false;  // <= 4 input planes at a cooperative transform size: see contract_stream.cu
   // frequency buffers, each sized for the largest use among the three passes
-  size_t bytes_in, bytes_out, bytes_w, bytes_small, bytes_total;
+  size_t bytes_in, bytes_out, bytes_w, bytes_small, bytes_gi, bytes_total;
+  // spectrum reuse (plane-major layers only): which tensor's forward spectrum a buffer holds
+  bool have_input_spec = false, have_grad_output_spec = false, have_weight_spec = false;
   char* ws = nullptr;
   bool ws_owned = false;
   // device copies for the host-buffer entry points
@@ -136,6 +138,10 @@ struct fbfftconv_handle {
   float2* buf_out() const { return reinterpret_cast<float2*>(ws + bytes_in); }
   float2* buf_w() const { return reinterpret_cast<float2*>(ws + bytes_in + bytes_out); }
   float* small() const { return reinterpret_cast<float*>(ws + bytes_in + bytes_out + bytes_w); }
+  // gradInput spectrum when the input spectrum has to survive updateGradInput
+  float2* buf_gi() const {
+    return bytes_gi ? reinterpret_cast<float2*>(ws + bytes_in + bytes_out + bytes_w + bytes_small) : buf_in();
+  }
 };
 
 namespace {
@@ -378,7 +384,8 @@ int fbfftconv_create(const fbfftconv_desc* desc, fbfftconv_handle** out) {
   h->bytes_small = align256((B * F + F) * sizeof(float));
   if (d.flags & FBFFTCONV_ALLREDUCE_SPATIAL)  // local gradWeight + gradBias, summed across ranks
     h->bytes_small += align256((F * P * d.kernel_h * d.kernel_w + F) * sizeof(float));
-  h->bytes_total = h->bytes_in + h->bytes_out + h->bytes_w + h->bytes_small;
+  h->bytes_gi = (h->plane_major && (d.flags & FBFFTCONV_REUSE_INPUT)) ? h->bytes_in : 0;
+  h->bytes_total = h->bytes_in + h->bytes_out + h->bytes_w + h->bytes_small + h->bytes_gi;
   *out = h;
   return FBFFTCONV_OK;
 }
@@ -455,6 +462,10 @@ int fbfftconv_update_output(fbfftconv_handle* h, const float* input, const float
     StageTimer t(h, pass, FBFFTCONV_STAGE_IFFT, s);
     FBF_CUDA(launch_inverse(inverse_params(h->buf_out(), output, bias, B, F, h->oH, h->oW, 0, 0, 0, pm, h->N), h->N, s));
   }
+  // what the buffers hold now (plane-major spectra have one layout for all passes)
+  h->have_input_spec = pm;
+  h->have_weight_spec = pm;
+  h->have_grad_output_spec = false;  // buf_out holds the output spectrum
   return FBFFTCONV_OK;
 }
 
@@ -477,22 +488,27 @@ int fbfftconv_update_grad_input(fbfftconv_handle* h, const float* grad_output, c
     StageTimer t(h, pass, FBFFTCONV_STAGE_FFT_A, s);
     FBF_CUDA(launch_forward(forward_params(grad_output, h->buf_out(), B, F, h->oH, h->oW, 0, 0, pm ? 2 : 0, h->N), h->N, s));
   }
-  {
+  h->have_grad_output_spec = pm;
+  if (!(pm && (d.flags & FBFFTCONV_REUSE_WEIGHT) && h->have_weight_spec)) {
     StageTimer t(h, pass, FBFFTCONV_STAGE_FFT_B, s);
     FBF_CUDA(launch_forward(forward_params(weight, h->buf_w(), F, P, d.kernel_h, d.kernel_w, 0, 0, pm ? 2 : 1, h->N), h->N, s));
+    h->have_weight_spec = pm;
   }
+  // with REUSE_INPUT the input spectrum stays in its buffer for accGradParameters
+  float2* gi = h->buf_gi();
+  if (gi == h->buf_in()) h->have_input_spec = false;
   // I'^[bin][b][p] = 1/N^2 sum_f O'^[b][f] W^[p][f]
   {
     StageTimer t(h, pass, FBFFTCONV_STAGE_CONTRACT, s);
     if (pm) {  // I'^[b][p] = sum_f O'^[b][f] W^[f][p]
-      FBF_CUDA(launch_stream_reduce(h->buf_out(), h->buf_w(), h->buf_in(), B, F, P, F, 1, false, h->bins, norm, s));
+      FBF_CUDA(launch_stream_reduce(h->buf_out(), h->buf_w(), gi, B, F, P, F, 1, false, h->bins, norm, s));
     } else {
-      FBF_TRY(contract(h->buf_out(), h->buf_w(), h->buf_in(), h->bins, B, P, F, norm, 0, 0, simt, s));
+      FBF_TRY(contract(h->buf_out(), h->buf_w(), gi, h->bins, B, P, F, norm, 0, 0, simt, s));
     }
   }
   {
     StageTimer t(h, pass, FBFFTCONV_STAGE_IFFT, s);
-    FBF_CUDA(launch_inverse(inverse_params(h->buf_in(), grad_input, nullptr, B, P, d.input_h, d.input_w,
+    FBF_CUDA(launch_inverse(inverse_params(gi, grad_input, nullptr, B, P, d.input_h, d.input_w,
                                            d.pad_h, d.pad_w, 0, pm, h->N), h->N, s));
   }
   return FBFFTCONV_OK;
@@ -514,14 +530,17 @@ int fbfftconv_acc_grad_parameters(fbfftconv_handle* h, const float* input, const
   const int pass = FBFFTCONV_PASS_ACC_GRAD_PARAMETERS;
   const bool pm = h->plane_major;
   // O'^[bin][f][b], I^[bin][p][b]: the batch is the contraction index here
-  {
+  if (!(pm && (d.flags & FBFFTCONV_REUSE_OUTPUT) && h->have_grad_output_spec)) {
     StageTimer t(h, pass, FBFFTCONV_STAGE_FFT_A, s);
     FBF_CUDA(launch_forward(forward_params(grad_output, h->buf_out(), B, F, h->oH, h->oW, 0, 0, pm ? 2 : 1, h->N), h->N, s));
+    h->have_grad_output_spec = pm;
   }
-  {
+  if (!(pm && (d.flags & FBFFTCONV_REUSE_INPUT) && h->have_input_spec)) {
     StageTimer t(h, pass, FBFFTCONV_STAGE_FFT_B, s);
     FBF_CUDA(launch_forward(forward_params(input, h->buf_in(), B, P, d.input_h, d.input_w, d.pad_h, d.pad_w, pm ? 2 : 1, h->N), h->N, s));
+    h->have_input_spec = pm;
   }
+  h->have_weight_spec = false;  // the weight buffer receives the gradient spectrum below
   NcclApi* api = h->comm ? nccl_api() : nullptr;
   if (h->comm && !api) return fail(FBFFTCONV_ERR_COMM, "libnccl is not loadable");
   const bool spatial = h->comm && (d.flags & FBFFTCONV_ALLREDUCE_SPATIAL);

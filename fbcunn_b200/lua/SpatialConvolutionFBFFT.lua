@@ -43,6 +43,9 @@ local lib_path = package.searchpath(lib_name, package.cpath)
 local C = ffi.load(lib_path and lib_path or lib_name)
 
 local FBFFTCONV_ACCUMULATE_GRADS = 1
+local FBFFTCONV_REUSE_INPUT = 16
+local FBFFTCONV_REUSE_OUTPUT = 32
+local FBFFTCONV_REUSE_WEIGHT = 64
 
 local SpatialConvolutionFBFFT, parent =
    torch.class('nn.SpatialConvolutionFBFFT', 'nn.Module')
@@ -80,6 +83,19 @@ function SpatialConvolutionFBFFT:__init(nInputPlane, nOutputPlane, kW, kH, dW, d
           "Padding must be smaller than kernel")
    self.fftImplementation = 'fbfft'
    self.memoryReusePolicy = memoryReusePolicy or SpatialConvolutionFBFFT.memoryReuseNone
+   local function has(policy)
+      local p = self.memoryReusePolicy
+      if torch.type(p) == 'table' then
+         for _, v in ipairs(p) do
+            if v == policy or v == SpatialConvolutionFBFFT.memoryReuseAll then return true end
+         end
+         return false
+      end
+      return p == policy or p == SpatialConvolutionFBFFT.memoryReuseAll
+   end
+   self.reuseInputs = has(SpatialConvolutionFBFFT.memoryReuseInput)
+   self.reuseOutputs = has(SpatialConvolutionFBFFT.memoryReuseOutput)
+   self.reuseWeights = has(SpatialConvolutionFBFFT.memoryReuseWeight)
    self.numCudaStreams = numCudaStreams or 16
    self.accumulateGrads = false   -- reference behaviour: accGradParameters overwrites
 
@@ -107,8 +123,12 @@ function SpatialConvolutionFBFFT:prepareSizeAndBuffers(input)
    assert(torch.type(input) == 'torch.CudaTensor', "CUDA support only!")
    assert(input:dim() == 4, "2D convolutions on 4D tensors atm")
    assert(input:isContiguous())
-   local key = string.format('%d:%d:%d:%d', cutorch.getDevice(),
-                             input:size(1), input:size(3), input:size(4))
+   local flags = (self.accumulateGrads and FBFFTCONV_ACCUMULATE_GRADS or 0)
+      + (self.reuseInputs and FBFFTCONV_REUSE_INPUT or 0)
+      + (self.reuseOutputs and FBFFTCONV_REUSE_OUTPUT or 0)
+      + (self.reuseWeights and FBFFTCONV_REUSE_WEIGHT or 0)
+   local key = string.format('%d:%d:%d:%d:%d', cutorch.getDevice(),
+                             input:size(1), input:size(3), input:size(4), flags)
    if self.handleKey ~= key then
       self:cleanupBuffers()
       local desc = ffi.new('fbfftconv_desc', {
@@ -116,7 +136,7 @@ function SpatialConvolutionFBFFT:prepareSizeAndBuffers(input)
          input:size(3), input:size(4), self.kH, self.kW,
          self.dH, self.dW, self.padUp, self.padLeft,
          cutorch.getDevice() - 1,
-         self.accumulateGrads and FBFFTCONV_ACCUMULATE_GRADS or 0})
+         flags})
       local out = ffi.new('fbfftconv_handle*[1]')
       check(C.fbfftconv_create(desc, out))
       self.handle = ffi.gc(out[0], C.fbfftconv_destroy)

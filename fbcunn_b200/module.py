@@ -168,7 +168,9 @@ class SpatialConvolutionFBFFT:
             self._handle = None
             self._handle_key = None
 
-    # accepted for interface compatibility; spectra are recomputed on every pass
+    # the reference's reuse switches (fbcunn/SpatialConvolutionFFT.lua:405-416): a spectrum is
+    # taken over from the earlier pass of the step where both passes read one layout (see
+    # FBFFTCONV_REUSE_* in include/fbfftconv.h); the native handle is rebuilt on a change
     def setReuseInputs(self, val):
         self._toggle(memoryReuseInput, val)
 
@@ -222,14 +224,17 @@ class SpatialConvolutionFBFFT:
     def _prepare(self, input):
         """prepareSizeAndBuffers: a native handle per (batch, image size)."""
         B, _, iH, iW = input.shape
-        key = (int(B), int(iH), int(iW))
-        if self._handle is not None and self._handle_key == key:
-            return self._handle
-        self.cleanupBuffers()
         flags = (capi.ACCUMULATE_GRADS if self._accumulate else 0) | \
                 (capi.CONTRACT_SIMT if self._contraction == "simt" else 0) | \
                 (capi.BIN_MAJOR_ONLY if self._contraction == "bin_major" else 0) | \
-                (capi.ALLREDUCE_SPATIAL if self._allreduce == "spatial" else 0)
+                (capi.ALLREDUCE_SPATIAL if self._allreduce == "spatial" else 0) | \
+                (capi.REUSE_INPUT if memoryReuseInput in self.memoryReusePolicy else 0) | \
+                (capi.REUSE_OUTPUT if memoryReuseOutput in self.memoryReusePolicy else 0) | \
+                (capi.REUSE_WEIGHT if memoryReuseWeight in self.memoryReusePolicy else 0)
+        key = (int(B), int(iH), int(iW), flags)
+        if self._handle is not None and self._handle_key == key:
+            return self._handle
+        self.cleanupBuffers()
         desc = capi.Desc(B, self.nInputPlane, self.nOutputPlane, iH, iW, self.kH, self.kW,
                          self.dH, self.dW, self.padUp, self.padLeft,
                          self.device.index if self.device.index is not None else torch.cuda.current_device(),

@@ -58,7 +58,22 @@ enum {
    * (F*P*kH*kW floats) instead of summing its spectrum before it (F*P*bins complex
    * values).  The transform is linear, so both orders give the same gradient; the
    * default is the frequency-domain sum. */
-  FBFFTCONV_ALLREDUCE_SPATIAL = 8
+  FBFFTCONV_ALLREDUCE_SPATIAL = 8,
+  /* Spectrum reuse across the passes of one training step, the memoryReusePolicy of the
+   * reference module (fbcunn/SpatialConvolutionFFT.lua:59-63, :405-416;
+   * fbcunn/SpatialConvolutionFBFFT.lua:226-237, :305-330).  The caller promises that the
+   * tensor in question has not changed since the pass that transformed it:
+   *   REUSE_WEIGHT  updateGradInput takes the weight spectrum of the last updateOutput,
+   *   REUSE_INPUT   accGradParameters takes the input spectrum of the last updateOutput,
+   *   REUSE_OUTPUT  accGradParameters takes the gradOutput spectrum of the last updateGradInput.
+   * A spectrum is taken over only where both passes read it in the same layout, which is
+   * the case for the plane-major buffers of layers with <= 4 input planes at transform sizes
+   * 64 / 128; elsewhere each pass needs its operands contiguous along its own contraction
+   * index, the transform is as cheap as the transposition a cached spectrum would need, and
+   * the flags have no effect. */
+  FBFFTCONV_REUSE_INPUT = 16,
+  FBFFTCONV_REUSE_OUTPUT = 32,
+  FBFFTCONV_REUSE_WEIGHT = 64
 };
 
 /* Constructor arguments of nn.SpatialConvolutionFBFFT

@@ -249,6 +249,55 @@ def test_thin_layers_in_both_frequency_layouts():
         assert float((ta - tc).abs().max()) <= 2e-5 * float(tc.abs().max()), name
 
 
+def _stage_launches(m):
+    """(pass, stage) -> number of timed launches since profiling was switched on."""
+    lib = capi.lib()
+    out = {}
+    for pi in range(3):
+        for si in range(6):
+            ms, n = ctypes.c_double(), ctypes.c_int()
+            capi.check(lib.fbfftconv_profile_read(m._handle, pi, si, ctypes.byref(ms), ctypes.byref(n)))
+            out[(pi, si)] = n.value
+    return out
+
+
+@pytest.mark.parametrize("plane_major", [True, False])
+def test_spectrum_reuse_across_the_passes_of_a_step(plane_major):
+    """memoryReusePolicy of the reference (fbcunn/SpatialConvolutionFFT.lua:405-416): the backward
+    passes take over spectra of the earlier passes.  Results must not change; where the layouts
+    coincide (plane-major layers) the transforms are really skipped, elsewhere they are redone."""
+    s = oracle.Shape(4, 3, 6, 50, 44, 5, 6, 1, 0) if plane_major else oracle.Shape(4, 8, 6, 20, 18, 3, 4, 1, 0)
+    x, w, go, b = _data(s, 991, bias=True)
+    m = SpatialConvolutionFBFFT(s.P, s.F, s.kW, s.kH, 1, 1, s.padW, s.padH, "all")
+    m.weight.copy_(_dev(w))
+    m.bias.copy_(_dev(b))
+    dx, dgo = _dev(x), _dev(go)
+    m.updateOutput(dx)
+    lib = capi.lib()
+    capi.check(lib.fbfftconv_profile_enable(m._handle, 1))
+    capi.check(lib.fbfftconv_profile_reset(m._handle))
+    for _ in range(2):  # a second step must find the buffers in a usable state again
+        out = m.updateOutput(dx).cpu().numpy()
+        gi = m.updateGradInput(dx, dgo).cpu().numpy()
+        m.accGradParameters(dx, dgo, 0.8)
+        assert _rel(out, oracle.update_output(s, x, w, b)) <= PASS_TOL
+        assert _rel(gi, oracle.update_grad_input(s, go, w)) <= PASS_TOL
+        assert _rel(m.gradWeight.cpu().numpy(), oracle.acc_grad_weight(s, x, go, 0.8)) <= PASS_TOL
+        assert _rel(m.gradBias.cpu().numpy(), oracle.acc_grad_bias(s, go, 0.8)) <= PASS_TOL
+    torch.cuda.synchronize()
+    n = _stage_launches(m)
+    FFT_A, FFT_B = 0, 1
+    assert n[(0, FFT_A)] == 2 and n[(0, FFT_B)] == 2 and n[(1, FFT_A)] == 2
+    skipped = 0 if plane_major else 2
+    assert n[(1, FFT_B)] == skipped, "weight spectrum of updateOutput"
+    assert n[(2, FFT_A)] == skipped, "gradOutput spectrum of updateGradInput"
+    assert n[(2, FFT_B)] == skipped, "input spectrum of updateOutput"
+    # accGradParameters on its own (nothing to take over) still transforms what it needs
+    m2 = SpatialConvolutionFBFFT(s.P, s.F, s.kW, s.kH, 1, 1, s.padW, s.padH, "all")
+    m2.accGradParameters(dx, dgo, 0.8)
+    assert _rel(m2.gradWeight.cpu().numpy(), oracle.acc_grad_weight(s, x, go, 0.8)) <= PASS_TOL
+
+
 def test_random_sweep():
     """Recipe of test/test_FFT.lua:82-107: B = 4*rand(4), planes <= 13, k <= 7, pad <= min(4, k-1)."""
     rng = np.random.default_rng(424242)
