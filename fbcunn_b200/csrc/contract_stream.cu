@@ -77,30 +77,65 @@ stream_expand_kernel(const float2* __restrict__ X, const float2* __restrict__ Y,
   }
 }
 
+// 16-byte asynchronous global -> shared copy; a thread only ever reads back its own copies, so
+// cp.async.wait_group is all the synchronisation the ring below needs.
+__device__ __forceinline__ void copy16_async(float4* smem_dst, const float2* gmem_src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(smem_dst)),
+               "l"(gmem_src)
+               : "memory");
+}
+__device__ __forceinline__ void copy_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int PENDING>
+__device__ __forceinline__ void copy_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(PENDING) : "memory");
+}
+__device__ __forceinline__ C2 as_c2(float4 v) { return C2{make_float2(v.x, v.y), make_float2(v.z, v.w)}; }
+
+constexpr int RING_STAGES = 4;  // iterations of w in flight per thread
+
 // Z[u][p][bin] = alpha * sum_{w<W} opX(X[u*xs_u + w*xs_w][bin]) * Y[w][p][bin],  p < P <= 4
-// block: TU rows u, 512 bins; the loop over w is the long one.
+// block: TU rows u, 512 bins; the loop over w is the long one.  The operands of the next
+// RING_STAGES - 1 iterations are in flight into a per-thread ring in shared memory: the bytes
+// in flight that a bandwidth-bound loop needs do not have to live in registers.
 template <int TU, bool CONJX>
 __global__ void __launch_bounds__(THREADS)
 stream_reduce_kernel(const float2* __restrict__ X, const float2* __restrict__ Y, float2* __restrict__ Z, int U,
                      int W, int P, long long xs_u, long long xs_w, long long bins, float alpha) {
+  extern __shared__ float4 ring[];  // [RING_STAGES][PMAX + TU][THREADS]
+  constexpr int NLOAD = PMAX + TU;
   const long long bin = ((long long)blockIdx.x * THREADS + threadIdx.x) * 2;
   if (bin >= bins) return;
   const int u0 = blockIdx.y * TU;
+  float4* mine = ring + threadIdx.x;
+  auto issue = [&](int w) {
+    if (w < W) {
+      float4* st = mine + (w % RING_STAGES) * NLOAD * THREADS;
+#pragma unroll
+      for (int p = 0; p < PMAX; ++p)
+        if (p < P) copy16_async(st + p * THREADS, Y + ((long long)w * P + p) * bins + bin);
+#pragma unroll
+      for (int i = 0; i < TU; ++i)
+        if (u0 + i < U) copy16_async(st + (PMAX + i) * THREADS, X + ((u0 + i) * xs_u + w * xs_w) * bins + bin);
+    }
+    copy_commit();  // one group per iteration, empty or not, keeps the wait count fixed
+  };
   C2 acc[TU][PMAX];
 #pragma unroll
   for (int i = 0; i < TU; ++i)
 #pragma unroll
     for (int p = 0; p < PMAX; ++p) acc[i][p] = C2{make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-#pragma unroll 2
+#pragma unroll
+  for (int w = 0; w < RING_STAGES - 1; ++w) issue(w);
+  const C2 zero{make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
   for (int w = 0; w < W; ++w) {
+    issue(w + RING_STAGES - 1);
+    copy_wait<RING_STAGES - 1>();
+    const float4* st = mine + (w % RING_STAGES) * NLOAD * THREADS;
     C2 y[PMAX], x[TU];
 #pragma unroll
-    for (int p = 0; p < PMAX; ++p)
-      y[p] = p < P ? ld2(Y + ((long long)w * P + p) * bins + bin) : C2{make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+    for (int p = 0; p < PMAX; ++p) y[p] = p < P ? as_c2(st[p * THREADS]) : zero;
 #pragma unroll
-    for (int i = 0; i < TU; ++i)
-      x[i] = u0 + i < U ? ld2(X + ((u0 + i) * xs_u + w * xs_w) * bins + bin)
-                        : C2{make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+    for (int i = 0; i < TU; ++i) x[i] = u0 + i < U ? as_c2(st[(PMAX + i) * THREADS]) : zero;
 #pragma unroll
     for (int i = 0; i < TU; ++i)
 #pragma unroll
@@ -142,17 +177,19 @@ cudaError_t launch_stream_reduce(const float2* x, const float2* y, float2* z, in
   const bool pair = (long long)bin_blocks * ((U + 1) / 2) >= 2 * 148;
   dim3 grid(bin_blocks, pair ? (U + 1) / 2 : U);
   if (grid.y > 65535) return cudaErrorInvalidValue;
-  if (pair) {
-    if (conj_x)
-      stream_reduce_kernel<2, true><<<grid, THREADS, 0, stream>>>(x, y, z, U, W, P, xs_u, xs_w, bins, alpha);
-    else
-      stream_reduce_kernel<2, false><<<grid, THREADS, 0, stream>>>(x, y, z, U, W, P, xs_u, xs_w, bins, alpha);
-  } else {
-    if (conj_x)
-      stream_reduce_kernel<1, true><<<grid, THREADS, 0, stream>>>(x, y, z, U, W, P, xs_u, xs_w, bins, alpha);
-    else
-      stream_reduce_kernel<1, false><<<grid, THREADS, 0, stream>>>(x, y, z, U, W, P, xs_u, xs_w, bins, alpha);
-  }
+  auto launch = [&](auto kernel, int tu) -> cudaError_t {
+    const int smem = RING_STAGES * (PMAX + tu) * THREADS * (int)sizeof(float4);
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    kernel<<<grid, THREADS, smem, stream>>>(x, y, z, U, W, P, xs_u, xs_w, bins, alpha);
+    return cudaSuccess;
+  };
+  cudaError_t e;
+  if (pair)
+    e = conj_x ? launch(stream_reduce_kernel<2, true>, 2) : launch(stream_reduce_kernel<2, false>, 2);
+  else
+    e = conj_x ? launch(stream_reduce_kernel<1, true>, 1) : launch(stream_reduce_kernel<1, false>, 1);
+  if (e != cudaSuccess) return e;
   count_launch();
   return cudaGetLastError();
 }
