@@ -97,25 +97,25 @@ constexpr int RING_STAGES = 4;  // iterations of w in flight per thread
 // block: TU rows u, 512 bins; the loop over w is the long one.  The operands of the next
 // RING_STAGES - 1 iterations are in flight into a per-thread ring in shared memory: the bytes
 // in flight that a bandwidth-bound loop needs do not have to live in registers.
-template <int TU, bool CONJX>
-__global__ void __launch_bounds__(THREADS)
+template <int TU, bool CONJX, int NT>
+__global__ void __launch_bounds__(NT)
 stream_reduce_kernel(const float2* __restrict__ X, const float2* __restrict__ Y, float2* __restrict__ Z, int U,
                      int W, int P, long long xs_u, long long xs_w, long long bins, float alpha) {
-  extern __shared__ float4 ring[];  // [RING_STAGES][PMAX + TU][THREADS]
+  extern __shared__ float4 ring[];  // [RING_STAGES][PMAX + TU][NT]
   constexpr int NLOAD = PMAX + TU;
-  const long long bin = ((long long)blockIdx.x * THREADS + threadIdx.x) * 2;
+  const long long bin = ((long long)blockIdx.x * NT + threadIdx.x) * 2;
   if (bin >= bins) return;
   const int u0 = blockIdx.y * TU;
   float4* mine = ring + threadIdx.x;
   auto issue = [&](int w) {
     if (w < W) {
-      float4* st = mine + (w % RING_STAGES) * NLOAD * THREADS;
+      float4* st = mine + (w % RING_STAGES) * NLOAD * NT;
 #pragma unroll
       for (int p = 0; p < PMAX; ++p)
-        if (p < P) copy16_async(st + p * THREADS, Y + ((long long)w * P + p) * bins + bin);
+        if (p < P) copy16_async(st + p * NT, Y + ((long long)w * P + p) * bins + bin);
 #pragma unroll
       for (int i = 0; i < TU; ++i)
-        if (u0 + i < U) copy16_async(st + (PMAX + i) * THREADS, X + ((u0 + i) * xs_u + w * xs_w) * bins + bin);
+        if (u0 + i < U) copy16_async(st + (PMAX + i) * NT, X + ((u0 + i) * xs_u + w * xs_w) * bins + bin);
     }
     copy_commit();  // one group per iteration, empty or not, keeps the wait count fixed
   };
@@ -130,12 +130,12 @@ stream_reduce_kernel(const float2* __restrict__ X, const float2* __restrict__ Y,
   for (int w = 0; w < W; ++w) {
     issue(w + RING_STAGES - 1);
     copy_wait<RING_STAGES - 1>();
-    const float4* st = mine + (w % RING_STAGES) * NLOAD * THREADS;
+    const float4* st = mine + (w % RING_STAGES) * NLOAD * NT;
     C2 y[PMAX], x[TU];
 #pragma unroll
-    for (int p = 0; p < PMAX; ++p) y[p] = p < P ? as_c2(st[p * THREADS]) : zero;
+    for (int p = 0; p < PMAX; ++p) y[p] = p < P ? as_c2(st[p * NT]) : zero;
 #pragma unroll
-    for (int i = 0; i < TU; ++i) x[i] = u0 + i < U ? as_c2(st[(PMAX + i) * THREADS]) : zero;
+    for (int i = 0; i < TU; ++i) x[i] = u0 + i < U ? as_c2(st[(PMAX + i) * NT]) : zero;
 #pragma unroll
     for (int i = 0; i < TU; ++i)
 #pragma unroll
@@ -171,24 +171,28 @@ cudaError_t launch_stream_expand(const float2* x, const float2* y, float2* z, in
 cudaError_t launch_stream_reduce(const float2* x, const float2* y, float2* z, int U, int W, int P, long long xs_u,
                                  long long xs_w, bool conj_x, long long bins, float alpha, cudaStream_t stream) {
   if (P < 1 || P > PMAX || (bins & 1)) return cudaErrorInvalidValue;
-  const unsigned bin_blocks = (unsigned)((bins / 2 + THREADS - 1) / THREADS);
-  // two rows per block halve the re-reads of Y; with few rows (a small batch shard) one row
-  // per block keeps every SM busy instead
-  const bool pair = (long long)bin_blocks * ((U + 1) / 2) >= 2 * 148;
-  dim3 grid(bin_blocks, pair ? (U + 1) / 2 : U);
+  // Four rows per block (128 threads) quarter the re-reads of Y, which come from L2 and would
+  // otherwise be twice the DRAM traffic; with few rows (a small batch shard) fewer rows per
+  // block keep every SM busy instead.
+  auto blocks_for = [&](int nt, int tu) { return (long long)((bins / 2 + nt - 1) / nt) * ((U + tu - 1) / tu); };
+  const int tu = blocks_for(128, 4) >= 3 * 148 ? 4 : blocks_for(256, 2) >= 2 * 148 ? 2 : 1;
+  const int nt = tu == 4 ? 128 : 256;
+  dim3 grid((unsigned)((bins / 2 + nt - 1) / nt), (U + tu - 1) / tu);
   if (grid.y > 65535) return cudaErrorInvalidValue;
-  auto launch = [&](auto kernel, int tu) -> cudaError_t {
-    const int smem = RING_STAGES * (PMAX + tu) * THREADS * (int)sizeof(float4);
+  auto launch = [&](auto kernel) -> cudaError_t {
+    const int smem = RING_STAGES * (PMAX + tu) * nt * (int)sizeof(float4);
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
-    kernel<<<grid, THREADS, smem, stream>>>(x, y, z, U, W, P, xs_u, xs_w, bins, alpha);
+    kernel<<<grid, nt, smem, stream>>>(x, y, z, U, W, P, xs_u, xs_w, bins, alpha);
     return cudaSuccess;
   };
   cudaError_t e;
-  if (pair)
-    e = conj_x ? launch(stream_reduce_kernel<2, true>, 2) : launch(stream_reduce_kernel<2, false>, 2);
+  if (tu == 4)
+    e = conj_x ? launch(stream_reduce_kernel<4, true, 128>) : launch(stream_reduce_kernel<4, false, 128>);
+  else if (tu == 2)
+    e = conj_x ? launch(stream_reduce_kernel<2, true, 256>) : launch(stream_reduce_kernel<2, false, 256>);
   else
-    e = conj_x ? launch(stream_reduce_kernel<1, true>, 1) : launch(stream_reduce_kernel<1, false>, 1);
+    e = conj_x ? launch(stream_reduce_kernel<1, true, 256>) : launch(stream_reduce_kernel<1, false, 256>);
   if (e != cudaSuccess) return e;
   count_launch();
   return cudaGetLastError();
