@@ -43,40 +43,6 @@ __device__ __forceinline__ void mac2(C2& acc, const C2& x, const C2& y) {
   mac1<CONJ>(acc.b, x.b, y.b);
 }
 
-// Z[u][v][bin] = alpha * sum_{p<P} X[u][p][bin] * conj(Y[v][p][bin])
-// block: TU rows u, a chunk of columns v, 512 bins.
-template <int TU>
-__global__ void __launch_bounds__(THREADS)
-stream_expand_kernel(const float2* __restrict__ X, const float2* __restrict__ Y, float2* __restrict__ Z, int U,
-                     int V, int P, int v_per_block, long long bins, float alpha) {
-  const long long bin = ((long long)blockIdx.x * THREADS + threadIdx.x) * 2;
-  if (bin >= bins) return;
-  const int u0 = blockIdx.y * TU;
-  const int v0 = blockIdx.z * v_per_block;
-  const int v1 = min(V, v0 + v_per_block);
-  C2 x[TU][PMAX];
-#pragma unroll
-  for (int i = 0; i < TU; ++i)
-#pragma unroll
-    for (int p = 0; p < PMAX; ++p)
-      x[i][p] = (u0 + i < U && p < P) ? ld2(X + ((long long)(u0 + i) * P + p) * bins + bin)
-                                      : C2{make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-  for (int v = v0; v < v1; ++v) {
-    C2 y[PMAX];
-#pragma unroll
-    for (int p = 0; p < PMAX; ++p)
-      y[p] = p < P ? ld2(Y + ((long long)v * P + p) * bins + bin) : C2{make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-#pragma unroll
-    for (int i = 0; i < TU; ++i) {
-      if (u0 + i >= U) break;
-      C2 acc{make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-#pragma unroll
-      for (int p = 0; p < PMAX; ++p) mac2<2>(acc, x[i][p], y[p]);
-      st2(Z + ((long long)(u0 + i) * V + v) * bins + bin, acc, alpha);
-    }
-  }
-}
-
 // 16-byte asynchronous global -> shared copy; a thread only ever reads back its own copies, so
 // cp.async.wait_group is all the synchronisation the ring below needs.
 __device__ __forceinline__ void copy16_async(float4* smem_dst, const float2* gmem_src) {
@@ -92,6 +58,56 @@ __device__ __forceinline__ void copy_wait() {
 __device__ __forceinline__ C2 as_c2(float4 v) { return C2{make_float2(v.x, v.y), make_float2(v.z, v.w)}; }
 
 constexpr int RING_STAGES = 4;  // iterations of w in flight per thread
+
+// Z[u][v][bin] = alpha * sum_{p<P} X[u][p][bin] * conj(Y[v][p][bin])
+// block: TU rows u, a chunk of columns v, 512 bins; the Y planes of the next RING_STAGES - 1
+// columns are in flight into the per-thread ring.
+template <int TU>
+__global__ void __launch_bounds__(THREADS)
+stream_expand_kernel(const float2* __restrict__ X, const float2* __restrict__ Y, float2* __restrict__ Z, int U,
+                     int V, int P, int v_per_block, long long bins, float alpha) {
+  extern __shared__ float4 ring[];  // [RING_STAGES][PMAX][THREADS]
+  const long long bin = ((long long)blockIdx.x * THREADS + threadIdx.x) * 2;
+  if (bin >= bins) return;
+  const int u0 = blockIdx.y * TU;
+  const int v0 = blockIdx.z * v_per_block;
+  const int v1 = min(V, v0 + v_per_block);
+  float4* mine = ring + threadIdx.x;
+  auto issue = [&](int v) {
+    if (v < v1) {
+      float4* st = mine + ((v - v0) % RING_STAGES) * PMAX * THREADS;
+#pragma unroll
+      for (int p = 0; p < PMAX; ++p)
+        if (p < P) copy16_async(st + p * THREADS, Y + ((long long)v * P + p) * bins + bin);
+    }
+    copy_commit();
+  };
+#pragma unroll
+  for (int i = 0; i < RING_STAGES - 1; ++i) issue(v0 + i);
+  const C2 zero{make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+  C2 x[TU][PMAX];
+#pragma unroll
+  for (int i = 0; i < TU; ++i)
+#pragma unroll
+    for (int p = 0; p < PMAX; ++p)
+      x[i][p] = (u0 + i < U && p < P) ? ld2(X + ((long long)(u0 + i) * P + p) * bins + bin) : zero;
+  for (int v = v0; v < v1; ++v) {
+    issue(v + RING_STAGES - 1);
+    copy_wait<RING_STAGES - 1>();
+    const float4* st = mine + ((v - v0) % RING_STAGES) * PMAX * THREADS;
+    C2 y[PMAX];
+#pragma unroll
+    for (int p = 0; p < PMAX; ++p) y[p] = p < P ? as_c2(st[p * THREADS]) : zero;
+#pragma unroll
+    for (int i = 0; i < TU; ++i) {
+      if (u0 + i >= U) break;
+      C2 acc = zero;
+#pragma unroll
+      for (int p = 0; p < PMAX; ++p) mac2<2>(acc, x[i][p], y[p]);
+      st2(Z + ((long long)(u0 + i) * V + v) * bins + bin, acc, alpha);
+    }
+  }
+}
 
 // Z[u][p][bin] = alpha * sum_{w<W} opX(X[u*xs_u + w*xs_w][bin]) * Y[w][p][bin],  p < P <= 4
 // block: TU rows u, 512 bins; the loop over w is the long one.  The operands of the next
@@ -163,7 +179,10 @@ cudaError_t launch_stream_expand(const float2* x, const float2* y, float2* z, in
   const int v_per_block = (V + v_chunks - 1) / v_chunks;
   dim3 grid(bin_blocks, (U + TU - 1) / TU, (V + v_per_block - 1) / v_per_block);
   if (grid.y > 65535 || grid.z > 65535) return cudaErrorInvalidValue;
-  stream_expand_kernel<TU><<<grid, THREADS, 0, stream>>>(x, y, z, U, V, P, v_per_block, bins, alpha);
+  const int smem = RING_STAGES * PMAX * THREADS * (int)sizeof(float4);
+  cudaError_t e = cudaFuncSetAttribute(stream_expand_kernel<TU>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return e;
+  stream_expand_kernel<TU><<<grid, THREADS, smem, stream>>>(x, y, z, U, V, P, v_per_block, bins, alpha);
   count_launch();
   return cudaGetLastError();
 }
