@@ -64,6 +64,8 @@ _SIGNATURES = {
     "fbfftconv_spectrum_bytes": (c_size_t, [c_int, c_int, c_int]),
     "fbfftconv_fft2d": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "fbfftconv_ifft2d": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "fbfftconv_fft1d": (c_int, [c_void_p, c_void_p, ctypes.c_longlong, c_int, c_int, c_int, c_void_p]),
+    "fbfftconv_ifft1d": (c_int, [c_void_p, c_void_p, ctypes.c_longlong, c_int, c_int, c_int, c_void_p]),
     "fbfftconv_transpose_mm": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p]),
     "fbfftconv_tensor_core_status": (c_int, [c_int]),
     "fbfftconv_update_output_bias": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),

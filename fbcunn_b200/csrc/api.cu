@@ -745,6 +745,28 @@ int fbfftconv_ifft2d(const void* spectrum, float* real, const float* bias, int d
   return FBFFTCONV_OK;
 }
 
+int fbfftconv_fft1d(const float* real, void* spectrum, long long rows, int n, int fft_size,
+                    int pad_left, fbfftconv_stream stream) {
+  if (!real || !spectrum) return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "null argument");
+  if (!valid_fft_size(fft_size)) return fail(FBFFTCONV_ERR_UNSUPPORTED_SIZE, "transform size %d not in {8,16,32,64,128}", fft_size);
+  if (rows <= 0 || n <= 0 || pad_left < 0 || n + pad_left > fft_size)
+    return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "row of %d floats at %d does not fit %d", n, pad_left, fft_size);
+  FBF_CUDA(launch_fft1d(false, real, nullptr, static_cast<float2*>(spectrum), rows, n, fft_size, pad_left,
+                        static_cast<cudaStream_t>(stream)));
+  return FBFFTCONV_OK;
+}
+
+int fbfftconv_ifft1d(const void* spectrum, float* real, long long rows, int n, int fft_size,
+                     int offset, fbfftconv_stream stream) {
+  if (!real || !spectrum) return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "null argument");
+  if (!valid_fft_size(fft_size)) return fail(FBFFTCONV_ERR_UNSUPPORTED_SIZE, "transform size %d not in {8,16,32,64,128}", fft_size);
+  if (rows <= 0 || n <= 0 || offset < 0 || n + offset > fft_size)
+    return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "window of %d floats at %d does not fit %d", n, offset, fft_size);
+  FBF_CUDA(launch_fft1d(true, nullptr, real, static_cast<float2*>(const_cast<void*>(spectrum)), rows, n, fft_size,
+                        offset, static_cast<cudaStream_t>(stream)));
+  return FBFFTCONV_OK;
+}
+
 int fbfftconv_transpose_mm(const void* a, const void* b, void* c, int bins, int m, int n, int k,
                            float alpha, int conj_a, int conj_b, int use_simt,
                            fbfftconv_stream stream) {

@@ -907,4 +907,51 @@ struct CoopInverse {
   }
 };
 
+// ===========================================================================
+// Batched 1-D transforms: the row half of the 2-D kernels.  A "plane" is a block of up to N
+// consecutive rows (p.h of them, p.w floats each); after the row phases the column buffer holds
+// the half spectrum of every row, and it is written out / read in as it is:
+//     spectrum1d[global row][k],  k in [0, N/2],  global row = inner * p.h + y.
+// p.n_rows must be 1; p.spec is the base of the 1-D spectrum.
+// ===========================================================================
+template <int N, int T>
+struct Rows1D {
+  static constexpr int KX = N / 2 + 1;
+
+  // element (y, t, k) of the column buffer, in either kernel family's layout
+  static FBF_HD int mid_index(int y, int t, int k) {
+    if constexpr (N <= 32) {
+      return y * TileLayout<N, T>::PITCH2 + k * T + t;
+    } else {
+      return y * CoopLayout<N, T>::PITCH2 + t * KX + k;
+    }
+  }
+
+  static FBF_HD void store_spectrum(const FftParams& p, const FftGeom& g, const char* smem, int tid,
+                                    int nthreads, int inner0) {
+    const float2* mid = reinterpret_cast<const float2*>(smem + g.off_b);
+    const int per_plane = g.he * KX;
+    for (int item = tid; item < T * per_plane; item += nthreads) {
+      const int t = item / per_plane, r = item - t * per_plane;
+      const int y = r / KX, k = r - y * KX;
+      const int inner = inner0 + t;
+      if (inner >= p.n_inner) break;
+      p.spec[((long long)inner * p.h + y) * KX + k] = mid[mid_index(y, t, k)];
+    }
+  }
+
+  static FBF_HD void load_spectrum(const FftParams& p, const FftGeom& g, char* smem, int tid, int nthreads,
+                                   int inner0) {
+    float2* mid = reinterpret_cast<float2*>(smem + g.off_b);
+    const int per_plane = g.he * KX;
+    for (int item = tid; item < T * per_plane; item += nthreads) {
+      const int t = item / per_plane, r = item - t * per_plane;
+      const int y = r / KX, k = r - y * KX;
+      const int inner = inner0 + t;
+      mid[mid_index(y, t, k)] =
+          inner < p.n_inner ? p.spec[((long long)inner * p.h + y) * KX + k] : make_float2(0.f, 0.f);
+    }
+  }
+};
+
 }  // namespace fbfft

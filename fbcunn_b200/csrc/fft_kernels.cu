@@ -179,6 +179,70 @@ fft2d_inverse_coop_kernel(const __grid_constant__ FftParams p, const __grid_cons
   }
 }
 
+// ---- batched 1-D transforms: the row phases only ------------------------------------------
+template <int N, int T>
+__global__ void __launch_bounds__(N <= 32 ? block_threads<N, T>() : FBF_COOP_THREADS)
+fft1d_forward_kernel(const __grid_constant__ FftParams p, const __grid_constant__ FftGeom g) {
+  extern __shared__ __align__(16) char smem[];
+  const int tid = threadIdx.x, nth = blockDim.x;
+  const int inner0 = blockIdx.x * T;
+  if constexpr (N <= 32) {
+    Forward<N, T>::load(p, g, smem, tid, nth, 0, inner0);
+    __syncthreads();
+    LineRegs<N> regs;
+    Forward<N, T>::row_fetch(p, g, smem, tid, 0, inner0, regs);
+    __syncthreads();
+    Forward<N, T>::row_pass(g, smem, tid, regs);
+  } else {
+    constexpr int N1 = CoopForward<N, T>::N1, N2 = CoopForward<N, T>::N2;
+    for (int line0 = 0; line0 < g.lines1; line0 += g.chunk) {
+      const int nl = min(g.chunk, g.lines1 - line0);
+      CoopForward<N, T>::row_step1(p, g, smem, tid, nth, 0, inner0, line0, nl);
+      __syncthreads();
+      const int items = nl * N1;
+      for (int base = 0; base < items; base += nth) {
+        float2 u[N2], mirror_odd[N2 / 2];
+        const bool active = CoopForward<N, T>::row_step2_fft(g, smem, base + tid, nl, u);
+#pragma unroll
+        for (int i = 0; i < N2 / 2; ++i) {
+          mirror_odd[i].x = __shfl_xor_sync(0xffffffffu, u[2 * i + 1].x, 1);
+          mirror_odd[i].y = __shfl_xor_sync(0xffffffffu, u[2 * i + 1].y, 1);
+        }
+        if (active) CoopForward<N, T>::row_step2_split(g, smem, base + tid, line0, u, mirror_odd);
+      }
+      __syncthreads();
+    }
+  }
+  __syncthreads();
+  Rows1D<N, T>::store_spectrum(p, g, smem, tid, nth, inner0);
+}
+
+template <int N, int T>
+__global__ void __launch_bounds__(N <= 32 ? block_threads<N, T>() : FBF_COOP_THREADS)
+fft1d_inverse_kernel(const __grid_constant__ FftParams p, const __grid_constant__ FftGeom g) {
+  extern __shared__ __align__(16) char smem[];
+  const int tid = threadIdx.x, nth = blockDim.x;
+  const int inner0 = blockIdx.x * T;
+  Rows1D<N, T>::load_spectrum(p, g, smem, tid, nth, inner0);
+  __syncthreads();
+  if constexpr (N <= 32) {
+    LineRegs<N> regs;
+    Inverse<N, T>::row_fetch(g, smem, tid, regs);
+    __syncthreads();
+    Inverse<N, T>::row_pass(p, g, smem, tid, 0, inner0, regs);
+    __syncthreads();
+    Inverse<N, T>::store(p, g, smem, tid, nth, 0, inner0);
+  } else {
+    for (int line0 = 0; line0 < g.lines1; line0 += g.chunk) {
+      const int nl = min(g.chunk, g.lines1 - line0);
+      CoopInverse<N, T>::row_step1(p, g, smem, tid, nth, line0, nl);
+      __syncthreads();
+      CoopInverse<N, T>::row_step2(p, g, smem, tid, nth, 0, inner0, line0, nl);
+      __syncthreads();
+    }
+  }
+}
+
 constexpr int kSmemMax = 227 * 1024;
 constexpr int kSmemTwoBlocks = 113 * 1024;
 
@@ -318,6 +382,76 @@ cudaError_t launch_inverse(const FftParams& p, int N, cudaStream_t stream) {
   const int T = pick_inverse_tile(N, p.h, p.w);
   if (T == 0 || p.n_rows > 65535 || !spectrum_fits(p, N)) return cudaErrorInvalidConfiguration;
   return dispatch(true, p, N, T, stream);
+}
+
+namespace {
+
+template <int N, int T>
+cudaError_t run_1d(bool inverse, const FftParams& p, cudaStream_t stream) {
+  if constexpr (!tile_allowed(N, T)) {
+    return cudaErrorInvalidConfiguration;
+  } else {
+    const FftGeom g = inverse ? inverse_geom(N, T, p.h, p.w) : forward_geom(N, T, p.h, p.w, 0, p.off_x);
+    void (*kernel)(FftParams, FftGeom) = inverse ? fft1d_inverse_kernel<N, T> : fft1d_forward_kernel<N, T>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, g.smem_bytes);
+    if (e != cudaSuccess) return e;
+    kernel<<<(p.n_inner + T - 1) / T, g.threads, g.smem_bytes, stream>>>(p, g);
+    count_launch();
+    return cudaGetLastError();
+  }
+}
+
+template <int N>
+cudaError_t dispatch_1d_tile(bool inverse, const FftParams& p, int T, cudaStream_t s) {
+  switch (T) {
+    case 1: return run_1d<N, 1>(inverse, p, s);
+    case 2: return run_1d<N, 2>(inverse, p, s);
+    case 4: return run_1d<N, 4>(inverse, p, s);
+    case 8: return run_1d<N, 8>(inverse, p, s);
+    case 16: return run_1d<N, 16>(inverse, p, s);
+  }
+  return cudaErrorInvalidConfiguration;
+}
+
+}  // namespace
+
+// Rows [0, rows) of `n` floats each, transform size N: full blocks of N rows, then the rest.
+cudaError_t launch_fft1d(bool inverse, const float* real_in, float* real_out, float2* spec, long long rows, int n,
+                         int N, int offset, cudaStream_t stream) {
+  const int KX = N / 2 + 1;
+  for (int part = 0; part < 2; ++part) {
+    const long long first = part == 0 ? 0 : rows / N * N;
+    const int h = part == 0 ? N : (int)(rows % N);
+    const long long planes = part == 0 ? rows / N : 1;
+    if (h == 0 || planes == 0) continue;
+    if (planes > 0x7fffffff) return cudaErrorInvalidValue;
+    FftParams p{};
+    p.real_in = real_in ? real_in + first * n : nullptr;
+    p.real_out = real_out ? real_out + first * n : nullptr;
+    p.spec = spec + first * KX;
+    p.h = h;
+    p.w = n;
+    p.off_y = 0;
+    p.off_x = offset;
+    p.n_rows = 1;
+    p.n_inner = (int)planes;
+    p.kc = (int)planes;
+    p.real_row_stride = 0;
+    p.real_inner_stride = 1;
+    const int T = inverse ? pick_inverse_tile(N, h, n) : pick_forward_tile(N, h, n, 0, offset);
+    if (T == 0) return cudaErrorInvalidConfiguration;
+    cudaError_t e;
+    switch (N) {
+      case 8: e = dispatch_1d_tile<8>(inverse, p, T, stream); break;
+      case 16: e = dispatch_1d_tile<16>(inverse, p, T, stream); break;
+      case 32: e = dispatch_1d_tile<32>(inverse, p, T, stream); break;
+      case 64: e = dispatch_1d_tile<64>(inverse, p, T, stream); break;
+      case 128: e = dispatch_1d_tile<128>(inverse, p, T, stream); break;
+      default: e = cudaErrorInvalidValue;
+    }
+    if (e != cudaSuccess) return e;
+  }
+  return cudaSuccess;
 }
 
 }  // namespace fbfft

@@ -17,6 +17,9 @@ int pick_forward_tile(int N, int h, int w, int pad_u, int pad_l);
 int pick_inverse_tile(int N, int oh, int ow);
 
 cudaError_t launch_forward(const FftParams& p, int N, cudaStream_t stream);
+// batched 1-D real <-> half-complex transforms of contiguous rows (the row phases of the 2-D kernels)
+cudaError_t launch_fft1d(bool inverse, const float* real_in, float* real_out, float2* spec, long long rows, int n,
+                         int N, int offset, cudaStream_t stream);
 cudaError_t launch_inverse(const FftParams& p, int N, cudaStream_t stream);
 
 struct ContractParams {

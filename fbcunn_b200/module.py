@@ -304,3 +304,70 @@ class FFTWrapper:
         out = torch.zeros((half * n, d1, (d2 + 3) // 4 * 4), dtype=torch.complex64, device=spec.device)
         out[:, :, :d2] = spec.permute(2, 3, 0, 1).reshape(half * n, d1, d2)
         return out
+
+    # -- the reference's tensor contract (fbcunn/FFTWrapper.lua:53-132) ----------------------
+    # time: (batch dims..., fft dims) real; frequency: the same with the first FFT dimension cut
+    # to N/2+1, plus a trailing 2 for (re, im).  One FFT dimension: frequency[b][k].  Two:
+    # sizes 8..32 keep the half spectrum along the first FFT dimension, frequency[b][i][j] =
+    # X[ky=i][kx=j]; the other sizes keep it along the second and store it transposed,
+    # frequency[b][i][j] = X[ky=j][kx=i] (test/test_FFTModule.lua:310-342).
+    @staticmethod
+    def _half_along_rows(n: int) -> bool:
+        return 8 <= n <= 32
+
+    def fft_reference_layout(self, time: torch.Tensor, frequency: torch.Tensor, batchDims: int):
+        assert 1 <= batchDims <= 2 and time.is_cuda and time.dtype == torch.float32 and time.is_contiguous()
+        fft_dims = time.dim() - batchDims
+        assert fft_dims in (1, 2) and frequency.shape[-1] == 2 and frequency.is_contiguous()
+        stream = _stream(time.device)
+        if fft_dims == 1:
+            n_fft = (frequency.shape[-2] - 1) * 2
+            rows = time.numel() // time.shape[-1]
+            capi.check(capi.lib().fbfftconv_fft1d(_ptr(time), _ptr(frequency), rows, time.shape[-1], n_fft,
+                                                  self.padLeft, stream))
+            return frequency
+        n_fft = frequency.shape[-2]
+        assert frequency.shape[-3] == n_fft // 2 + 1
+        h, w = time.shape[-2:]
+        planes = time.numel() // (h * w)
+        spec = self.frequency_tensor(1, planes, n_fft, device=time.device)
+        capi.check(capi.lib().fbfftconv_fft2d(_ptr(time), _ptr(spec), 1, planes, h, w, n_fft, self.padUp,
+                                              self.padLeft, 0, stream))
+        s = self.to_plane_major(spec, planes, n_fft)[0]            # planes, ky, kx (kx <= N/2)
+        if self._half_along_rows(n_fft):
+            # X[ky][kx] for ky <= N/2 and every kx: the columns beyond N/2 by Hermitian symmetry
+            idx = (n_fft - torch.arange(n_fft, device=time.device)) % n_fft
+            upper = s[:, idx][:, :, idx[n_fft // 2 + 1:]].conj()    # X[-ky][-kx], kx > N/2
+            full = torch.cat([s, upper], dim=2)                       # planes, ky, all kx
+            out = full[:, :n_fft // 2 + 1, :]
+        else:
+            out = s.transpose(1, 2)                                   # planes, kx, ky
+        frequency.copy_(torch.view_as_real(out.contiguous()).reshape(frequency.shape))
+        return frequency
+
+    def ffti_reference_layout(self, time: torch.Tensor, frequency: torch.Tensor, batchDims: int):
+        assert 1 <= batchDims <= 2 and time.is_cuda and time.dtype == torch.float32 and time.is_contiguous()
+        fft_dims = time.dim() - batchDims
+        assert fft_dims in (1, 2) and frequency.shape[-1] == 2 and frequency.is_contiguous()
+        stream = _stream(time.device)
+        if fft_dims == 1:
+            n_fft = (frequency.shape[-2] - 1) * 2
+            rows = time.numel() // time.shape[-1]
+            capi.check(capi.lib().fbfftconv_ifft1d(_ptr(frequency), _ptr(time), rows, time.shape[-1], n_fft,
+                                                   self.padLeft, stream))
+            return time
+        n_fft = frequency.shape[-2]
+        h, w = time.shape[-2:]
+        planes = time.numel() // (h * w)
+        f = torch.view_as_complex(frequency.reshape(planes, n_fft // 2 + 1, n_fft, 2))
+        if self._half_along_rows(n_fft):
+            # S[ky][kx], kx <= N/2: rows beyond N/2 by Hermitian symmetry
+            idx = (n_fft - torch.arange(n_fft, device=time.device)) % n_fft
+            lower = f[:, idx[n_fft // 2 + 1:]][:, :, idx].conj()      # X[ky > N/2][kx] = conj(X[-ky][-kx])
+            s = torch.cat([f, lower], dim=1)[:, :, :n_fft // 2 + 1]
+        else:
+            s = f.transpose(1, 2)
+        spec = self.from_plane_major(s.reshape(1, planes, n_fft, n_fft // 2 + 1).contiguous(), n_fft)
+        capi.check(capi.lib().fbfftconv_ifft2d(_ptr(spec), _ptr(time), None, 1, planes, h, w, n_fft, self.padUp,
+                                               self.padLeft, 0, 0, stream))
+        return time

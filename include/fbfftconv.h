@@ -164,6 +164,17 @@ int fbfftconv_fft2d(const float* real, void* spectrum, int d1, int d2, int h, in
 int fbfftconv_ifft2d(const void* spectrum, float* real, const float* bias, int d1, int d2, int h,
                      int w, int fft_size, int off_y, int off_x, int accumulate, int plane_major,
                      fbfftconv_stream stream);
+/* Replaces FFTWrapper_fft / FFTWrapper_ffti for the 1-D batched case
+ * (src/fft/FFTWrapperLua.cpp:209-272, fbfft1dHost in src/fft/FBFFTHost.cpp:119-160): `rows`
+ * contiguous rows of n floats, each placed at `pad_left` of a zero line of fft_size, ->
+ * spectrum[row][k], k in [0, fft_size/2], complex fp32: the reference's (batch, N/2+1, 2)
+ * tensor.  The inverse is un-normalised and keeps columns [offset, offset + n).
+ * fft_size in {8, 16, 32, 64, 128}. */
+int fbfftconv_fft1d(const float* real, void* spectrum, long long rows, int n, int fft_size,
+                    int pad_left, fbfftconv_stream stream);
+int fbfftconv_ifft1d(const void* spectrum, float* real, long long rows, int n, int fft_size,
+                     int offset, fbfftconv_stream stream);
+
 /* Replaces transposeMMFFI (fbcunn/FFTCDefs.lua:7-14, src/MM.cu:54-73) on bin-major
  * operands: for every bin  C[m][n] = alpha * sum_k opA(A[m][k]) * opB(B[n][k]),
  * op = complex conjugate when the flag is set.  A is [bins][m][k_padded],

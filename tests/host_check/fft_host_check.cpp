@@ -114,6 +114,80 @@ void run_inverse(const FftParams& p, int oh, int ow) {
   }
 }
 
+// The 1-D kernels: the row phases around Rows1D::store_spectrum / load_spectrum.
+template <int N, int T>
+void run_1d(bool inverse, const FftParams& p) {
+  const FftGeom g = inverse ? inverse_geom(N, T, p.h, p.w) : forward_geom(N, T, p.h, p.w, 0, p.off_x);
+  const int tiles = (p.n_inner + T - 1) / T;
+  std::vector<char> smem(g.smem_bytes);
+  std::vector<LineRegs<N>> regs(g.threads);
+  const int nth = g.threads;
+  for (int tile = 0; tile < tiles; ++tile) {
+    const int inner0 = tile * T;
+    std::memset(smem.data(), 0xFF, smem.size());
+    if (!inverse) {
+      if constexpr (N <= 32) {
+        for (int tid = 0; tid < nth; ++tid) Forward<N, T>::load(p, g, smem.data(), tid, nth, 0, inner0);
+        for (int tid = 0; tid < nth; ++tid) Forward<N, T>::row_fetch(p, g, smem.data(), tid, 0, inner0, regs[tid]);
+        std::memset(smem.data(), 0xFF, smem.size());
+        for (int tid = 0; tid < nth; ++tid) Forward<N, T>::row_pass(g, smem.data(), tid, regs[tid]);
+      } else {
+        constexpr int N1 = CoopForward<N, T>::N1, N2 = CoopForward<N, T>::N2;
+        for (int line0 = 0; line0 < g.lines1; line0 += g.chunk) {
+          const int nl = std::min(g.chunk, g.lines1 - line0);
+          for (int tid = 0; tid < nth; ++tid)
+            CoopForward<N, T>::row_step1(p, g, smem.data(), tid, nth, 0, inner0, line0, nl);
+          const int items = nl * N1;
+          std::vector<float2> all(static_cast<size_t>(items) * N2);
+          for (int item = 0; item < items; ++item) {
+            float2 u[N2];
+            CoopForward<N, T>::row_step2_fft(g, smem.data(), item, nl, u);
+            std::copy(u, u + N2, all.begin() + static_cast<size_t>(item) * N2);
+          }
+          for (int item = 0; item < items; ++item) {
+            float2 u[N2], mirror_odd[N2 / 2];
+            std::copy(all.begin() + static_cast<size_t>(item) * N2, all.begin() + static_cast<size_t>(item + 1) * N2, u);
+            const int partner = item ^ 1;
+            for (int i = 0; i < N2 / 2; ++i)
+              mirror_odd[i] = partner < items ? all[static_cast<size_t>(partner) * N2 + 2 * i + 1] : make_float2(NAN, NAN);
+            CoopForward<N, T>::row_step2_split(g, smem.data(), item, line0, u, mirror_odd);
+          }
+        }
+      }
+      for (int tid = 0; tid < nth; ++tid) Rows1D<N, T>::store_spectrum(p, g, smem.data(), tid, nth, inner0);
+    } else {
+      for (int tid = 0; tid < nth; ++tid) Rows1D<N, T>::load_spectrum(p, g, smem.data(), tid, nth, inner0);
+      if constexpr (N <= 32) {
+        for (int tid = 0; tid < nth; ++tid) Inverse<N, T>::row_fetch(g, smem.data(), tid, regs[tid]);
+        std::memset(smem.data(), 0xFF, smem.size());
+        for (int tid = 0; tid < nth; ++tid) Inverse<N, T>::row_pass(p, g, smem.data(), tid, 0, inner0, regs[tid]);
+        for (int tid = 0; tid < nth; ++tid) Inverse<N, T>::store(p, g, smem.data(), tid, nth, 0, inner0);
+      } else {
+        for (int line0 = 0; line0 < g.lines1; line0 += g.chunk) {
+          const int nl = std::min(g.chunk, g.lines1 - line0);
+          std::memset(smem.data() + g.off_a, 0xFF, g.off_b - g.off_a);
+          for (int tid = 0; tid < nth; ++tid) CoopInverse<N, T>::row_step1(p, g, smem.data(), tid, nth, line0, nl);
+          for (int tid = 0; tid < nth; ++tid)
+            CoopInverse<N, T>::row_step2(p, g, smem.data(), tid, nth, 0, inner0, line0, nl);
+        }
+      }
+    }
+  }
+}
+
+template <int N>
+int dispatch_1d_t(bool inverse, const FftParams& p, int T) {
+  if (cooperative(N) && T > 8) return 2;
+  switch (T) {
+    case 1: run_1d<N, 1>(inverse, p); return 0;
+    case 2: run_1d<N, 2>(inverse, p); return 0;
+    case 4: run_1d<N, 4>(inverse, p); return 0;
+    case 8: run_1d<N, 8>(inverse, p); return 0;
+    case 16: if constexpr (N <= 32) { run_1d<N, 16>(inverse, p); return 0; } else { return 2; }
+  }
+  return 2;
+}
+
 template <int N>
 int dispatch_t(bool inverse, const FftParams& p, int T, int oh, int ow) {
 #define FBF_CASE(TT)                                  \
@@ -158,6 +232,25 @@ void set_layout(FftParams& p, int N, int plane_major) {
 }  // namespace
 
 extern "C" {
+
+// rows of n floats <-> rows of N/2+1 complex values; h rows per block, `planes` blocks
+int hostcheck_fft1d(int inverse, float* real, float* spec, int N, int T, int h, int n, int offset, int planes) {
+  FftParams p{};
+  p.real_in = real;
+  p.real_out = real;
+  p.spec = reinterpret_cast<float2*>(spec);
+  p.h = h; p.w = n; p.off_y = 0; p.off_x = offset;
+  p.n_rows = 1; p.n_inner = planes; p.kc = planes;
+  p.real_row_stride = 0; p.real_inner_stride = 1;
+  switch (N) {
+    case 8: return dispatch_1d_t<8>(inverse != 0, p, T);
+    case 16: return dispatch_1d_t<16>(inverse != 0, p, T);
+    case 32: return dispatch_1d_t<32>(inverse != 0, p, T);
+    case 64: return dispatch_1d_t<64>(inverse != 0, p, T);
+    case 128: return dispatch_1d_t<128>(inverse != 0, p, T);
+  }
+  return 1;
+}
 
 int hostcheck_fft_forward(const float* real, float* spec, int N, int T, int h, int w, int pad_u,
                           int pad_l, int n_rows, int n_inner, int kc, long long row_stride,

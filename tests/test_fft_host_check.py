@@ -111,3 +111,30 @@ def test_plane_major_layout(hc, N, T):
                                   N, T, h, w, pu, pl, d1, d2, d2, LL(d2), LL(1), 0, 1)
     assert rc == 0
     assert np.abs(out / (N * N) - x).max() <= 5e-6 * np.abs(x).max()
+
+
+@pytest.mark.parametrize("N,T", [(8, 16), (16, 4), (32, 16), (64, 2), (64, 8), (128, 1), (128, 2)])
+def test_1d_transforms(hc, N, T):
+    """The batched 1-D kernels (row phases + plain store / load of the column buffer) against numpy."""
+    rng = np.random.default_rng(N + T)
+    for (h, n, off, planes) in [(N, N, 0, 3), (5, N - 3, 2, 2), (1, 1, 0, 1), (N, 7, 0, 5)]:
+        if hc.hostcheck_forward_smem_bytes(N, T, h, n, 0, off) > 227 * 1024:
+            continue
+        x = rng.standard_normal((planes * h, n)).astype(np.float32)
+        spec = np.full((planes * h, N // 2 + 1, 2), np.nan, np.float32)
+        assert hc.hostcheck_fft1d(0, x.ctypes.data_as(ctypes.c_void_p), spec.ctypes.data_as(ctypes.c_void_p),
+                                  N, T, h, n, off, planes) == 0
+        padded = np.zeros((planes * h, N))
+        padded[:, off:off + n] = x
+        ref = np.fft.rfft(padded, axis=1)
+        got = spec[..., 0] + 1j * spec[..., 1]
+        assert np.abs(got - ref).max() <= 3e-6 * max(np.abs(ref).max(), 1.0)
+        # inverse: un-normalised, cropped to [off, off + n)
+        full = rng.standard_normal((planes * h, N))
+        sp = np.fft.rfft(full, axis=1)
+        spec2 = np.stack([sp.real, sp.imag], axis=-1).astype(np.float32)
+        out = np.full((planes * h, n), np.nan, np.float32)
+        assert hc.hostcheck_fft1d(1, out.ctypes.data_as(ctypes.c_void_p), spec2.ctypes.data_as(ctypes.c_void_p),
+                                  N, T, h, n, off, planes) == 0
+        ref_t = N * full[:, off:off + n]
+        assert np.abs(out - ref_t).max() <= 3e-6 * np.abs(ref_t).max() * N
