@@ -607,11 +607,7 @@ struct CoopForward {
     for (int n1 = 0; n1 < N1; ++n1) {
       const int x = N2 * n1 + n2 - p.off_x;
       const bool vx = x >= 0 && x < p.w;
-#ifdef FBF_EXP_NOLOAD
-      r.v[n1] = make_float2(va && vx ? 1.f + x : 0.f, vb && vx ? 2.f + x : 0.f);
-#else
       r.v[n1] = make_float2(va && vx ? pa[N2 * n1] : 0.f, vb && vx ? pb[N2 * n1] : 0.f);
-#endif
     }
     r.slot = ll * L::PITCH1 + n2;
     r.n2 = n2;
@@ -619,14 +615,6 @@ struct CoopForward {
 
   static FBF_HD void row_transform(float2* rb, RowLoad& r, const float2 (&tw)[N1]) {
     if (r.slot < 0) return;
-#ifdef FBF_EXP_NOFFT
-    {
-      float2* dst0 = rb + r.slot;
-#pragma unroll
-      for (int k1 = 0; k1 < N1; ++k1) dst0[k1 * (N2 + 1)] = r.v[k1];
-      return;
-    }
-#endif
     fft_inreg<N1, false>(r.v);
     float2* dst = rb + r.slot;
     dst[0] = r.v[0];
