@@ -295,6 +295,36 @@ class LayerRun:
         return self.m._handle
 
 
+def step_times(torch, capi, lib, run, iters):
+    """ms per step of three passes launched back to back (no flush, no profiling events), and the
+    same step replayed from a CUDA graph: what launch gaps cost on the small layers."""
+    capi.check(lib.fbfftconv_profile_enable(run.handle(), 0))
+    out = {}
+
+    def timed(fn):
+        fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(max(iters, 5)):
+            fn()
+        b.record()
+        b.synchronize()
+        return a.elapsed_time(b) / max(iters, 5)
+
+    out["eager"] = timed(run.step)
+    try:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            run.step()
+        out["cuda_graph"] = timed(graph.replay)
+    except Exception as e:  # a capture the runtime refuses is reported, not fatal
+        out["cuda_graph"] = None
+        out["cuda_graph_error"] = str(e).splitlines()[0][:200]
+        torch.cuda.synchronize()
+    return out
+
+
 def read_profile(handle):
     from fbcunn_b200 import capi
     out = {}
@@ -472,6 +502,8 @@ def run_gpu_arm(args):
             prof_l = read_profile(r.handle())
             layers[lname] = {"fft_size": fft_size(LL), "local_batch": lb, "passes": per_pass,
                              "kernels": kernel_table(LL, lb, prof_l, pk)}
+            if world == 1:
+                layers[lname]["step_ms"] = step_times(torch, capi, lib, r, args.layer_iters)
             del r
             torch.cuda.empty_cache()
 

@@ -194,8 +194,16 @@ cudaError_t launch_stream_reduce(const float2* x, const float2* y, float2* z, in
   // otherwise be twice the DRAM traffic; with few rows (a small batch shard) fewer rows per
   // block keep every SM busy instead.
   auto blocks_for = [&](int nt, int tu) { return (long long)((bins / 2 + nt - 1) / nt) * ((U + tu - 1) / tu); };
-  const int tu = blocks_for(128, 4) >= 3 * 148 ? 4 : blocks_for(256, 2) >= 2 * 148 ? 2 : 1;
-  const int nt = tu == 4 ? 128 : 256;
+  // most rows per block that still gives every SM three blocks; 128-thread blocks below that
+  int tu = 1, nt = 128;
+  if (blocks_for(128, 4) >= 3 * 148) {
+    tu = 4;
+  } else if (blocks_for(256, 2) >= 2 * 148) {
+    tu = 2;
+    nt = 256;
+  } else if (blocks_for(128, 2) >= 3 * 148) {
+    tu = 2;
+  }
   dim3 grid((unsigned)((bins / 2 + nt - 1) / nt), (U + tu - 1) / tu);
   if (grid.y > 65535) return cudaErrorInvalidValue;
   auto launch = [&](auto kernel) -> cudaError_t {
@@ -208,10 +216,12 @@ cudaError_t launch_stream_reduce(const float2* x, const float2* y, float2* z, in
   cudaError_t e;
   if (tu == 4)
     e = conj_x ? launch(stream_reduce_kernel<4, true, 128>) : launch(stream_reduce_kernel<4, false, 128>);
-  else if (tu == 2)
+  else if (tu == 2 && nt == 256)
     e = conj_x ? launch(stream_reduce_kernel<2, true, 256>) : launch(stream_reduce_kernel<2, false, 256>);
+  else if (tu == 2)
+    e = conj_x ? launch(stream_reduce_kernel<2, true, 128>) : launch(stream_reduce_kernel<2, false, 128>);
   else
-    e = conj_x ? launch(stream_reduce_kernel<1, true, 256>) : launch(stream_reduce_kernel<1, false, 256>);
+    e = conj_x ? launch(stream_reduce_kernel<1, true, 128>) : launch(stream_reduce_kernel<1, false, 128>);
   if (e != cudaSuccess) return e;
   count_launch();
   return cudaGetLastError();

@@ -298,6 +298,37 @@ def test_spectrum_reuse_across_the_passes_of_a_step(plane_major):
     assert _rel(m2.gradWeight.cpu().numpy(), oracle.acc_grad_weight(s, x, go, 0.8)) <= PASS_TOL
 
 
+@pytest.mark.parametrize("shape", [oracle.Shape(4, 8, 12, 14, 14, 3, 3, 1, 1), oracle.Shape(2, 3, 4, 40, 40, 5, 5, 0, 0)])
+def test_passes_replay_from_a_cuda_graph(shape):
+    """After the first call a pass allocates nothing and only enqueues work on the caller's stream,
+    so a training step can be captured once and replayed: small layers are bound by launch gaps."""
+    s = shape
+    x, w, go, b = _data(s, 31, bias=True)
+    m = _module(s, w, b)
+    dx, dgo = _dev(x), _dev(go)
+    m.updateOutput(dx)
+    m.updateGradInput(dx, dgo)
+    m.accGradParameters(dx, dgo, 1.0)          # warm: workspace and staging exist now
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        m.updateOutput(dx)
+        m.updateGradInput(dx, dgo)
+        m.accGradParameters(dx, dgo, 1.0)
+    x2, _, go2, _ = _data(s, 32, bias=True)     # new contents in the captured buffers
+    dx.copy_(_dev(x2))
+    dgo.copy_(_dev(go2))
+    m.output.zero_()
+    m.gradInput.zero_()
+    m.gradWeight.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    assert _rel(m.output.cpu().numpy(), oracle.update_output(s, x2, w, b)) <= PASS_TOL
+    assert _rel(m.gradInput.cpu().numpy(), oracle.update_grad_input(s, go2, w)) <= PASS_TOL
+    assert _rel(m.gradWeight.cpu().numpy(), oracle.acc_grad_weight(s, x2, go2, 1.0)) <= PASS_TOL
+    assert _rel(m.gradBias.cpu().numpy(), oracle.acc_grad_bias(s, go2, 1.0)) <= PASS_TOL
+
+
 def test_random_sweep():
     """Recipe of test/test_FFT.lua:82-107: B = 4*rand(4), planes <= 13, k <= 7, pad <= min(4, k-1)."""
     rng = np.random.default_rng(424242)
