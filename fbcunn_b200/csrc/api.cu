@@ -129,6 +129,9 @@ struct fbfftconv_handle {
   // device copies for the host-buffer entry points
   char* stage = nullptr;
   size_t stage_bytes = 0;
+  // second stream for the second forward transform of a pass, when the two together fit the GPU
+  cudaStream_t aux = nullptr;
+  cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
   // communicator
   ncclComm_t comm = nullptr;
   std::string comm_key;
@@ -183,6 +186,50 @@ struct StageTimer {
     if (ev) cudaEventRecord(ev->stop, s);
   }
 };
+
+// The two forward transforms of a pass are independent.  Where at least one of them is too
+// small to fill the GPU by itself (small layers, small batch shards) the second runs on the
+// handle's own stream between an event fork and join, so the two overlap; the pattern is
+// capturable in a CUDA graph.  Large transforms stay in order on the caller's stream.
+struct Fork {
+  fbfftconv_handle* h;
+  cudaStream_t main;
+  bool active = false;
+  Fork(fbfftconv_handle* h_, cudaStream_t s, long long tiles_a, long long tiles_b) : h(h_), main(s) {
+    constexpr long long kFillsTheGpu = 4 * 148;
+    if (tiles_a >= kFillsTheGpu && tiles_b >= kFillsTheGpu) return;
+    if (!h->aux) {
+      if (cudaStreamCreateWithFlags(&h->aux, cudaStreamNonBlocking) != cudaSuccess ||
+          cudaEventCreateWithFlags(&h->ev_fork, cudaEventDisableTiming) != cudaSuccess ||
+          cudaEventCreateWithFlags(&h->ev_join, cudaEventDisableTiming) != cudaSuccess) {
+        cudaGetLastError();
+        return;  // stay on one stream
+      }
+    }
+    if (cudaEventRecord(h->ev_fork, main) != cudaSuccess || cudaStreamWaitEvent(h->aux, h->ev_fork, 0) != cudaSuccess) {
+      cudaGetLastError();
+      return;
+    }
+    active = true;
+  }
+  cudaStream_t second() const { return active ? h->aux : main; }
+  cudaError_t join() {
+    if (!active) return cudaSuccess;
+    active = false;
+    cudaError_t e = cudaEventRecord(h->ev_join, h->aux);
+    if (e != cudaSuccess) return e;
+    return cudaStreamWaitEvent(main, h->ev_join, 0);
+  }
+  ~Fork() { join(); }  // an early return between fork and join must not leave the streams apart
+};
+
+// Tiles (blocks of work) of a forward transform of d1 x d2 planes.
+long long forward_tiles(int N, int d1, int d2, int h, int w, int pad_u, int pad_l, bool transposed) {
+  const int T = pick_forward_tile(N, h, w, pad_u, pad_l);
+  if (T <= 0) return 1LL << 40;
+  const long long rows = transposed ? d2 : d1, inner = transposed ? d1 : d2;
+  return rows * ((inner + T - 1) / T);
+}
 
 struct DeviceGuard {
   int prev = -1;
@@ -397,6 +444,9 @@ int fbfftconv_destroy(fbfftconv_handle* h) {
   release_comm(h);
   if (h->ws && h->ws_owned) cudaFree(h->ws);
   if (h->stage) cudaFree(h->stage);
+  if (h->aux) cudaStreamDestroy(h->aux);
+  if (h->ev_fork) cudaEventDestroy(h->ev_fork);
+  if (h->ev_join) cudaEventDestroy(h->ev_join);
   for (auto& per_pass : h->events)
     for (auto& pool : per_pass)
       for (auto& p : pool) {
@@ -442,12 +492,17 @@ int fbfftconv_update_output(fbfftconv_handle* h, const float* input, const float
   const float norm = 1.0f / (float)(h->N * h->N);
   // I^[bin][b][p], W^[bin][f][p]   (plane-major: I^[b][p][bin], W^[f][p][bin])
   {
-    StageTimer t(h, pass, FBFFTCONV_STAGE_FFT_A, s);
-    FBF_CUDA(launch_forward(forward_params(input, h->buf_in(), B, P, d.input_h, d.input_w, d.pad_h, d.pad_w, pm ? 2 : 0, h->N), h->N, s));
-  }
-  {
-    StageTimer t(h, pass, FBFFTCONV_STAGE_FFT_B, s);
-    FBF_CUDA(launch_forward(forward_params(weight, h->buf_w(), F, P, d.kernel_h, d.kernel_w, 0, 0, pm ? 2 : 0, h->N), h->N, s));
+    Fork fork(h, s, forward_tiles(h->N, B, P, d.input_h, d.input_w, d.pad_h, d.pad_w, false),
+              forward_tiles(h->N, F, P, d.kernel_h, d.kernel_w, 0, 0, false));
+    {
+      StageTimer t(h, pass, FBFFTCONV_STAGE_FFT_A, s);
+      FBF_CUDA(launch_forward(forward_params(input, h->buf_in(), B, P, d.input_h, d.input_w, d.pad_h, d.pad_w, pm ? 2 : 0, h->N), h->N, s));
+    }
+    {
+      StageTimer t(h, pass, FBFFTCONV_STAGE_FFT_B, fork.second());
+      FBF_CUDA(launch_forward(forward_params(weight, h->buf_w(), F, P, d.kernel_h, d.kernel_w, 0, 0, pm ? 2 : 0, h->N), h->N, fork.second()));
+    }
+    FBF_CUDA(fork.join());
   }
   // O^[b][f] = 1/N^2 sum_p I^[b][p] conj(W^[f][p]) per bin
   {
@@ -485,14 +540,19 @@ int fbfftconv_update_grad_input(fbfftconv_handle* h, const float* grad_output, c
   const float norm = 1.0f / (float)(h->N * h->N);
   // O'^[bin][b][f], W^[bin][p][f] (weight planes transposed on the fly)
   {
-    StageTimer t(h, pass, FBFFTCONV_STAGE_FFT_A, s);
-    FBF_CUDA(launch_forward(forward_params(grad_output, h->buf_out(), B, F, h->oH, h->oW, 0, 0, pm ? 2 : 0, h->N), h->N, s));
-  }
-  h->have_grad_output_spec = pm;
-  if (!(pm && (d.flags & FBFFTCONV_REUSE_WEIGHT) && h->have_weight_spec)) {
-    StageTimer t(h, pass, FBFFTCONV_STAGE_FFT_B, s);
-    FBF_CUDA(launch_forward(forward_params(weight, h->buf_w(), F, P, d.kernel_h, d.kernel_w, 0, 0, pm ? 2 : 1, h->N), h->N, s));
-    h->have_weight_spec = pm;
+    Fork fork(h, s, forward_tiles(h->N, B, F, h->oH, h->oW, 0, 0, false),
+              forward_tiles(h->N, F, P, d.kernel_h, d.kernel_w, 0, 0, !pm));
+    {
+      StageTimer t(h, pass, FBFFTCONV_STAGE_FFT_A, s);
+      FBF_CUDA(launch_forward(forward_params(grad_output, h->buf_out(), B, F, h->oH, h->oW, 0, 0, pm ? 2 : 0, h->N), h->N, s));
+    }
+    h->have_grad_output_spec = pm;
+    if (!(pm && (d.flags & FBFFTCONV_REUSE_WEIGHT) && h->have_weight_spec)) {
+      StageTimer t(h, pass, FBFFTCONV_STAGE_FFT_B, fork.second());
+      FBF_CUDA(launch_forward(forward_params(weight, h->buf_w(), F, P, d.kernel_h, d.kernel_w, 0, 0, pm ? 2 : 1, h->N), h->N, fork.second()));
+      h->have_weight_spec = pm;
+    }
+    FBF_CUDA(fork.join());
   }
   // with REUSE_INPUT the input spectrum stays in its buffer for accGradParameters
   float2* gi = h->buf_gi();
@@ -530,15 +590,20 @@ int fbfftconv_acc_grad_parameters(fbfftconv_handle* h, const float* input, const
   const int pass = FBFFTCONV_PASS_ACC_GRAD_PARAMETERS;
   const bool pm = h->plane_major;
   // O'^[bin][f][b], I^[bin][p][b]: the batch is the contraction index here
-  if (!(pm && (d.flags & FBFFTCONV_REUSE_OUTPUT) && h->have_grad_output_spec)) {
-    StageTimer t(h, pass, FBFFTCONV_STAGE_FFT_A, s);
-    FBF_CUDA(launch_forward(forward_params(grad_output, h->buf_out(), B, F, h->oH, h->oW, 0, 0, pm ? 2 : 1, h->N), h->N, s));
-    h->have_grad_output_spec = pm;
-  }
-  if (!(pm && (d.flags & FBFFTCONV_REUSE_INPUT) && h->have_input_spec)) {
-    StageTimer t(h, pass, FBFFTCONV_STAGE_FFT_B, s);
-    FBF_CUDA(launch_forward(forward_params(input, h->buf_in(), B, P, d.input_h, d.input_w, d.pad_h, d.pad_w, pm ? 2 : 1, h->N), h->N, s));
-    h->have_input_spec = pm;
+  {
+    Fork fork(h, s, forward_tiles(h->N, B, F, h->oH, h->oW, 0, 0, !pm),
+              forward_tiles(h->N, B, P, d.input_h, d.input_w, d.pad_h, d.pad_w, !pm));
+    if (!(pm && (d.flags & FBFFTCONV_REUSE_OUTPUT) && h->have_grad_output_spec)) {
+      StageTimer t(h, pass, FBFFTCONV_STAGE_FFT_A, s);
+      FBF_CUDA(launch_forward(forward_params(grad_output, h->buf_out(), B, F, h->oH, h->oW, 0, 0, pm ? 2 : 1, h->N), h->N, s));
+      h->have_grad_output_spec = pm;
+    }
+    if (!(pm && (d.flags & FBFFTCONV_REUSE_INPUT) && h->have_input_spec)) {
+      StageTimer t(h, pass, FBFFTCONV_STAGE_FFT_B, fork.second());
+      FBF_CUDA(launch_forward(forward_params(input, h->buf_in(), B, P, d.input_h, d.input_w, d.pad_h, d.pad_w, pm ? 2 : 1, h->N), h->N, fork.second()));
+      h->have_input_spec = pm;
+    }
+    FBF_CUDA(fork.join());
   }
   h->have_weight_spec = false;  // the weight buffer receives the gradient spectrum below
   NcclApi* api = h->comm ? nccl_api() : nullptr;
