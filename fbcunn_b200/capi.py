@@ -74,6 +74,7 @@ _SIGNATURES = {
     "fbfftconv_profile_enable": (c_int, [c_void_p, c_int]),
     "fbfftconv_profile_reset": (c_int, [c_void_p]),
     "fbfftconv_profile_read": (c_int, [c_void_p, c_int, c_int, POINTER(ctypes.c_double), POINTER(c_int)]),
+    "fbfftconv_profile_overlapped": (c_int, [c_void_p, c_int, c_int]),
     "fbfftconv_comm_unique_id": (c_int, [c_void_p]),
     "fbfftconv_comm_init": (c_int, [c_void_p, c_void_p, c_int, c_int]),
     "fbfftconv_comm_destroy": (c_int, [c_void_p]),

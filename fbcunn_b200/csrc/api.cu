@@ -116,6 +116,7 @@ struct fbfftconv_handle {
   bool profiling = false;
   std::vector<EventPair> events[3][FBFFTCONV_STAGE_COUNT];
   int events_used[3][FBFFTCONV_STAGE_COUNT] = {};
+  bool overlapped[3][FBFFTCONV_STAGE_COUNT] = {};  // stage ran on the second stream since the last reset
   int device;
   int N, bins;
   int oH, oW;
@@ -500,6 +501,7 @@ int fbfftconv_update_output(fbfftconv_handle* h, const float* input, const float
     }
     {
       StageTimer t(h, pass, FBFFTCONV_STAGE_FFT_B, fork.second());
+      if (fork.active) h->overlapped[pass][FBFFTCONV_STAGE_FFT_B] = true;
       FBF_CUDA(launch_forward(forward_params(weight, h->buf_w(), F, P, d.kernel_h, d.kernel_w, 0, 0, pm ? 2 : 0, h->N), h->N, fork.second()));
     }
     FBF_CUDA(fork.join());
@@ -549,6 +551,7 @@ int fbfftconv_update_grad_input(fbfftconv_handle* h, const float* grad_output, c
     h->have_grad_output_spec = pm;
     if (!(pm && (d.flags & FBFFTCONV_REUSE_WEIGHT) && h->have_weight_spec)) {
       StageTimer t(h, pass, FBFFTCONV_STAGE_FFT_B, fork.second());
+      if (fork.active) h->overlapped[pass][FBFFTCONV_STAGE_FFT_B] = true;
       FBF_CUDA(launch_forward(forward_params(weight, h->buf_w(), F, P, d.kernel_h, d.kernel_w, 0, 0, pm ? 2 : 1, h->N), h->N, fork.second()));
       h->have_weight_spec = pm;
     }
@@ -600,6 +603,7 @@ int fbfftconv_acc_grad_parameters(fbfftconv_handle* h, const float* input, const
     }
     if (!(pm && (d.flags & FBFFTCONV_REUSE_INPUT) && h->have_input_spec)) {
       StageTimer t(h, pass, FBFFTCONV_STAGE_FFT_B, fork.second());
+      if (fork.active) h->overlapped[pass][FBFFTCONV_STAGE_FFT_B] = true;
       FBF_CUDA(launch_forward(forward_params(input, h->buf_in(), B, P, d.input_h, d.input_w, d.pad_h, d.pad_w, pm ? 2 : 1, h->N), h->N, fork.second()));
       h->have_input_spec = pm;
     }
@@ -874,7 +878,13 @@ int fbfftconv_profile_enable(fbfftconv_handle* h, int enable) {
 int fbfftconv_profile_reset(fbfftconv_handle* h) {
   if (!h) return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "null handle");
   memset(h->events_used, 0, sizeof(h->events_used));
+  memset(h->overlapped, 0, sizeof(h->overlapped));
   return FBFFTCONV_OK;
+}
+
+int fbfftconv_profile_overlapped(const fbfftconv_handle* h, int pass, int stage) {
+  if (!h || pass < 0 || pass > 2 || stage < 0 || stage >= FBFFTCONV_STAGE_COUNT) return -1;
+  return h->overlapped[pass][stage] ? 1 : 0;
 }
 
 int fbfftconv_profile_read(fbfftconv_handle* h, int pass, int stage, double* total_ms, int* launches) {

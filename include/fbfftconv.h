@@ -248,6 +248,10 @@ enum {
 int fbfftconv_profile_enable(fbfftconv_handle* h, int enable);
 int fbfftconv_profile_reset(fbfftconv_handle* h);
 int fbfftconv_profile_read(fbfftconv_handle* h, int pass, int stage, double* total_ms, int* launches);
+/* 1 if launches of this stage since the last reset ran next to another stage of the pass on the
+ * handle's second stream (a small second forward transform): its time then overlaps the other
+ * stage's and is not its cost alone.  0 otherwise, negative on a bad query. */
+int fbfftconv_profile_overlapped(const fbfftconv_handle* h, int pass, int stage);
 
 /* ---- diagnostics ------------------------------------------------------------ */
 const char* fbfftconv_last_error(void);
