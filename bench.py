@@ -556,25 +556,41 @@ def measure_e2e(torch, lib, run, L, local_b, world, barrier, max_over_ranks, ste
     st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
     h = run.handle()
 
-    def step():
+    def step_sync():
         capi.check(lib.fbfftconv_update_output_host(h, p(hx), p(hw), p(hb) if has_bias else None, p(hout), st))
         capi.check(lib.fbfftconv_update_grad_input_host(h, p(hgo), p(hw), p(hgi), st))
         capi.check(lib.fbfftconv_acc_grad_parameters_host(h, p(hx), p(hgo), p(hgw), p(hgb), ctypes.c_float(1.0), st))
 
-    step()
-    barrier()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    for _ in range(steps):
+    def step_async():
+        # the three passes enqueue uploads, kernels and downloads on three streams; the step's results
+        # are read (waited for) once per step
+        capi.check(lib.fbfftconv_update_output_host_async(h, p(hx), p(hw), p(hb) if has_bias else None, p(hout), st))
+        capi.check(lib.fbfftconv_update_grad_input_host_async(h, p(hgo), p(hw), p(hgi), st))
+        capi.check(lib.fbfftconv_acc_grad_parameters_host_async(h, p(hx), p(hgo), p(hgw), p(hgb),
+                                                                ctypes.c_float(1.0), st))
+        capi.check(lib.fbfftconv_host_sync(h))
+
+    def timed(step):
         step()
-    b.record()
-    barrier()
-    ms = max_over_ranks(a.elapsed_time(b)) / steps
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            step()  # ends with a host-side wait for the step's downloads
+        b.record()
+        barrier()
+        return max_over_ranks(a.elapsed_time(b)) / steps
+
+    ms_sync = timed(step_sync)
+    ms = timed(step_async)
     h2d = 4 * (2 * hx.numel() + 2 * hgo.numel() + 2 * hw.numel() + (hb.numel() if has_bias else 0))
     d2h = 4 * (hout.numel() + hgi.numel() + hgw.numel() + hgb.numel())
     return {"value": 3.0 * conv_flops(L) / (ms / 1e3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms,
             "h2d_bytes_per_step": int(h2d) * world, "d2h_bytes_per_step": int(d2h) * world,
-            "api": "fbfftconv_update_output_host / _update_grad_input_host / _acc_grad_parameters_host, pinned host buffers"}
+            "api": "fbfftconv_update_output_host_async / _update_grad_input_host_async / "
+                   "_acc_grad_parameters_host_async + fbfftconv_host_sync once per step, pinned host buffers",
+            "call_by_call_ms_per_step": ms_sync,
+            "call_by_call_api": "fbfftconv_*_host: each call waits for its own download"}
 
 
 def main():

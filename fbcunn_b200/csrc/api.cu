@@ -130,6 +130,13 @@ struct fbfftconv_handle {
   // device copies for the host-buffer entry points
   char* stage = nullptr;
   size_t stage_bytes = 0;
+  // asynchronous host-buffer passes: staging per pass, an upload and a download stream, and per
+  // pass the events 'kernels done' (its input staging may be overwritten) and 'download done'
+  // (its output staging may be overwritten)
+  char* astage[3] = {nullptr, nullptr, nullptr};
+  cudaStream_t up = nullptr, down = nullptr;
+  cudaEvent_t ev_up = nullptr, ev_kernels[3] = {nullptr, nullptr, nullptr}, ev_down[3] = {nullptr, nullptr, nullptr};
+  bool async_used[3] = {false, false, false};
   // second stream for the second forward transform of a pass, when the two together fit the GPU
   cudaStream_t aux = nullptr;
   cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
@@ -445,6 +452,14 @@ int fbfftconv_destroy(fbfftconv_handle* h) {
   release_comm(h);
   if (h->ws && h->ws_owned) cudaFree(h->ws);
   if (h->stage) cudaFree(h->stage);
+  for (int i = 0; i < 3; ++i) {
+    if (h->astage[i]) cudaFree(h->astage[i]);
+    if (h->ev_kernels[i]) cudaEventDestroy(h->ev_kernels[i]);
+    if (h->ev_down[i]) cudaEventDestroy(h->ev_down[i]);
+  }
+  if (h->ev_up) cudaEventDestroy(h->ev_up);
+  if (h->up) cudaStreamDestroy(h->up);
+  if (h->down) cudaStreamDestroy(h->down);
   if (h->aux) cudaStreamDestroy(h->aux);
   if (h->ev_fork) cudaEventDestroy(h->ev_fork);
   if (h->ev_join) cudaEventDestroy(h->ev_join);
@@ -784,6 +799,167 @@ int fbfftconv_acc_grad_parameters_host(fbfftconv_handle* h, const float* input,
   FBF_CUDA(cudaMemcpyAsync(grad_weight, dw, n_w * 4, cudaMemcpyDeviceToHost, s));
   if (grad_bias) FBF_CUDA(cudaMemcpyAsync(grad_bias, dgb, (size_t)d.n_output_plane * 4, cudaMemcpyDeviceToHost, s));
   FBF_CUDA(cudaStreamSynchronize(s));
+  return FBFFTCONV_OK;
+}
+
+// ---- asynchronous host-buffer variants ----------------------------------------
+
+namespace {
+
+int ensure_async(fbfftconv_handle* h, int pass) {
+  if (!h->up) {
+    FBF_CUDA(cudaStreamCreateWithFlags(&h->up, cudaStreamNonBlocking));
+    FBF_CUDA(cudaStreamCreateWithFlags(&h->down, cudaStreamNonBlocking));
+    FBF_CUDA(cudaEventCreateWithFlags(&h->ev_up, cudaEventDisableTiming));
+    for (int i = 0; i < 3; ++i) {
+      FBF_CUDA(cudaEventCreateWithFlags(&h->ev_kernels[i], cudaEventDisableTiming));
+      FBF_CUDA(cudaEventCreateWithFlags(&h->ev_down[i], cudaEventDisableTiming));
+    }
+  }
+  if (!h->astage[pass]) {
+    void* p = nullptr;
+    const size_t bytes = stage_layout(h).total;
+    cudaError_t e = cudaMalloc(&p, bytes);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return fail(FBFFTCONV_ERR_NOMEM, "staging of %zu bytes: %s", bytes, cudaGetErrorString(e));
+    }
+    h->astage[pass] = static_cast<char*>(p);
+  }
+  return FBFFTCONV_OK;
+}
+
+// Order of one asynchronous pass: uploads (after the kernels of this pass's previous use have
+// read the staging) -> kernels on the caller's stream (after the previous download has read the
+// output staging) -> downloads.
+struct AsyncPass {
+  fbfftconv_handle* h;
+  int pass;
+  cudaStream_t s;
+  int begin_uploads() {
+    if (h->async_used[pass]) FBF_CUDA(cudaStreamWaitEvent(h->up, h->ev_kernels[pass], 0));
+    return FBFFTCONV_OK;
+  }
+  int begin_kernels() {
+    FBF_CUDA(cudaEventRecord(h->ev_up, h->up));
+    FBF_CUDA(cudaStreamWaitEvent(s, h->ev_up, 0));
+    if (h->async_used[pass]) FBF_CUDA(cudaStreamWaitEvent(s, h->ev_down[pass], 0));
+    return FBFFTCONV_OK;
+  }
+  int begin_downloads() {
+    FBF_CUDA(cudaEventRecord(h->ev_kernels[pass], s));
+    FBF_CUDA(cudaStreamWaitEvent(h->down, h->ev_kernels[pass], 0));
+    return FBFFTCONV_OK;
+  }
+  int finish() {
+    FBF_CUDA(cudaEventRecord(h->ev_down[pass], h->down));
+    h->async_used[pass] = true;
+    return FBFFTCONV_OK;
+  }
+};
+
+}  // namespace
+
+int fbfftconv_update_output_host_async(fbfftconv_handle* h, const float* input, const float* weight,
+                                       const float* bias, float* output, fbfftconv_stream stream) {
+  if (!h || !input || !weight || !output) return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "null argument");
+  DeviceGuard g;
+  FBF_CUDA(g.enter(h->device));
+  FBF_TRY(ensure_async(h, 0));
+  const fbfftconv_desc& d = h->d;
+  const StageLayout l = stage_layout(h);
+  char* st = h->astage[0];
+  float* din = reinterpret_cast<float*>(st + l.input);
+  float* dw = reinterpret_cast<float*>(st + l.weight);
+  float* db = reinterpret_cast<float*>(st + l.bias);
+  float* dout = reinterpret_cast<float*>(st + l.output);
+  const size_t n_in = (size_t)d.batch * d.n_input_plane * d.input_h * d.input_w;
+  const size_t n_w = (size_t)d.n_output_plane * d.n_input_plane * d.kernel_h * d.kernel_w;
+  const size_t n_out = (size_t)d.batch * d.n_output_plane * h->oH * h->oW;
+  AsyncPass a{h, 0, static_cast<cudaStream_t>(stream)};
+  FBF_TRY(a.begin_uploads());
+  FBF_CUDA(cudaMemcpyAsync(din, input, n_in * 4, cudaMemcpyHostToDevice, h->up));
+  FBF_CUDA(cudaMemcpyAsync(dw, weight, n_w * 4, cudaMemcpyHostToDevice, h->up));
+  if (bias) FBF_CUDA(cudaMemcpyAsync(db, bias, (size_t)d.n_output_plane * 4, cudaMemcpyHostToDevice, h->up));
+  FBF_TRY(a.begin_kernels());
+  FBF_TRY(fbfftconv_update_output(h, din, dw, bias ? db : nullptr, dout, stream));
+  FBF_TRY(a.begin_downloads());
+  FBF_CUDA(cudaMemcpyAsync(output, dout, n_out * 4, cudaMemcpyDeviceToHost, h->down));
+  return a.finish();
+}
+
+int fbfftconv_update_grad_input_host_async(fbfftconv_handle* h, const float* grad_output,
+                                           const float* weight, float* grad_input,
+                                           fbfftconv_stream stream) {
+  if (!h || !grad_output || !weight || !grad_input)
+    return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "null argument");
+  DeviceGuard g;
+  FBF_CUDA(g.enter(h->device));
+  FBF_TRY(ensure_async(h, 1));
+  const fbfftconv_desc& d = h->d;
+  const StageLayout l = stage_layout(h);
+  char* st = h->astage[1];
+  float* din = reinterpret_cast<float*>(st + l.input);
+  float* dw = reinterpret_cast<float*>(st + l.weight);
+  float* dout = reinterpret_cast<float*>(st + l.output);
+  const size_t n_in = (size_t)d.batch * d.n_input_plane * d.input_h * d.input_w;
+  const size_t n_w = (size_t)d.n_output_plane * d.n_input_plane * d.kernel_h * d.kernel_w;
+  const size_t n_out = (size_t)d.batch * d.n_output_plane * h->oH * h->oW;
+  AsyncPass a{h, 1, static_cast<cudaStream_t>(stream)};
+  FBF_TRY(a.begin_uploads());
+  FBF_CUDA(cudaMemcpyAsync(dout, grad_output, n_out * 4, cudaMemcpyHostToDevice, h->up));
+  FBF_CUDA(cudaMemcpyAsync(dw, weight, n_w * 4, cudaMemcpyHostToDevice, h->up));
+  FBF_TRY(a.begin_kernels());
+  FBF_TRY(fbfftconv_update_grad_input(h, dout, dw, din, stream));
+  FBF_TRY(a.begin_downloads());
+  FBF_CUDA(cudaMemcpyAsync(grad_input, din, n_in * 4, cudaMemcpyDeviceToHost, h->down));
+  return a.finish();
+}
+
+int fbfftconv_acc_grad_parameters_host_async(fbfftconv_handle* h, const float* input,
+                                             const float* grad_output, float* grad_weight,
+                                             float* grad_bias, float scale, fbfftconv_stream stream) {
+  if (!h || !input || !grad_output || !grad_weight)
+    return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "null argument");
+  DeviceGuard g;
+  FBF_CUDA(g.enter(h->device));
+  FBF_TRY(ensure_async(h, 2));
+  const fbfftconv_desc& d = h->d;
+  const StageLayout l = stage_layout(h);
+  char* st = h->astage[2];
+  float* din = reinterpret_cast<float*>(st + l.input);
+  float* dw = reinterpret_cast<float*>(st + l.weight);
+  float* dgb = reinterpret_cast<float*>(st + l.grad_bias);
+  float* dout = reinterpret_cast<float*>(st + l.output);
+  const size_t n_in = (size_t)d.batch * d.n_input_plane * d.input_h * d.input_w;
+  const size_t n_w = (size_t)d.n_output_plane * d.n_input_plane * d.kernel_h * d.kernel_w;
+  const size_t n_out = (size_t)d.batch * d.n_output_plane * h->oH * h->oW;
+  const bool accumulate = d.flags & FBFFTCONV_ACCUMULATE_GRADS;
+  AsyncPass a{h, 2, static_cast<cudaStream_t>(stream)};
+  FBF_TRY(a.begin_uploads());
+  // the gradient staging is both output of the kernels and input of the download: with
+  // accumulation it is also uploaded, which must wait for the previous download of it
+  if (accumulate && h->async_used[2]) FBF_CUDA(cudaStreamWaitEvent(h->up, h->ev_down[2], 0));
+  FBF_CUDA(cudaMemcpyAsync(din, input, n_in * 4, cudaMemcpyHostToDevice, h->up));
+  FBF_CUDA(cudaMemcpyAsync(dout, grad_output, n_out * 4, cudaMemcpyHostToDevice, h->up));
+  if (accumulate) {
+    FBF_CUDA(cudaMemcpyAsync(dw, grad_weight, n_w * 4, cudaMemcpyHostToDevice, h->up));
+    if (grad_bias) FBF_CUDA(cudaMemcpyAsync(dgb, grad_bias, (size_t)d.n_output_plane * 4, cudaMemcpyHostToDevice, h->up));
+  }
+  FBF_TRY(a.begin_kernels());
+  FBF_TRY(fbfftconv_acc_grad_parameters(h, din, dout, dw, grad_bias ? dgb : nullptr, scale, stream));
+  FBF_TRY(a.begin_downloads());
+  FBF_CUDA(cudaMemcpyAsync(grad_weight, dw, n_w * 4, cudaMemcpyDeviceToHost, h->down));
+  if (grad_bias) FBF_CUDA(cudaMemcpyAsync(grad_bias, dgb, (size_t)d.n_output_plane * 4, cudaMemcpyDeviceToHost, h->down));
+  return a.finish();
+}
+
+int fbfftconv_host_sync(fbfftconv_handle* h) {
+  if (!h) return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "null handle");
+  if (!h->down) return FBFFTCONV_OK;
+  DeviceGuard g;
+  FBF_CUDA(g.enter(h->device));
+  FBF_CUDA(cudaStreamSynchronize(h->down));
   return FBFFTCONV_OK;
 }
 

@@ -143,6 +143,23 @@ int fbfftconv_acc_grad_parameters_host(fbfftconv_handle* h, const float* input,
                                        const float* grad_output, float* grad_weight,
                                        float* grad_bias, float scale, fbfftconv_stream stream);
 
+/* Asynchronous forms of the three calls above for callers that pipeline a training step: each
+ * returns as soon as its work is enqueued, and the host outputs of every call issued so far are
+ * valid after fbfftconv_host_sync().  Uploads, kernels and downloads run on three streams (the
+ * caller's for the kernels) linked by events, and each pass has staging buffers of its own, so
+ * the download of one pass overlaps the upload of the next: PCIe carries both directions at once.
+ * Host buffers must stay untouched until the sync and should be pinned (pageable memory makes
+ * the copies synchronous). */
+int fbfftconv_update_output_host_async(fbfftconv_handle* h, const float* input, const float* weight,
+                                       const float* bias, float* output, fbfftconv_stream stream);
+int fbfftconv_update_grad_input_host_async(fbfftconv_handle* h, const float* grad_output,
+                                           const float* weight, float* grad_input,
+                                           fbfftconv_stream stream);
+int fbfftconv_acc_grad_parameters_host_async(fbfftconv_handle* h, const float* input,
+                                             const float* grad_output, float* grad_weight,
+                                             float* grad_bias, float scale, fbfftconv_stream stream);
+int fbfftconv_host_sync(fbfftconv_handle* h);
+
 /* ---- the sub-steps, for callers and tests that drive them one by one --------- */
 
 /* Frequency buffers are complex fp32 laid out [bin][row][inner_padded] with

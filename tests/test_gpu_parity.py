@@ -393,6 +393,40 @@ def test_host_buffer_entry_points():
     lib.fbfftconv_destroy(h)
 
 
+def test_asynchronous_host_buffer_entry_points():
+    """Three passes enqueued without waiting, results read after one fbfftconv_host_sync; repeated with
+    new data so that the staging buffers of a pass are reused while the previous step is in flight."""
+    s = oracle.Shape(6, 4, 5, 30, 29, 3, 2, 1, 0)
+    lib = capi.lib()
+    desc = capi.Desc(s.B, s.P, s.F, s.iH, s.iW, s.kH, s.kW, 1, 1, s.padH, s.padW, 0, 0)
+    h = ctypes.c_void_p()
+    capi.check(lib.fbfftconv_create(ctypes.byref(desc), ctypes.byref(h)))
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    steps = []
+    for step in range(3):
+        x, w, go, b = _data(s, 50 + step, bias=True)
+        host = dict(x=x, w=w, go=go, b=b,
+                    out=torch.empty((s.B, s.F, s.oH, s.oW)).pin_memory(), gi=torch.empty((s.B, s.P, s.iH, s.iW)).pin_memory(),
+                    gw=torch.empty((s.F, s.P, s.kH, s.kW)).pin_memory(), gb=torch.empty((s.F,)).pin_memory(),
+                    tx=torch.from_numpy(x).pin_memory(), tw=torch.from_numpy(w).pin_memory(),
+                    tgo=torch.from_numpy(go).pin_memory(), tb=torch.from_numpy(b).pin_memory())
+        steps.append(host)
+        capi.check(lib.fbfftconv_update_output_host_async(h, p(host["tx"]), p(host["tw"]), p(host["tb"]), p(host["out"]), st))
+        capi.check(lib.fbfftconv_update_grad_input_host_async(h, p(host["tgo"]), p(host["tw"]), p(host["gi"]), st))
+        capi.check(lib.fbfftconv_acc_grad_parameters_host_async(h, p(host["tx"]), p(host["tgo"]), p(host["gw"]),
+                                                                p(host["gb"]), ctypes.c_float(0.5), st))
+    capi.check(lib.fbfftconv_host_sync(h))   # one wait for all three steps
+    for host in steps:
+        x, w, go, b = host["x"], host["w"], host["go"], host["b"]
+        assert _rel(host["out"].numpy(), oracle.update_output(s, x, w, b)) <= PASS_TOL
+        assert _rel(host["gi"].numpy(), oracle.update_grad_input(s, go, w)) <= PASS_TOL
+        assert _rel(host["gw"].numpy(), oracle.acc_grad_weight(s, x, go, 0.5)) <= PASS_TOL
+        assert _rel(host["gb"].numpy(), oracle.acc_grad_bias(s, go, 0.5)) <= PASS_TOL
+    lib.fbfftconv_destroy(h)
+
+
+
 # ---------------------------------------------------------------------------
 # the benchmark's full-size layers: sampled planes against the oracle, plus
 # size-independent properties
