@@ -562,12 +562,12 @@ def measure_e2e(torch, lib, run, L, local_b, world, barrier, max_over_ranks, ste
         capi.check(lib.fbfftconv_acc_grad_parameters_host(h, p(hx), p(hgo), p(hgw), p(hgb), ctypes.c_float(1.0), st))
 
     def step_async():
-        # the three passes enqueue uploads, kernels and downloads on three streams; the step's results
-        # are read (waited for) once per step
+        # forward, then nn.Module:backward (updateGradInput + accGradParameters with gradOutput uploaded
+        # once): uploads, kernels and downloads are enqueued on three streams and the step's results are
+        # read (waited for) once per step
         capi.check(lib.fbfftconv_update_output_host_async(h, p(hx), p(hw), p(hb) if has_bias else None, p(hout), st))
-        capi.check(lib.fbfftconv_update_grad_input_host_async(h, p(hgo), p(hw), p(hgi), st))
-        capi.check(lib.fbfftconv_acc_grad_parameters_host_async(h, p(hx), p(hgo), p(hgw), p(hgb),
-                                                                ctypes.c_float(1.0), st))
+        capi.check(lib.fbfftconv_backward_host_async(h, p(hx), p(hgo), p(hw), p(hgi), p(hgw), p(hgb),
+                                                     ctypes.c_float(1.0), st))
         capi.check(lib.fbfftconv_host_sync(h))
 
     def timed(step):
@@ -583,14 +583,16 @@ def measure_e2e(torch, lib, run, L, local_b, world, barrier, max_over_ranks, ste
 
     ms_sync = timed(step_sync)
     ms = timed(step_async)
-    h2d = 4 * (2 * hx.numel() + 2 * hgo.numel() + 2 * hw.numel() + (hb.numel() if has_bias else 0))
+    h2d = 4 * (2 * hx.numel() + hgo.numel() + 2 * hw.numel() + (hb.numel() if has_bias else 0))
+    h2d_sync = 4 * (2 * hx.numel() + 2 * hgo.numel() + 2 * hw.numel() + (hb.numel() if has_bias else 0))
     d2h = 4 * (hout.numel() + hgi.numel() + hgw.numel() + hgb.numel())
     return {"value": 3.0 * conv_flops(L) / (ms / 1e3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms,
             "h2d_bytes_per_step": int(h2d) * world, "d2h_bytes_per_step": int(d2h) * world,
-            "api": "fbfftconv_update_output_host_async / _update_grad_input_host_async / "
-                   "_acc_grad_parameters_host_async + fbfftconv_host_sync once per step, pinned host buffers",
-            "call_by_call_ms_per_step": ms_sync,
-            "call_by_call_api": "fbfftconv_*_host: each call waits for its own download"}
+            "api": "fbfftconv_update_output_host_async + fbfftconv_backward_host_async (updateGradInput and "
+                   "accGradParameters, gradOutput uploaded once) + fbfftconv_host_sync once per step, pinned host "
+                   "buffers",
+            "call_by_call_ms_per_step": ms_sync, "call_by_call_h2d_bytes_per_step": int(h2d_sync) * world,
+            "call_by_call_api": "fbfftconv_*_host, three calls, each uploads its operands and waits for its download"}
 
 
 def main():

@@ -64,6 +64,7 @@ _SIGNATURES = {
     "fbfftconv_update_output_host_async": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "fbfftconv_update_grad_input_host_async": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "fbfftconv_acc_grad_parameters_host_async": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p]),
+    "fbfftconv_backward_host_async": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p]),
     "fbfftconv_host_sync": (c_int, [c_void_p]),
     "fbfftconv_spectrum_bytes": (c_size_t, [c_int, c_int, c_int]),
     "fbfftconv_fft2d": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),

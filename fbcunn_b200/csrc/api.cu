@@ -954,6 +954,55 @@ int fbfftconv_acc_grad_parameters_host_async(fbfftconv_handle* h, const float* i
   return a.finish();
 }
 
+int fbfftconv_backward_host_async(fbfftconv_handle* h, const float* input, const float* grad_output,
+                                  const float* weight, float* grad_input, float* grad_weight,
+                                  float* grad_bias, float scale, fbfftconv_stream stream) {
+  if (!h || !input || !grad_output || !weight || !grad_input || !grad_weight)
+    return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "null argument");
+  DeviceGuard g;
+  FBF_CUDA(g.enter(h->device));
+  FBF_TRY(ensure_async(h, 1));
+  FBF_TRY(ensure_async(h, 2));
+  const fbfftconv_desc& d = h->d;
+  const StageLayout l = stage_layout(h);
+  // staging of pass 1: gradOutput, weight, gradInput; of pass 2: input, gradWeight, gradBias
+  float* dgo = reinterpret_cast<float*>(h->astage[1] + l.output);
+  float* dw = reinterpret_cast<float*>(h->astage[1] + l.weight);
+  float* dgi = reinterpret_cast<float*>(h->astage[1] + l.input);
+  float* din = reinterpret_cast<float*>(h->astage[2] + l.input);
+  float* dgw = reinterpret_cast<float*>(h->astage[2] + l.weight);
+  float* dgb = reinterpret_cast<float*>(h->astage[2] + l.grad_bias);
+  const size_t n_in = (size_t)d.batch * d.n_input_plane * d.input_h * d.input_w;
+  const size_t n_w = (size_t)d.n_output_plane * d.n_input_plane * d.kernel_h * d.kernel_w;
+  const size_t n_out = (size_t)d.batch * d.n_output_plane * h->oH * h->oW;
+  const bool accumulate = d.flags & FBFFTCONV_ACCUMULATE_GRADS;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  AsyncPass a1{h, 1, s}, a2{h, 2, s};
+  FBF_TRY(a1.begin_uploads());
+  FBF_TRY(a2.begin_uploads());
+  if (accumulate && h->async_used[2]) FBF_CUDA(cudaStreamWaitEvent(h->up, h->ev_down[2], 0));
+  FBF_CUDA(cudaMemcpyAsync(dw, weight, n_w * 4, cudaMemcpyHostToDevice, h->up));
+  FBF_CUDA(cudaMemcpyAsync(din, input, n_in * 4, cudaMemcpyHostToDevice, h->up));
+  FBF_CUDA(cudaMemcpyAsync(dgo, grad_output, n_out * 4, cudaMemcpyHostToDevice, h->up));
+  if (accumulate) {
+    FBF_CUDA(cudaMemcpyAsync(dgw, grad_weight, n_w * 4, cudaMemcpyHostToDevice, h->up));
+    if (grad_bias) FBF_CUDA(cudaMemcpyAsync(dgb, grad_bias, (size_t)d.n_output_plane * 4, cudaMemcpyHostToDevice, h->up));
+  }
+  FBF_TRY(a1.begin_kernels());
+  if (h->async_used[2]) FBF_CUDA(cudaStreamWaitEvent(s, h->ev_down[2], 0));
+  FBF_TRY(fbfftconv_update_grad_input(h, dgo, dw, dgi, stream));
+  FBF_TRY(a1.begin_downloads());  // gradInput can leave while the weight gradient is computed
+  FBF_CUDA(cudaMemcpyAsync(grad_input, dgi, n_in * 4, cudaMemcpyDeviceToHost, h->down));
+  FBF_TRY(fbfftconv_acc_grad_parameters(h, din, dgo, dgw, grad_bias ? dgb : nullptr, scale, stream));
+  // gradOutput's staging belongs to pass 1 but is read until here: its 'kernels done' moves
+  FBF_CUDA(cudaEventRecord(h->ev_kernels[1], s));
+  FBF_TRY(a2.begin_downloads());
+  FBF_CUDA(cudaMemcpyAsync(grad_weight, dgw, n_w * 4, cudaMemcpyDeviceToHost, h->down));
+  if (grad_bias) FBF_CUDA(cudaMemcpyAsync(grad_bias, dgb, (size_t)d.n_output_plane * 4, cudaMemcpyDeviceToHost, h->down));
+  FBF_TRY(a1.finish());
+  return a2.finish();
+}
+
 int fbfftconv_host_sync(fbfftconv_handle* h) {
   if (!h) return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "null handle");
   if (!h->down) return FBFFTCONV_OK;

@@ -158,6 +158,12 @@ int fbfftconv_update_grad_input_host_async(fbfftconv_handle* h, const float* gra
 int fbfftconv_acc_grad_parameters_host_async(fbfftconv_handle* h, const float* input,
                                              const float* grad_output, float* grad_weight,
                                              float* grad_bias, float scale, fbfftconv_stream stream);
+/* nn.Module:backward(input, gradOutput, scale) for host buffers: updateGradInput and
+ * accGradParameters (fbcunn/SpatialConvolutionFFT.lua:405-416) with input, gradOutput and weight
+ * uploaded once for both. */
+int fbfftconv_backward_host_async(fbfftconv_handle* h, const float* input, const float* grad_output,
+                                  const float* weight, float* grad_input, float* grad_weight,
+                                  float* grad_bias, float scale, fbfftconv_stream stream);
 int fbfftconv_host_sync(fbfftconv_handle* h);
 
 /* ---- the sub-steps, for callers and tests that drive them one by one --------- */

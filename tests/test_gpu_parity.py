@@ -413,9 +413,13 @@ def test_asynchronous_host_buffer_entry_points():
                     tgo=torch.from_numpy(go).pin_memory(), tb=torch.from_numpy(b).pin_memory())
         steps.append(host)
         capi.check(lib.fbfftconv_update_output_host_async(h, p(host["tx"]), p(host["tw"]), p(host["tb"]), p(host["out"]), st))
-        capi.check(lib.fbfftconv_update_grad_input_host_async(h, p(host["tgo"]), p(host["tw"]), p(host["gi"]), st))
-        capi.check(lib.fbfftconv_acc_grad_parameters_host_async(h, p(host["tx"]), p(host["tgo"]), p(host["gw"]),
-                                                                p(host["gb"]), ctypes.c_float(0.5), st))
+        if step == 1:   # nn.Module:backward in one call
+            capi.check(lib.fbfftconv_backward_host_async(h, p(host["tx"]), p(host["tgo"]), p(host["tw"]), p(host["gi"]),
+                                                         p(host["gw"]), p(host["gb"]), ctypes.c_float(0.5), st))
+        else:
+            capi.check(lib.fbfftconv_update_grad_input_host_async(h, p(host["tgo"]), p(host["tw"]), p(host["gi"]), st))
+            capi.check(lib.fbfftconv_acc_grad_parameters_host_async(h, p(host["tx"]), p(host["tgo"]), p(host["gw"]),
+                                                                    p(host["gb"]), ctypes.c_float(0.5), st))
     capi.check(lib.fbfftconv_host_sync(h))   # one wait for all three steps
     for host in steps:
         x, w, go, b = host["x"], host["w"], host["go"], host["b"]
