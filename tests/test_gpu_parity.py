@@ -329,6 +329,20 @@ def test_passes_replay_from_a_cuda_graph(shape):
     assert _rel(m.gradBias.cpu().numpy(), oracle.acc_grad_bias(s, go2, 1.0)) <= PASS_TOL
 
 
+@pytest.mark.parametrize("shape", [
+    oracle.Shape(1, 1, 1, 8, 8, 1, 1, 0, 0),          # 1x1 kernel, one plane of each kind
+    oracle.Shape(2, 1, 1, 5, 7, 5, 7, 0, 0),          # kernel as large as the image: 1x1 output
+    oracle.Shape(1, 2, 3, 128, 128, 3, 3, 0, 0),      # the largest transform exactly filled
+    oracle.Shape(1, 2, 3, 126, 120, 3, 5, 1, 2),      # padded image reaches 128 in one direction
+    oracle.Shape(2, 130, 70, 9, 9, 3, 3, 1, 1),       # more than 128 input planes: K and M tails on the tensor cores
+    oracle.Shape(3, 40, 260, 6, 6, 2, 2, 0, 0),       # more than 256 filters: several column tiles
+    oracle.Shape(130, 5, 6, 4, 4, 2, 2, 1, 1),        # batch above one 128-row tile
+])
+def test_edge_shapes(shape):
+    x, w, go, b = _data(shape, 1234, bias=True)
+    _check_three_passes(shape, x, w, go, b, scale=0.9)
+
+
 def test_random_sweep():
     """Recipe of test/test_FFT.lua:82-107: B = 4*rand(4), planes <= 13, k <= 7, pad <= min(4, k-1)."""
     rng = np.random.default_rng(424242)
