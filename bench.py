@@ -66,7 +66,7 @@ def fft_size(L):
 
 
 def stage_algorithmic(L, B, pass_idx, stage):
-    """(bytes, flops) one launch of a stage moves / performs, by the definitions in DESIGN.md:
+    """Algorithmic (bytes, flops) of one launch of a stage:
     a transform of D planes of h x w reads or writes 4*D*h*w real bytes and 8*D*bins
     spectrum bytes; the contraction reads two spectra, writes one and does 8*M*N*K*bins flops."""
     _, P, F, iH, iW, kH, kW, pH, pW, _ = L
