@@ -64,6 +64,11 @@ struct NcclApi {
   ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
   ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t,
                             cudaStream_t) = nullptr;
+  ncclResult_t (*ReduceScatter)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t,
+                                cudaStream_t) = nullptr;
+  ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+  ncclResult_t (*GroupStart)() = nullptr;
+  ncclResult_t (*GroupEnd)() = nullptr;
   ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
   const char* (*GetErrorString)(ncclResult_t) = nullptr;
 };
@@ -83,6 +88,10 @@ NcclApi* nccl_api() {
   api.GetUniqueId = reinterpret_cast<decltype(api.GetUniqueId)>(dlsym(lib, "ncclGetUniqueId"));
   api.CommInitRank = reinterpret_cast<decltype(api.CommInitRank)>(dlsym(lib, "ncclCommInitRank"));
   api.AllReduce = reinterpret_cast<decltype(api.AllReduce)>(dlsym(lib, "ncclAllReduce"));
+  api.ReduceScatter = reinterpret_cast<decltype(api.ReduceScatter)>(dlsym(lib, "ncclReduceScatter"));
+  api.AllGather = reinterpret_cast<decltype(api.AllGather)>(dlsym(lib, "ncclAllGather"));
+  api.GroupStart = reinterpret_cast<decltype(api.GroupStart)>(dlsym(lib, "ncclGroupStart"));
+  api.GroupEnd = reinterpret_cast<decltype(api.GroupEnd)>(dlsym(lib, "ncclGroupEnd"));
   api.CommDestroy = reinterpret_cast<decltype(api.CommDestroy)>(dlsym(lib, "ncclCommDestroy"));
   api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(dlsym(lib, "ncclGetErrorString"));
   if (!api.GetUniqueId || !api.CommInitRank || !api.AllReduce || !api.CommDestroy) return nullptr;
@@ -437,8 +446,8 @@ int fbfftconv_create(const fbfftconv_desc* desc, fbfftconv_handle** out) {
   // (+ F floats behind the gradWeight spectrum: the bias gradient rides in the same all-reduce)
   h->bytes_w = align256(bins * mx(F * pad4(P), P * pad4(F)) * sizeof(float2) + F * sizeof(float));
   h->bytes_small = align256((B * F + F) * sizeof(float));
-  if (d.flags & FBFFTCONV_ALLREDUCE_SPATIAL)  // local gradWeight + gradBias, summed across ranks
-    h->bytes_small += align256((F * P * d.kernel_h * d.kernel_w + F) * sizeof(float));
+  // local gradWeight + gradBias where they are summed or gathered across ranks in the spatial domain
+  h->bytes_small += align256((F * P * d.kernel_h * d.kernel_w + F) * sizeof(float));
   h->bytes_gi = (h->plane_major && (d.flags & FBFFTCONV_REUSE_INPUT)) ? h->bytes_in : 0;
   h->bytes_total = h->bytes_in + h->bytes_out + h->bytes_w + h->bytes_small + h->bytes_gi;
   *out = h;
@@ -633,7 +642,12 @@ int fbfftconv_acc_grad_parameters(fbfftconv_handle* h, const float* input, const
   // Across ranks the bias gradient travels behind whatever the weight gradient is summed
   // as: behind its spectrum, or behind the local spatial gradient.
   float* local_w = h->small() + align256(((size_t)B * F + F) * sizeof(float)) / sizeof(float);
-  float* bias_part = spatial ? local_w + n_weight : reinterpret_cast<float*>(h->buf_w()) + spec_floats;
+  // Plane-major spectra are contiguous per filter, so the sum across ranks can be a reduce-scatter
+  // by filters (half the bytes of an all-reduce): every rank inverts its own filters and the
+  // spatial slices (a few hundred KB) are gathered.  Still the frequency-domain sum.
+  const bool scatter = h->comm && !spatial && pm && F % h->nranks == 0 && api->ReduceScatter && api->AllGather &&
+                       api->GroupStart && api->GroupEnd;
+  float* bias_part = (spatial || scatter) ? local_w + n_weight : reinterpret_cast<float*>(h->buf_w()) + spec_floats;
   // W'^[bin][f][p] = scale/N^2 sum_b conj(O'^[f][b]) I^[p][b]
   {
     StageTimer t(h, pass, FBFFTCONV_STAGE_CONTRACT, s);
@@ -658,12 +672,38 @@ int fbfftconv_acc_grad_parameters(fbfftconv_handle* h, const float* input, const
       FBF_CUDA(launch_row_sum(dc, grad_bias, F, B, ld, dc_step, scale, accumulate, s));
   }
   const size_t bias_floats = grad_bias ? (size_t)F : 0;
-  if (h->comm && !spatial) {
+  if (scatter) {
+    const size_t chunk = spec_floats / h->nranks, slice = n_weight / h->nranks;
+    float* mine = reinterpret_cast<float*>(h->buf_w()) + (size_t)h->rank * chunk;
+    {
+      StageTimer t(h, pass, FBFFTCONV_STAGE_ALLREDUCE, s);
+      ncclResult_t r = api->ReduceScatter(h->buf_w(), mine, chunk, ncclFloat, ncclSum, h->comm, s);
+      if (r != ncclSuccess) return nccl_fail(api, r, "ncclReduceScatter(gradWeight spectrum)");
+    }
+    {
+      StageTimer t(h, pass, FBFFTCONV_STAGE_IFFT, s);
+      FBF_CUDA(launch_inverse(inverse_params(reinterpret_cast<const float2*>(mine), local_w + (size_t)h->rank * slice,
+                                             nullptr, F / h->nranks, P, d.kernel_h, d.kernel_w, 0, 0, 0, true, h->N),
+                              h->N, s));
+    }
+    {
+      StageTimer t(h, pass, FBFFTCONV_STAGE_ALLREDUCE, s);
+      ncclResult_t r = api->GroupStart();
+      if (r == ncclSuccess)
+        r = api->AllGather(local_w + (size_t)h->rank * slice, local_w, slice, ncclFloat, h->comm, s);
+      if (r == ncclSuccess && bias_floats)
+        r = api->AllReduce(bias_part, bias_part, bias_floats, ncclFloat, ncclSum, h->comm, s);
+      const ncclResult_t r2 = api->GroupEnd();
+      if (r != ncclSuccess || r2 != ncclSuccess)
+        return nccl_fail(api, r != ncclSuccess ? r : r2, "ncclAllGather(gradWeight) / ncclAllReduce(gradBias)");
+      FBF_CUDA(launch_copy_or_add(local_w, grad_weight, (long long)n_weight, accumulate, s));
+    }
+  } else if (h->comm && !spatial) {
     StageTimer t(h, pass, FBFFTCONV_STAGE_ALLREDUCE, s);
     ncclResult_t r = api->AllReduce(h->buf_w(), h->buf_w(), spec_floats + bias_floats, ncclFloat, ncclSum, h->comm, s);
     if (r != ncclSuccess) return nccl_fail(api, r, "ncclAllReduce(gradWeight spectrum)");
   }
-  {
+  if (!scatter) {
     StageTimer t(h, pass, FBFFTCONV_STAGE_IFFT, s);
     FBF_CUDA(launch_inverse(inverse_params(h->buf_w(), spatial ? local_w : grad_weight, nullptr, F, P, d.kernel_h,
                                            d.kernel_w, 0, 0, spatial ? 0 : accumulate, pm, h->N), h->N, s));
