@@ -183,8 +183,11 @@ class SpatialConvolutionFBFFT:
     # -- multi-GPU -----------------------------------------------------------------
     def attachCommunicator(self, unique_id: bytes, rank: int, nranks: int):
         """One rank per GPU: accGradParameters then sums the frequency-domain weight
-        gradient (and gradBias) over all ranks with an NCCL all-reduce before the
-        inverse transform.  Replaces the gather/add/broadcast of nn.DataParallel
+        gradient (and gradBias) over all ranks with NCCL before the inverse transform
+        (an all-reduce; for plane-major layers a reduce-scatter by filters, the inverse
+        transform of the rank's own filters and an all-gather of the result).  With
+        allreduce="spatial" the sum happens after the inverse transform instead.
+        Replaces the gather/add/broadcast of nn.DataParallel
         (fbcunn/DataParallel.lua:105-131)."""
         assert len(unique_id) == 128
         self._comm = (bytes(unique_id), int(rank), int(nranks))
