@@ -647,7 +647,14 @@ int fbfftconv_acc_grad_parameters(fbfftconv_handle* h, const float* input, const
   // spatial slices (a few hundred KB) are gathered.  Still the frequency-domain sum.
   const bool scatter = h->comm && !spatial && pm && F % h->nranks == 0 && api->ReduceScatter && api->AllGather &&
                        api->GroupStart && api->GroupEnd;
-  float* bias_part = (spatial || scatter) ? local_w + n_weight : reinterpret_cast<float*>(h->buf_w()) + spec_floats;
+  // Bin-major spectra are contiguous per bin: the sum across ranks is a reduce-scatter by bin
+  // range (half the bytes of an all-reduce), every rank inverts the spectrum that is zero outside
+  // its own bins (the transform is linear in the bins), and the spatial partial results -- a few
+  // MB -- are all-reduced.
+  const bool scatter_bins = h->comm && !spatial && !pm && h->nranks > 1 && h->bins % h->nranks == 0 &&
+                            api->ReduceScatter;
+  float* bias_part =
+      (spatial || scatter || scatter_bins) ? local_w + n_weight : reinterpret_cast<float*>(h->buf_w()) + spec_floats;
   // W'^[bin][f][p] = scale/N^2 sum_b conj(O'^[f][b]) I^[p][b]
   {
     StageTimer t(h, pass, FBFFTCONV_STAGE_CONTRACT, s);
@@ -698,12 +705,36 @@ int fbfftconv_acc_grad_parameters(fbfftconv_handle* h, const float* input, const
         return nccl_fail(api, r != ncclSuccess ? r : r2, "ncclAllGather(gradWeight) / ncclAllReduce(gradBias)");
       FBF_CUDA(launch_copy_or_add(local_w, grad_weight, (long long)n_weight, accumulate, s));
     }
+  } else if (scatter_bins) {
+    const size_t chunk = spec_floats / h->nranks;
+    float* all = reinterpret_cast<float*>(h->buf_w());
+    float* mine = all + (size_t)h->rank * chunk;
+    {
+      StageTimer t(h, pass, FBFFTCONV_STAGE_ALLREDUCE, s);
+      ncclResult_t r = api->ReduceScatter(all, mine, chunk, ncclFloat, ncclSum, h->comm, s);
+      if (r != ncclSuccess) return nccl_fail(api, r, "ncclReduceScatter(gradWeight spectrum)");
+    }
+    // the other ranks' bins still hold this rank's partial products
+    if (h->rank > 0) FBF_CUDA(cudaMemsetAsync(all, 0, (size_t)h->rank * chunk * sizeof(float), s));
+    if (h->rank + 1 < h->nranks)
+      FBF_CUDA(cudaMemsetAsync(mine + chunk, 0, (size_t)(h->nranks - 1 - h->rank) * chunk * sizeof(float), s));
+    {
+      StageTimer t(h, pass, FBFFTCONV_STAGE_IFFT, s);
+      FBF_CUDA(launch_inverse(inverse_params(h->buf_w(), local_w, nullptr, F, P, d.kernel_h, d.kernel_w, 0, 0, 0, false,
+                                             h->N), h->N, s));
+    }
+    {
+      StageTimer t(h, pass, FBFFTCONV_STAGE_ALLREDUCE, s);
+      ncclResult_t r = api->AllReduce(local_w, local_w, n_weight + bias_floats, ncclFloat, ncclSum, h->comm, s);
+      if (r != ncclSuccess) return nccl_fail(api, r, "ncclAllReduce(gradWeight partial transforms)");
+      FBF_CUDA(launch_copy_or_add(local_w, grad_weight, (long long)n_weight, accumulate, s));
+    }
   } else if (h->comm && !spatial) {
     StageTimer t(h, pass, FBFFTCONV_STAGE_ALLREDUCE, s);
     ncclResult_t r = api->AllReduce(h->buf_w(), h->buf_w(), spec_floats + bias_floats, ncclFloat, ncclSum, h->comm, s);
     if (r != ncclSuccess) return nccl_fail(api, r, "ncclAllReduce(gradWeight spectrum)");
   }
-  if (!scatter) {
+  if (!scatter && !scatter_bins) {
     StageTimer t(h, pass, FBFFTCONV_STAGE_IFFT, s);
     FBF_CUDA(launch_inverse(inverse_params(h->buf_w(), spatial ? local_w : grad_weight, nullptr, F, P, d.kernel_h,
                                            d.kernel_w, 0, 0, spatial ? 0 : accumulate, pm, h->N), h->N, s));
