@@ -9,6 +9,8 @@
 //
 // Stands where the reference calls transposeMMFFI on its plane-major buffers
 // (fbcunn/SpatialConvolutionFBFFT.lua:157-164, :244-251, :337-344; src/MM.cu:54-73).
+#include <cstdlib>
+
 #include "kernels.h"
 
 namespace fbfft {
@@ -201,8 +203,16 @@ cudaError_t launch_stream_reduce(const float2* x, const float2* y, float2* z, in
   } else if (blocks_for(256, 2) >= 2 * 148) {
     tu = 2;
     nt = 256;
-  } else if (blocks_for(128, 2) >= 3 * 148) {
+  } else if (2 * blocks_for(128, 2) >= 3 * 148) {  // measured at 16 rows: 42 us against 51 (one row) and 49 (four)
     tu = 2;
+  }
+  static const int forced = [] {  // tuning aid: FBFFTCONV_REDUCE_ROWS = 1, 2 or 4 rows per 128-thread block
+    const char* e = getenv("FBFFTCONV_REDUCE_ROWS");
+    return e ? atoi(e) : 0;
+  }();
+  if (forced == 1 || forced == 2 || forced == 4) {
+    tu = forced;
+    nt = 128;
   }
   dim3 grid((unsigned)((bins / 2 + nt - 1) / nt), (U + tu - 1) / tu);
   if (grid.y > 65535) return cudaErrorInvalidValue;
