@@ -59,7 +59,10 @@ __device__ __forceinline__ void copy_wait() {
 }
 __device__ __forceinline__ C2 as_c2(float4 v) { return C2{make_float2(v.x, v.y), make_float2(v.z, v.w)}; }
 
-constexpr int RING_STAGES = 4;  // iterations of w in flight per thread
+#ifndef FBF_RING_STAGES
+#define FBF_RING_STAGES 3
+#endif
+constexpr int RING_STAGES = FBF_RING_STAGES;  // iterations of w in flight per thread
 
 // Z[u][v][bin] = alpha * sum_{p<P} X[u][p][bin] * conj(Y[v][p][bin])
 // block: TU rows u, a chunk of columns v, 512 bins; the Y planes of the next RING_STAGES - 1
