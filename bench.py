@@ -9,6 +9,9 @@ layer over one seeded synthetic batch; `value` is direct-convolution-equivalent 
 ranks the global batch of 128 is split across ranks (strong scaling) and the weight
 gradient's spectrum is all-reduced inside accGradParameters.  `e2e` is the same step
 through the host-buffer entry points of the C ABI (pinned host memory, copies timed).
+The last stdout line is the short result object; the per-kernel and per-layer tables go
+to --detail-file.  Outside the timed region every timed layer is checked on sampled
+planes against the fp64 direct convolution (`parity_checked`).
 `--impl reference` times the reference's own CPU convolution (compiled from its source
 under oracle/_ref) on a bounded batch slice with every host thread.
 """
@@ -38,7 +41,8 @@ LAYERS = {
 }
 PASSES = ("updateOutput", "updateGradInput", "accGradParameters")
 STAGES = ("fft_a", "fft_b", "contract", "allreduce", "ifft", "bias")
-METRIC = "direct-conv-equivalent TFLOP/s over updateOutput+updateGradInput+accGradParameters (ms per pass in `layers`)"
+METRIC = "direct-conv-equivalent TFLOP/s, updateOutput+updateGradInput+accGradParameters"
+PARITY_TOL = 1e-4  # max|x - ref| <= PARITY_TOL * max|ref| against the fp64 direct convolution
 
 
 def peaks():
@@ -182,15 +186,22 @@ def run_reference_arm(args):
     return 0
 
 
+def step_bytes(L):
+    """Bytes of the real tensors one step touches (input, output / gradOutput, weight)."""
+    B, P, F, iH, iW, kH, kW, pH, pW, _ = L
+    oH, oW = iH + 2 * pH - kH + 1, iW + 2 * pW - kW + 1
+    return 4 * (B * P * iH * iW + B * F * oH * oW + F * P * kH * kW)
+
+
 def workload_config(name, L, gpus, allreduce="spectrum", reuse="none"):
     B, P, F, iH, iW, kH, kW, pH, pW, _ = L
     return {
-        "workload": f"{name}: batch {B} x {P} planes x {iH}x{iW}, {F} filters {kH}x{kW}, pad {pH}, stride 1, "
-                    f"FFT size {fft_size(L)}; one step = updateOutput + updateGradInput + accGradParameters",
-        "global_batch": B, "parallelism": f"batch sharded over {gpus} rank(s), "
-        + ("gradWeight spectrum" if allreduce == "spectrum" else "spatial gradWeight") + " all-reduced (NCCL)"
+        "workload": f"{name}: {B}x{P}x{iH}x{iW} input, {F} filters {kH}x{kW}, pad {pH}, FFT {fft_size(L)}; step = 3 passes",
+        "global_batch": B,
+        "parallelism": (f"batch over {gpus} ranks, gradWeight "
+                        + ("spectrum" if allreduce == "spectrum" else "(spatial)") + " summed by NCCL")
         if gpus > 1 else "single GPU",
-        "l2": "per-step working set exceeds the 126 MB L2; per-pass rows in `layers` are timed after an L2 flush",
+        "l2": "inputs > L2" if step_bytes(L) > (126 << 20) else "inputs fit L2 (warm); per-layer rows follow a flush",
         "memory_reuse": reuse,
     }
 
@@ -374,6 +385,17 @@ def captured_traffic(layer, top, L, local_b):
     return float(entry["bytes_per_unit"]) * local_b * L[2]  # planes (b, f) in this launch
 
 
+def sig(v, digits=4):
+    """Rounds to `digits` significant digits (keeps the result line short)."""
+    if v is None or isinstance(v, (bool, int, str)):
+        return v
+    return float(f"{float(v):.{digits}g}")
+
+
+def compact(d, keys):
+    return {k: sig(d[k], 5) if isinstance(d.get(k), float) else d.get(k) for k in keys if k in d}
+
+
 def tensor_peak_3xtf32(pk):
     """Algorithmic TFLOP/s the 3xTF32 contraction can reach: dense TF32 is taken as half the
     measured bf16 rate and every product costs three MMAs."""
@@ -476,6 +498,13 @@ def run_gpu_arm(args):
     e2e = measure_e2e(torch, lib, run, L, local_b, world, barrier, max_over_ranks,
                       steps=max(1, min(args.steps, 5)))
 
+    # ---- parity of what was timed, on sampled planes (not timed) -------------------
+    parity = None
+    if not args.no_parity:
+        parity = parity_check(torch, dist, run, L, local_b, world, max_over_ranks)
+        if not parity["ok"]:
+            raise SystemExit(f"parity check failed: {parity}")
+
     # ---- per layer, per pass (cold L2) ------------------------------------------
     layers = {}
     if not args.no_layers:
@@ -510,35 +539,108 @@ def run_gpu_arm(args):
                              "kernels": kernel_table(LL, lb, prof_l, pk)}
             if world == 1:
                 layers[lname]["step_ms"] = step_times(torch, capi, lib, r, args.layer_iters)
+            if parity is not None and lname != name:
+                pc = parity_check(torch, dist, r, LL, lb, world, max_over_ranks)
+                layers[lname]["parity"] = pc
+                if not pc["ok"]:
+                    raise SystemExit(f"parity check failed on {lname}: {pc}")
+                parity["max_rel_err"] = max(parity["max_rel_err"], pc["max_rel_err"])
+                parity.setdefault("layers", [name]).append(lname)
             del r
             torch.cuda.empty_cache()
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
+        # the reference's CPU convolution is single-threaded: one thread on one batch element is the
+        # reference as it stands; the threaded figure (one batch slice per host thread) is what the
+        # host can do with it and is the one carried as `value`
         threads = host_threads()
+        items1, filters1 = cpu_sample(L, 1, 4.0)
+        dt1, kind = cpu_reference_step(L, 1, items1, filters1)
         items, filters = cpu_sample(L, threads, 6.0)
         dt, kind = cpu_reference_step(L, threads, items, filters)
         dt2, kind = cpu_reference_step(L, threads, items, filters, seed=1)
         dt = min(dt, dt2)
-        cpu = {"value": sample_flops(L, items, filters) / dt / 1e12, "unit": "TFLOP/s",
-               "cores": min(threads, items), "kind": kind,
-               "sample": sample_text(name, L, items, filters, threads) + f"; {dt:.1f} s per sample"}
+        cpu = {"value": sig(sample_flops(L, items, filters) / dt / 1e12), "unit": "TFLOP/s",
+               "cores": min(threads, items), "host_cores": threads, "kind": kind,
+               "one_thread_value": sig(sample_flops(L, items1, filters1) / dt1 / 1e12),
+               "sample": f"{items}/{L[0]} batch x {filters}/{L[2]} filters, {dt:.1f} s; 1 thread: {items1} x {filters1}, "
+                         f"{dt1:.1f} s; scaled linearly"}
 
     if rank == 0:
+        detail = {"kernels": kernels, "layers": layers, "roofline": roofline, "e2e": e2e, "parity": parity,
+                  "config": workload_config(name, L, world, args.allreduce, args.reuse)}
+        try:
+            with open(args.detail_file, "w") as f:
+                json.dump(detail, f, indent=1)
+        except OSError as e:
+            sys.stderr.write(f"bench detail not written: {e}\n")
+        # per layer: sum of the three per-pass medians (ms), each timed after an L2 flush
+        layers_step_ms = {k: sig(sum(p["ms"] for p in v["passes"])) for k, v in layers.items()}
         line = {
-            "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "metric": METRIC, "value": sig(value, 5), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": sig(ms_per_step, 5), "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": workload_config(name, L, world, args.allreduce, args.reuse), "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
-            "gpu_launches": int(launches), "clocks": clocks, "kernels": kernels, "layers": layers,
+            "config": workload_config(name, L, world, args.allreduce, args.reuse),
+            "roofline": compact(roofline, ("bound", "kernel", "achieved", "peak", "unit", "frac", "traffic",
+                                           "avg_launch_us", "peak_source")),
+            "cpu_baseline": cpu,
+            "e2e": compact(e2e, ("value", "unit", "ms_per_step", "h2d_bytes_per_step", "d2h_bytes_per_step")),
+            "gpu_launches": int(launches), "clocks": clocks, "layers_step_ms": layers_step_ms,
+            "parity_checked": bool(parity and parity["checked"]),
+            "parity_max_rel_err": sig(parity["max_rel_err"], 3) if parity else None,
         }
-        print(json.dumps(line), flush=True)
+        print(json.dumps(line, separators=(",", ":")), flush=True)
     if world > 1:
         import gc
         gc.collect()  # handles detach from the communicator before it is shut down
         lib.fbfftconv_comm_shutdown()
         dist.destroy_process_group()
     return 0
+
+
+def parity_check(torch, dist, run, L, local_b, world, max_over_ranks, planes=8):
+    """Outside the timed region: the three passes of the timed layer, on the tensors that were
+    timed, against the fp64 direct convolution (the CPU oracle, here only as the checker) on
+    `planes` sampled planes per pass.  With several ranks every rank computes the oracle planes of
+    the weight gradient for its own batch shard and the partial results are summed over ranks
+    (what the reference's data-parallel test asserts about replicas, test/test_DataParallel.lua:73-159)."""
+    import numpy as np
+    import oracle
+    _, P, F, iH, iW, kH, kW, pH, pW, has_bias = L
+    s = oracle.Shape(local_b, P, F, iH, iW, kH, kW, pH, pW)
+    m = run.m
+    x, go = run.x.cpu().numpy(), run.go.cpu().numpy()
+    w = m.weight.cpu().numpy()
+    b = m.bias.cpu().numpy() if has_bias else None
+    rng = np.random.default_rng(20240229)  # the same planes on every rank
+    bi, fi, pi = rng.integers(0, local_b, planes), rng.integers(0, F, planes), rng.integers(0, P, planes)
+    out = m.updateOutput(run.x)
+    got_out = out[torch.as_tensor(bi), torch.as_tensor(fi)].cpu().numpy()
+    gi = m.updateGradInput(run.x, run.go)
+    got_gi = gi[torch.as_tensor(bi), torch.as_tensor(pi)].cpu().numpy()
+    m.accGradParameters(run.x, run.go, 1.0)
+    torch.cuda.synchronize()
+    got_gw = m.gradWeight[torch.as_tensor(fi), torch.as_tensor(pi)].cpu().numpy()
+    got_gb = m.gradBias.cpu().numpy()
+    ref_gw = oracle.acc_grad_weight_planes(s, x, go, 1.0, fi, pi)
+    ref_gb = oracle.acc_grad_bias(s, go, 1.0)
+    if world > 1:
+        t = torch.from_numpy(np.concatenate([ref_gw.ravel(), ref_gb.ravel()])).cuda()
+        dist.all_reduce(t)
+        t = t.cpu().numpy()
+        ref_gw, ref_gb = t[:ref_gw.size].reshape(ref_gw.shape), t[ref_gw.size:]
+
+    def rel(a, ref):
+        return float(np.abs(a.astype(np.float64) - ref).max() / max(np.abs(ref).max(), 1e-30))
+
+    errs = {"updateOutput": rel(got_out, oracle.update_output_planes(s, x, w, b, bi, fi)),
+            "updateGradInput": rel(got_gi, oracle.update_grad_input_planes(s, go, w, bi, pi)),
+            "gradWeight": rel(got_gw, ref_gw), "gradBias": rel(got_gb, ref_gb)}
+    errs = {k: max_over_ranks(v) for k, v in errs.items()}
+    worst = max(errs.values())
+    return {"checked": True, "planes_per_pass": planes, "tol": PARITY_TOL, "max_rel_err": worst,
+            "per_pass": errs, "ok": worst <= PARITY_TOL}
 
 
 def measure_e2e(torch, lib, run, L, local_b, world, barrier, max_over_ranks, steps):
@@ -613,6 +715,9 @@ def main():
                          "of the earlier passes of the step (not the default, which recomputes everything)")
     ap.add_argument("--no-layers", action="store_true", help="skip the per-layer / per-pass table")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-parity", action="store_true", help="skip the sampled-plane check against the CPU oracle")
+    ap.add_argument("--detail-file", default=os.path.join(ROOT, "bench_detail.json"),
+                    help="per-kernel and per-layer tables (the result line on stdout stays short)")
     args = ap.parse_args()
     if args.batch > 0:
         for k, v in list(LAYERS.items()):

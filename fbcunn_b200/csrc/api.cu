@@ -104,6 +104,7 @@ NcclApi* nccl_api() {
 struct SharedComm {
   ncclComm_t comm = nullptr;
   int refs = 0;
+  int rank = 0, nranks = 0, device = -1;  // what the communicator was initialised with
 };
 std::mutex g_comm_mutex;
 std::map<std::string, SharedComm> g_comms;
@@ -213,8 +214,8 @@ struct Fork {
   cudaStream_t main;
   bool active = false;
   Fork(fbfftconv_handle* h_, cudaStream_t s, long long tiles_a, long long tiles_b) : h(h_), main(s) {
-    constexpr long long kFillsTheGpu = 4 * 148;
-    if (tiles_a >= kFillsTheGpu && tiles_b >= kFillsTheGpu) return;
+    const long long fills_the_gpu = 4LL * sm_count();
+    if (tiles_a >= fills_the_gpu && tiles_b >= fills_the_gpu) return;
     if (!h->aux) {
       if (cudaStreamCreateWithFlags(&h->aux, cudaStreamNonBlocking) != cudaSuccess ||
           cudaEventCreateWithFlags(&h->ev_fork, cudaEventDisableTiming) != cudaSuccess ||
@@ -358,6 +359,34 @@ bool thin_contraction(int m, int n, int k) {
 
 bool valid_fft_size(int n) { return n == 8 || n == 16 || n == 32 || n == 64 || n == 128; }
 
+// What the reference's bindings check before they launch (THCudaTensor_checkGPU over all tensors,
+// src/fft/SpatialConvolutionCuFFTHost.cpp:33-66): every tensor lives in device memory of the
+// module's GPU.  A host pointer, or memory of another GPU, is refused instead of launched on.
+int check_device_pointer(const fbfftconv_handle* h, const void* ptr, const char* name) {
+  if (!ptr) return FBFFTCONV_OK;  // optional arguments; the required ones were checked for null
+  cudaPointerAttributes attr{};
+  cudaError_t e = cudaPointerGetAttributes(&attr, ptr);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return cuda_fail(e, "cudaPointerGetAttributes");
+  }
+  if (attr.type == cudaMemoryTypeManaged) return FBFFTCONV_OK;
+  if (attr.type != cudaMemoryTypeDevice)
+    return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "%s is not a device pointer (use the *_host entry points for host buffers)", name);
+  if (attr.device != h->device)
+    return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "%s lives on device %d, the handle on device %d", name, attr.device, h->device);
+  return FBFFTCONV_OK;
+}
+
+// A bounded wait of the tensor-core contraction that ran out leaves its tile unwritten and a
+// sticky device code; entry points that have just synchronised report it.
+int check_tensor_core_status() {
+  const int code = contract_tc_error(false);
+  if (code > 0)
+    return fail(FBFFTCONV_ERR_CUDA, "tensor-core contraction gave up a bounded wait (device code %d); results are incomplete", code);
+  return FBFFTCONV_OK;
+}
+
 void release_comm(fbfftconv_handle* h) {
   if (!h->comm) return;
   std::lock_guard<std::mutex> lock(g_comm_mutex);
@@ -497,6 +526,8 @@ int fbfftconv_set_workspace(fbfftconv_handle* h, void* device_ptr, size_t bytes)
   }
   h->ws = static_cast<char*>(device_ptr);
   h->ws_owned = false;
+  // the new block holds no spectra yet: nothing of an earlier pass can be taken over
+  h->have_input_spec = h->have_grad_output_spec = h->have_weight_spec = false;
   return FBFFTCONV_OK;
 }
 
@@ -507,6 +538,10 @@ int fbfftconv_update_output(fbfftconv_handle* h, const float* input, const float
   if (!h || !input || !weight || !output) return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "null argument");
   DeviceGuard g;
   FBF_CUDA(g.enter(h->device));
+  FBF_TRY(check_device_pointer(h, input, "input"));
+  FBF_TRY(check_device_pointer(h, weight, "weight"));
+  FBF_TRY(check_device_pointer(h, bias, "bias"));
+  FBF_TRY(check_device_pointer(h, output, "output"));
   FBF_TRY(ensure_workspace(h));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const fbfftconv_desc& d = h->d;
@@ -556,6 +591,9 @@ int fbfftconv_update_grad_input(fbfftconv_handle* h, const float* grad_output, c
     return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "null argument");
   DeviceGuard g;
   FBF_CUDA(g.enter(h->device));
+  FBF_TRY(check_device_pointer(h, grad_output, "gradOutput"));
+  FBF_TRY(check_device_pointer(h, weight, "weight"));
+  FBF_TRY(check_device_pointer(h, grad_input, "gradInput"));
   FBF_TRY(ensure_workspace(h));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const fbfftconv_desc& d = h->d;
@@ -608,6 +646,10 @@ int fbfftconv_acc_grad_parameters(fbfftconv_handle* h, const float* input, const
     return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "null argument");
   DeviceGuard g;
   FBF_CUDA(g.enter(h->device));
+  FBF_TRY(check_device_pointer(h, input, "input"));
+  FBF_TRY(check_device_pointer(h, grad_output, "gradOutput"));
+  FBF_TRY(check_device_pointer(h, grad_weight, "gradWeight"));
+  FBF_TRY(check_device_pointer(h, grad_bias, "gradBias"));
   FBF_TRY(ensure_workspace(h));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const fbfftconv_desc& d = h->d;
@@ -814,7 +856,7 @@ int fbfftconv_update_output_host(fbfftconv_handle* h, const float* input, const 
   FBF_TRY(fbfftconv_update_output(h, din, dw, bias ? db : nullptr, dout, stream));
   FBF_CUDA(cudaMemcpyAsync(output, dout, n_out * 4, cudaMemcpyDeviceToHost, s));
   FBF_CUDA(cudaStreamSynchronize(s));
-  return FBFFTCONV_OK;
+  return check_tensor_core_status();
 }
 
 int fbfftconv_update_grad_input_host(fbfftconv_handle* h, const float* grad_output,
@@ -838,7 +880,7 @@ int fbfftconv_update_grad_input_host(fbfftconv_handle* h, const float* grad_outp
   FBF_TRY(fbfftconv_update_grad_input(h, dout, dw, din, stream));
   FBF_CUDA(cudaMemcpyAsync(grad_input, din, n_in * 4, cudaMemcpyDeviceToHost, s));
   FBF_CUDA(cudaStreamSynchronize(s));
-  return FBFFTCONV_OK;
+  return check_tensor_core_status();
 }
 
 int fbfftconv_acc_grad_parameters_host(fbfftconv_handle* h, const float* input,
@@ -870,7 +912,7 @@ int fbfftconv_acc_grad_parameters_host(fbfftconv_handle* h, const float* input,
   FBF_CUDA(cudaMemcpyAsync(grad_weight, dw, n_w * 4, cudaMemcpyDeviceToHost, s));
   if (grad_bias) FBF_CUDA(cudaMemcpyAsync(grad_bias, dgb, (size_t)d.n_output_plane * 4, cudaMemcpyDeviceToHost, s));
   FBF_CUDA(cudaStreamSynchronize(s));
-  return FBFFTCONV_OK;
+  return check_tensor_core_status();
 }
 
 // ---- asynchronous host-buffer variants ----------------------------------------
@@ -1080,7 +1122,7 @@ int fbfftconv_host_sync(fbfftconv_handle* h) {
   DeviceGuard g;
   FBF_CUDA(g.enter(h->device));
   FBF_CUDA(cudaStreamSynchronize(h->down));
-  return FBFFTCONV_OK;
+  return check_tensor_core_status();
 }
 
 // ---- sub-steps ---------------------------------------------------------------
@@ -1235,6 +1277,13 @@ int fbfftconv_comm_init(fbfftconv_handle* h, const void* id128, int rank, int nr
       g_comms.erase(key);
       return nccl_fail(api, r, "ncclCommInitRank");
     }
+    shared.rank = rank;
+    shared.nranks = nranks;
+    shared.device = h->device;
+  } else if (shared.rank != rank || shared.nranks != nranks || shared.device != h->device) {
+    return fail(FBFFTCONV_ERR_INVALID_ARGUMENT,
+                "this id already names a communicator of rank %d/%d on device %d; asked for rank %d/%d on device %d",
+                shared.rank, shared.nranks, shared.device, rank, nranks, h->device);
   }
   ++shared.refs;
   h->comm = shared.comm;

@@ -70,7 +70,7 @@ copy_or_add_kernel(const float* __restrict__ src, float* dst, long long n, int a
 cudaError_t launch_copy_or_add(const float* src, float* dst, long long n, int accumulate, cudaStream_t stream) {
   if (n <= 0) return cudaSuccess;
   const long long want = (n + 255) / 256;
-  const int blocks = (int)(want < 148 * 8 ? want : 148 * 8);
+  const int blocks = (int)(want < sm_count() * 8 ? want : sm_count() * 8);
   copy_or_add_kernel<<<blocks, 256, 0, stream>>>(src, dst, n, accumulate);
   count_launch();
   return cudaGetLastError();
@@ -79,7 +79,7 @@ cudaError_t launch_copy_or_add(const float* src, float* dst, long long n, int ac
 cudaError_t launch_bias_add(float* out, const float* bias, int batch, int planes, int hw,
                             cudaStream_t stream) {
   const long long total = (long long)batch * planes * hw;
-  const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  const int blocks = (int)((total + 255) / 256 < sm_count() * 16 ? (total + 255) / 256 : sm_count() * 16);
   bias_add_kernel<<<blocks > 0 ? blocks : 1, 256, 0, stream>>>(out, bias, planes, hw, total);
   count_launch();
   return cudaGetLastError();

@@ -59,10 +59,7 @@ __device__ __forceinline__ void copy_wait() {
 }
 __device__ __forceinline__ C2 as_c2(float4 v) { return C2{make_float2(v.x, v.y), make_float2(v.z, v.w)}; }
 
-#ifndef FBF_RING_STAGES
-#define FBF_RING_STAGES 3
-#endif
-constexpr int RING_STAGES = FBF_RING_STAGES;  // iterations of w in flight per thread
+constexpr int RING_STAGES = 3;  // iterations of w in flight per thread (measured best of 2 / 3 / 4 / 6)
 
 // Z[u][v][bin] = alpha * sum_{p<P} X[u][p][bin] * conj(Y[v][p][bin])
 // block: TU rows u, a chunk of columns v, 512 bins; the Y planes of the next RING_STAGES - 1
@@ -179,7 +176,7 @@ cudaError_t launch_stream_expand(const float2* x, const float2* y, float2* z, in
   constexpr int TU = 4;
   const int bin_blocks = (int)((bins / 2 + THREADS - 1) / THREADS);
   int v_chunks = 1;
-  while (v_chunks < 8 && (long long)bin_blocks * ((U + TU - 1) / TU) * v_chunks < 148 * 8 && V / (v_chunks * 2) >= 8)
+  while (v_chunks < 8 && (long long)bin_blocks * ((U + TU - 1) / TU) * v_chunks < sm_count() * 8 && V / (v_chunks * 2) >= 8)
     v_chunks *= 2;
   const int v_per_block = (V + v_chunks - 1) / v_chunks;
   dim3 grid(bin_blocks, (U + TU - 1) / TU, (V + v_per_block - 1) / v_per_block);
@@ -200,22 +197,15 @@ cudaError_t launch_stream_reduce(const float2* x, const float2* y, float2* z, in
   // block keep every SM busy instead.
   auto blocks_for = [&](int nt, int tu) { return (long long)((bins / 2 + nt - 1) / nt) * ((U + tu - 1) / tu); };
   // most rows per block that still gives every SM three blocks; 128-thread blocks below that
+  const long long sms = sm_count();
   int tu = 1, nt = 128;
-  if (blocks_for(128, 4) >= 3 * 148) {
+  if (blocks_for(128, 4) >= 3 * sms) {
     tu = 4;
-  } else if (blocks_for(256, 2) >= 2 * 148) {
+  } else if (blocks_for(256, 2) >= 2 * sms) {
     tu = 2;
     nt = 256;
-  } else if (2 * blocks_for(128, 2) >= 3 * 148) {  // measured at 16 rows: 42 us against 51 (one row) and 49 (four)
+  } else if (2 * blocks_for(128, 2) >= 3 * sms) {  // measured at 16 rows: 42 us against 51 (one row) and 49 (four)
     tu = 2;
-  }
-  static const int forced = [] {  // tuning aid: FBFFTCONV_REDUCE_ROWS = 1, 2 or 4 rows per 128-thread block
-    const char* e = getenv("FBFFTCONV_REDUCE_ROWS");
-    return e ? atoi(e) : 0;
-  }();
-  if (forced == 1 || forced == 2 || forced == 4) {
-    tu = forced;
-    nt = 128;
   }
   dim3 grid((unsigned)((bins / 2 + nt - 1) / nt), (U + tu - 1) / tu);
   if (grid.y > 65535) return cudaErrorInvalidValue;

@@ -476,8 +476,7 @@ cudaError_t launch_contract_tc_wide(const ContractParams& p, cudaStream_t stream
   t.s_b2_im = sa;
   cudaError_t e = cudaFuncSetAttribute(contract_tc_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, W_SMEM_BYTES);
   if (e != cudaSuccess) return e;
-  int dev = 0, sms = 148;
-  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int sms = sm_count();
   const int grid = (int)(total < sms ? total : sms);
   contract_tc_wide_kernel<<<grid, W_THREADS, W_SMEM_BYTES, stream>>>(map_a, map_b, t);
   count_launch();
@@ -486,8 +485,7 @@ cudaError_t launch_contract_tc_wide(const ContractParams& p, cudaStream_t stream
 
 cudaError_t launch_contract_tc(const ContractParams& p, cudaStream_t stream) {
   if (!contract_tc_supported(p)) return cudaErrorInvalidValue;
-  static const bool narrow_only = getenv("FBFFTCONV_TC_NARROW") != nullptr;  // tuning aid
-  if (!narrow_only && p.ldc >= 96) return launch_contract_tc_wide(p, stream);
+  if (p.ldc >= 96) return launch_contract_tc_wide(p, stream);
   CUtensorMap map_a, map_b;
   if (!make_map(&map_a, p.a, 2 * p.lda, p.m, p.bins, BM) || !make_map(&map_b, p.b, 2 * p.ldb, p.n, p.bins, BNC))
     return cudaErrorInvalidValue;

@@ -235,9 +235,7 @@ struct FftGeom {
 };
 
 static inline bool cooperative(int N) { return N > 32; }
-#ifndef FBF_COOP_THREADS
-#define FBF_COOP_THREADS 256
-#endif
+#define FBF_COOP_THREADS 256  // more threads per block (384, 512) measured slower
 static_assert(FBF_COOP_THREADS % 32 == 0, "whole warps, and a multiple of every N2");
 static inline int coop_threads() { return FBF_COOP_THREADS; }
 

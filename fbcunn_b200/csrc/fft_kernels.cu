@@ -61,24 +61,6 @@ __device__ __forceinline__ void prefetch_l2(const void* p) {
   asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
 }
 
-#ifdef FBF_PHASE_TIMING
-// Debug builds only: clock cycles spent between phase boundaries, summed over blocks
-// (thread 0 of each block), read back through fbfft_debug_phase_clocks().
-__device__ unsigned long long g_phase_clocks[16];
-#define FBF_PHASE_BEGIN() long long fbf_t0 = clock64()
-#define FBF_PHASE_MARK(i)                                                   \
-  do {                                                                      \
-    if (threadIdx.x == 0) {                                                 \
-      const long long fbf_t1 = clock64();                                   \
-      atomicAdd(&g_phase_clocks[i], (unsigned long long)(fbf_t1 - fbf_t0)); \
-      fbf_t0 = fbf_t1;                                                      \
-    }                                                                       \
-  } while (0)
-#else
-#define FBF_PHASE_BEGIN()
-#define FBF_PHASE_MARK(i)
-#endif
-
 template <int N, int T>
 __global__ void __launch_bounds__(FBF_COOP_THREADS, 2)
 fft2d_forward_coop_kernel(const __grid_constant__ FftParams p, const __grid_constant__ FftGeom g) {
@@ -102,12 +84,10 @@ fft2d_forward_coop_kernel(const __grid_constant__ FftParams p, const __grid_cons
       for (long long off = (long long)tid * 128; off < plane_bytes; off += (long long)nth * 128) prefetch_l2(src + off);
     }
   }
-  FBF_PHASE_BEGIN();
   for (int line0 = 0; line0 < g.lines1; line0 += g.chunk) {
     const int nl = min(g.chunk, g.lines1 - line0);
     CoopForward<N, T>::row_step1(p, g, smem, tid, nth, row, inner0, line0, nl);
     __syncthreads();
-    FBF_PHASE_MARK(0);
     // groups of eight lanes hold the eight residues of one line; mirror residues are
     // neighbours, so one shuffle hands each lane the partner's odd-indexed outputs
     constexpr int N1 = CoopForward<N, T>::N1, N2 = CoopForward<N, T>::N2;
@@ -123,16 +103,13 @@ fft2d_forward_coop_kernel(const __grid_constant__ FftParams p, const __grid_cons
       if (active) CoopForward<N, T>::row_step2_split(g, smem, base + tid, line0, u, mirror_odd);
     }
     __syncthreads();
-    FBF_PHASE_MARK(1);
   }
   CoopForward<N, T>::col_step1(g, smem, tid, nth);
   __syncthreads();
-  FBF_PHASE_MARK(2);
   if (p.spec_bin == 1 && p.spec_inner == (N / 2 + 1) * N)
     CoopForward<N, T>::template col_step2<true>(p, g, smem, tid, nth, row, inner0);
   else
     CoopForward<N, T>::template col_step2<false>(p, g, smem, tid, nth, row, inner0);
-  FBF_PHASE_MARK(3);
   __syncthreads();  // the buffers are reused by the next tile
   }
 }
@@ -157,24 +134,19 @@ fft2d_inverse_coop_kernel(const __grid_constant__ FftParams p, const __grid_cons
       for (long long off = (long long)tid * 128; off < plane_bytes; off += (long long)nth * 128) prefetch_l2(src + off);
     }
   }
-  FBF_PHASE_BEGIN();
   if (p.spec_bin == 1 && p.spec_inner == (N / 2 + 1) * N)
     CoopInverse<N, T>::template col_step1<true>(p, g, smem, tid, nth, row, inner0);
   else
     CoopInverse<N, T>::template col_step1<false>(p, g, smem, tid, nth, row, inner0);
   __syncthreads();
-  FBF_PHASE_MARK(8);
   CoopInverse<N, T>::col_step2(g, smem, tid, nth);
   __syncthreads();
-  FBF_PHASE_MARK(9);
   for (int line0 = 0; line0 < g.lines1; line0 += g.chunk) {
     const int nl = min(g.chunk, g.lines1 - line0);
     CoopInverse<N, T>::row_step1(p, g, smem, tid, nth, line0, nl);
     __syncthreads();
-    FBF_PHASE_MARK(10);
     CoopInverse<N, T>::row_step2(p, g, smem, tid, nth, row, inner0, line0, nl);
     __syncthreads();
-    FBF_PHASE_MARK(11);
   }
   }
 }
@@ -248,21 +220,8 @@ constexpr int kSmemTwoBlocks = 113 * 1024;
 
 constexpr bool tile_allowed(int N, int T) { return N > 32 ? T <= 8 : (N / 2 + 1) * T <= 512; }
 
-// Tuning aid: FBFFTCONV_TILE=<planes per block> overrides the automatic choice when valid.
-int tile_override() {
-  static int value = [] {
-    const char* e = getenv("FBFFTCONV_TILE");
-    return e ? atoi(e) : 0;
-  }();
-  return value;
-}
-
 template <class GeomFn>
 int pick_tile(int N, GeomFn geom) {
-  const int forced = tile_override();
-  if (forced > 0 && forced <= 16 && (forced & (forced - 1)) == 0 && tile_allowed(N, forced) &&
-      geom(forced).smem_bytes <= kSmemMax)
-    return forced;
   int best_any = 0;
   // 32-point transforms: 8 planes per block (more blocks per SM at 64-86 registers per thread) measured 5-10 %
   // faster than 16; 8- and 16-point ones are fastest at 16
@@ -277,11 +236,7 @@ int pick_tile(int N, GeomFn geom) {
 
 // Blocks of a persistent cooperative kernel: as many as are resident at once.
 int persistent_blocks(long long tiles, int smem_bytes) {
-  static int sms = [] {
-    int dev = 0, n = 148;
-    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    return n > 0 ? n : 148;
-  }();
+  const int sms = sm_count();
   const int per_sm = smem_bytes <= kSmemTwoBlocks ? 2 : 1;
   const long long resident = (long long)sms * per_sm;
   return (int)(tiles < resident ? tiles : resident);
@@ -357,6 +312,21 @@ cudaError_t dispatch(bool inverse, const FftParams& p, int N, int T, cudaStream_
 }
 
 }  // namespace
+
+int sm_count() {
+  constexpr int kMaxDevices = 64;
+  static std::atomic<int> cache[kMaxDevices];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) dev = 0;
+  int n = cache[dev].load(std::memory_order_relaxed);
+  if (n > 0) return n;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
+    cudaGetLastError();
+    return 1;  // not cached: asked again at the next launch
+  }
+  cache[dev].store(n, std::memory_order_relaxed);
+  return n;
+}
 
 void count_launch(int n) { g_launches.fetch_add(static_cast<uint64_t>(n), std::memory_order_relaxed); }
 uint64_t launch_count() { return g_launches.load(std::memory_order_relaxed); }
@@ -458,12 +428,3 @@ cudaError_t launch_fft1d(bool inverse, const float* real_in, float* real_out, fl
 
 }  // namespace fbfft
 
-#ifdef FBF_PHASE_TIMING
-extern "C" void fbfft_debug_phase_clocks(unsigned long long* out, int reset) {
-  cudaMemcpyFromSymbol(out, fbfft::g_phase_clocks, sizeof(fbfft::g_phase_clocks));
-  if (reset) {
-    unsigned long long zero[16] = {};
-    cudaMemcpyToSymbol(fbfft::g_phase_clocks, zero, sizeof(zero));
-  }
-}
-#endif

@@ -11,6 +11,10 @@ namespace fbfft {
 void count_launch(int n = 1);
 uint64_t launch_count();
 
+// Streaming multiprocessors of the current device (queried once per device); grids of the
+// persistent kernels and the "does this launch fill the GPU" decisions are sized from it.
+int sm_count();
+
 // Largest plane tile (planes per block) whose shared memory fits, preferring two
 // resident blocks per SM; 0 when even one plane does not fit.
 int pick_forward_tile(int N, int h, int w, int pad_u, int pad_l);

@@ -8,6 +8,20 @@
    bias-FFI sequence of the reference (fbcunn/SpatialConvolutionFBFFT.lua:102-354);
    there is no cudnn fallback: a failed pass raises a Lua error.
 
+   Surface kept for the reference's callers:
+     * nn.Module: updateOutput / updateGradInput / accGradParameters / backward / reset;
+     * the per-pass implementations updateOutputFFTImpl(input, reuseList, metaData),
+       updateGradInputFFTImpl(input, gradOutput, reuseList, metaData) and
+       accGradParametersFFTImpl(input, gradOutput, scale, reuseList, metaData), which honour
+       metaData.skipBias (fbcunn/SpatialConvolutionFBFFT.lua:172, :298);
+     * the fields fbnn.SpatialConvolution reads and sets: printDebugLevel, cudnnDebug, success,
+       autotuningPass, reportErrors, timeSteps (fbcunn/SpatialConvolutionFFT.lua:162-163, :259-268);
+     * the second class name nn.SpatialConvolutionFBFFTGemm
+       (fbcunn/SpatialConvolutionFBFFTGemm.lua:18-66) over the same native path.
+   Not kept: the class derives from nn.Module, not from the reference's nn.SpatialConvolutionFFT,
+   so code that reaches into that base class's buffers, streams or FFTWrapper objects -- the
+   reference's own SpatialConvolutionFFTTiled*.lua files do -- does not run on it.
+
    Requires LuaJIT (ffi), torch, cutorch.  Not executed by this repository's tests
    (no Lua toolchain there); the same C ABI is exercised from Python.
 --]]
@@ -98,6 +112,12 @@ function SpatialConvolutionFBFFT:__init(nInputPlane, nOutputPlane, kW, kH, dW, d
    self.reuseWeights = has(SpatialConvolutionFBFFT.memoryReuseWeight)
    self.numCudaStreams = numCudaStreams or 16
    self.accumulateGrads = false   -- reference behaviour: accGradParameters overwrites
+   self.printDebugLevel = -1
+   self.cudnnDebug = false
+   self.success = true
+   self.autotuningPass = false
+   self.reportErrors = true
+   self.timeSteps = { updateOutput = 0, updateGradInput = 0, accGradParameters = 0 }
 
    self.weight = torch.Tensor(nOutputPlane, nInputPlane, kH, kW)
    self.bias = torch.Tensor(nOutputPlane)
@@ -152,32 +172,55 @@ local function stream()
    return ffi.C.THCState_getCurrentStream(cutorch._state)
 end
 
-function SpatialConvolutionFBFFT:updateOutput(input)
+-- self.output / self.gradInput are made CUDA tensors once and only resized afterwards.
+local function cudaResize(t, ...)
+   if torch.type(t) ~= 'torch.CudaTensor' then t = torch.CudaTensor() end
+   return t:resize(...)
+end
+
+function SpatialConvolutionFBFFT:updateOutputFFTImpl(input, reuseList, metaData)
    self:prepareSizeAndBuffers(input)
    local oH = input:size(3) + 2 * self.padUp - self.kH + 1
    local oW = input:size(4) + 2 * self.padLeft - self.kW + 1
-   self.output = self.output:cuda():resize(input:size(1), self.nOutputPlane, oH, oW)
-   local bias = (self.skipBias and nil) or self.bias:data()
+   self.output = cudaResize(self.output, input:size(1), self.nOutputPlane, oH, oW)
+   local bias = nil
+   if not (metaData and metaData.skipBias) then bias = self.bias:data() end
    check(C.fbfftconv_update_output(self.handle, input:data(), self.weight:data(), bias,
                                    self.output:data(), stream()))
    return self.output
 end
 
-function SpatialConvolutionFBFFT:updateGradInput(input, gradOutput)
+function SpatialConvolutionFBFFT:updateGradInputFFTImpl(input, gradOutput, reuseList, metaData)
    self:prepareSizeAndBuffers(input)
    assert(gradOutput:isContiguous())
-   self.gradInput = self.gradInput:cuda():resizeAs(input)
+   self.gradInput = cudaResize(self.gradInput, input:size())
    check(C.fbfftconv_update_grad_input(self.handle, gradOutput:data(), self.weight:data(),
                                        self.gradInput:data(), stream()))
    return self.gradInput
 end
 
-function SpatialConvolutionFBFFT:accGradParameters(input, gradOutput, scale)
+function SpatialConvolutionFBFFT:accGradParametersFFTImpl(input, gradOutput, scale, reuseList, metaData)
    self:prepareSizeAndBuffers(input)
    assert(gradOutput:isContiguous())
-   local gradBias = (self.skipBias and nil) or self.gradBias:data()
+   local gradBias = nil
+   if not (metaData and metaData.skipBias) then gradBias = self.gradBias:data() end
    check(C.fbfftconv_acc_grad_parameters(self.handle, input:data(), gradOutput:data(),
                                          self.gradWeight:data(), gradBias, scale or 1, stream()))
+end
+
+function SpatialConvolutionFBFFT:updateOutput(input)
+   self.timeSteps.updateOutput = self.timeSteps.updateOutput + 1
+   return self:updateOutputFFTImpl(input)
+end
+
+function SpatialConvolutionFBFFT:updateGradInput(input, gradOutput)
+   self.timeSteps.updateGradInput = self.timeSteps.updateGradInput + 1
+   return self:updateGradInputFFTImpl(input, gradOutput)
+end
+
+function SpatialConvolutionFBFFT:accGradParameters(input, gradOutput, scale)
+   self.timeSteps.accGradParameters = self.timeSteps.accGradParameters + 1
+   self:accGradParametersFFTImpl(input, gradOutput, scale)
 end
 
 function SpatialConvolutionFBFFT:backward(input, gradOutput, scale)
@@ -203,4 +246,14 @@ function SpatialConvolutionFBFFT:cleanupBuffers()
    self.handle = nil      -- ffi.gc destroys the native handle and its scratch
    self.handleKey = nil
    collectgarbage()
+end
+
+-- The reference's cgeam + cgemm variant (fbcunn/SpatialConvolutionFBFFTGemm.lua) under its own
+-- class name: the spectra are bin-major from the transform on and the per-bin product is the same
+-- tensor-core contraction, so the variant is this module.
+local SpatialConvolutionFBFFTGemm, gemmParent =
+   torch.class('nn.SpatialConvolutionFBFFTGemm', 'nn.SpatialConvolutionFBFFT')
+
+function SpatialConvolutionFBFFTGemm:__init(...)
+   gemmParent.__init(self, ...)
 end

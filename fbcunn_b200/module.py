@@ -97,6 +97,13 @@ class SpatialConvolutionFBFFT:
         self.output: Optional[torch.Tensor] = None
         self.gradInput: Optional[torch.Tensor] = None
         self.timeSteps = {"updateOutput": 0, "updateGradInput": 0, "accGradParameters": 0}
+        # fields the reference's callers read or set on the module (fbcunn/SpatialConvolutionFFT.lua:162-163,
+        # :259-268; fbnn.SpatialConvolution, fbcunn/SpatialConvolution.lua:188-422)
+        self.printDebugLevel = -1
+        self.cudnnDebug = False
+        self.success = True
+        self.autotuningPass = False
+        self.reportErrors = True
         self._handle = None
         self._handle_key = None
         self._comm = None
@@ -147,6 +154,21 @@ class SpatialConvolutionFBFFT:
         capi.check(capi.lib().fbfftconv_acc_grad_parameters(
             h, _ptr(input), _ptr(gradOutput), _ptr(self.gradWeight),
             None if skipBias else _ptr(self.gradBias), ctypes.c_float(scale), _stream(self.device)))
+
+    # The per-pass implementations the reference's subclasses and wrappers call directly
+    # (fbcunn/SpatialConvolutionFBFFT.lua:102, :189, :269; callers
+    # fbcunn/SpatialConvolutionFFTTiled.lua:262-263, :479, :593, :714).  `reuseList` is accepted for
+    # signature compatibility (the reuse policy of the module decides); `metaData` may carry
+    # skipBias, which the tiled callers set to add the bias once after the last tile.
+    def updateOutputFFTImpl(self, input, reuseList=None, metaData=None):
+        return self.updateOutput(input, skipBias=bool(metaData and metaData.get("skipBias")))
+
+    def updateGradInputFFTImpl(self, input, gradOutput, reuseList=None, metaData=None):
+        return self.updateGradInput(input, gradOutput)
+
+    def accGradParametersFFTImpl(self, input, gradOutput, scale=None, reuseList=None, metaData=None):
+        return self.accGradParameters(input, gradOutput, scale,
+                                      skipBias=bool(metaData and metaData.get("skipBias")))
 
     def forward(self, input):
         return self.updateOutput(input)
@@ -258,6 +280,39 @@ class SpatialConvolutionFBFFT:
             self.cleanupBuffers()
         except Exception:
             pass
+
+
+class SpatialConvolutionFBFFTGemm(SpatialConvolutionFBFFT):
+    """nn.SpatialConvolutionFBFFTGemm (fbcunn/SpatialConvolutionFBFFTGemm.lua:18-66): the variant of
+    the reference that transposes its spectra with cublasCgeam and multiplies them with
+    cublasCgemmBatched.  Here the spectra are written bin-major by the transform itself and the
+    per-bin product is the same tensor-core contraction, so the variant is the same native path
+    under the reference's second class name."""
+
+
+class CuBLASWrapper:
+    """nn.CuBLASWrapper (fbcunn/CuBLASWrapper.lua:1-49) for the one use the convolution makes of it:
+    matmultComplex on bin-major operands, C[bin] = scale * op(A[bin]) * op(B[bin]) with op 'n' or 'c'
+    (fbcunn/SpatialConvolutionFBFFTGemm.lua:179-186, :301-308, :424-431).  A is (bins, m, k),
+    B is (bins, n, k), C is (bins, m, n), complex64, k and n padded to multiples of 4 (see
+    fbfftconv_transpose_mm): the rows of B are what the reference reaches with transB."""
+
+    def __init__(self, timed=False):
+        self.timed = bool(timed)
+
+    def matmultComplex(self, A, B, C, iterDims=(), batchDims=(), transA="n", transB="n", scale=1.0):
+        assert transA in ("n", "c") and transB in ("n", "c")
+        assert A.is_cuda and A.dtype == torch.complex64 and A.dim() == 3 and A.is_contiguous()
+        assert B.dtype == torch.complex64 and B.dim() == 3 and B.is_contiguous()
+        assert C.dtype == torch.complex64 and C.dim() == 3 and C.is_contiguous()
+        bins, m, kpad = A.shape
+        n = B.shape[1]
+        assert B.shape[0] == bins and B.shape[2] == kpad and kpad % 4 == 0
+        assert tuple(C.shape) == (bins, m, (n + 3) // 4 * 4)
+        capi.check(capi.lib().fbfftconv_transpose_mm(
+            _ptr(A), _ptr(B), _ptr(C), bins, m, n, kpad, ctypes.c_float(scale),
+            int(transA == "c"), int(transB == "c"), 0, _stream(A.device)))
+        return C
 
 
 class FFTWrapper:

@@ -111,7 +111,11 @@ size_t fbfftconv_workspace_bytes(const fbfftconv_handle* h);
  * first pass and freed by fbfftconv_destroy. */
 int fbfftconv_set_workspace(fbfftconv_handle* h, void* device_ptr, size_t bytes);
 
-/* ---- the three nn passes, device pointers ----------------------------------- */
+/* ---- the three nn passes, device pointers -----------------------------------
+ * Every tensor argument is checked before anything is launched: a host pointer or memory of
+ * another GPU than the handle's returns FBFFTCONV_ERR_INVALID_ARGUMENT (what
+ * THCudaTensor_checkGPU does for the reference's bindings,
+ * src/fft/SpatialConvolutionCuFFTHost.cpp:33-66).  Managed memory is accepted. */
 
 /* Replaces SpatialConvolutionFBFFT:updateOutputFFTImpl
  * (fbcunn/SpatialConvolutionFBFFT.lua:102-183): FFT(input), FFT(weight),
@@ -209,7 +213,9 @@ int fbfftconv_transpose_mm(const void* a, const void* b, void* c, int bins, int 
 /* The tensor-core contraction bounds every wait on the device; a block whose wait runs out
  * stops, frees its tensor memory and records a non-zero code.  This call waits for the
  * device and returns the first such code since the last reset (0 = none, -1 = the query
- * itself failed). */
+ * itself failed).  The host-buffer entry points and fbfftconv_host_sync, which wait for the
+ * device anyway, check it themselves and return FBFFTCONV_ERR_CUDA; callers of the
+ * device-pointer passes, which never wait, poll it where they synchronise. */
 int fbfftconv_tensor_core_status(int reset);
 /* Replaces updateOutputBiasFFI (fbcunn/FFTCDefs.lua:4, src/ConvolutionBias.cu:39-51). */
 int fbfftconv_update_output_bias(float* output, const float* bias, int batch, int planes, int h,

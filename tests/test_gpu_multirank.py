@@ -4,8 +4,8 @@ With a communicator attached the weight and bias gradients are summed over ranks
 inside accGradParameters (what nn.DataParallel's gradient combine does for the
 reference module, fbcunn/DataParallel.lua:105-131): either the gradWeight spectrum
 before the inverse transform or gradWeight after it.  A one-rank communicator runs
-the whole path on a single GPU; the two-rank case needs two GPUs and is skipped
-otherwise.  Tolerance: max|x - ref| <= 1e-4 * max|ref| against the fp64 oracle.
+the whole path on a single GPU; the 2-, 3-, 4- and 8-rank cases need that many GPUs and
+are skipped otherwise.  Tolerance: max|x - ref| <= 1e-4 * max|ref| against the fp64 oracle.
 """
 import os
 import socket
@@ -80,9 +80,23 @@ def _free_port():
     return port
 
 
+# Shapes for the ranks: every exchange of accGradParameters is reached --
+#   plane-major, filters divisible by the ranks   -> reduce-scatter by filters + all-gather
+#   plane-major, filters not divisible             -> all-reduce of the whole spectrum
+#   bin-major, bins divisible by the ranks         -> reduce-scatter by bin range + all-reduce of partial transforms
+#   bin-major, bins not divisible (3 ranks: N = 16 has 144 bins, N = 32 has 544)  -> all-reduce of the whole spectrum
+RANK_SHAPES = [
+    oracle.Shape(B=8, P=5, F=7, iH=12, iW=11, kH=3, kW=4, padH=1, padW=0),      # bin-major, CUDA-core contraction, N=16
+    oracle.Shape(B=16, P=16, F=24, iH=20, iW=20, kH=5, kW=5, padH=0, padW=0),   # bin-major, tensor cores, N=32
+    oracle.Shape(B=8, P=3, F=8, iH=40, iW=36, kH=7, kW=7, padH=0, padW=0),      # plane-major, F = 8
+    oracle.Shape(B=9, P=2, F=7, iH=33, iW=40, kH=5, kW=3, padH=1, padW=1),      # plane-major, F = 7, ragged batch split
+]
+
+
 def _worker(rank, world, port, out_dir):
     sys.path.insert(0, ROOT)
     import torch.distributed as dist
+    from fbcunn_b200 import capi
     from fbcunn_b200.sharding import batch_slice, share_unique_id
 
     os.environ["MASTER_ADDR"] = "127.0.0.1"
@@ -91,27 +105,40 @@ def _worker(rank, world, port, out_dir):
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         uid = share_unique_id(dist, SpatialConvolutionFBFFT.makeUniqueId, device="cpu")
-        worst = 0.0
-        for idx, s in enumerate(SHAPES):
+        worst, cases = 0.0, 0
+        for idx, s in enumerate(RANK_SHAPES):
             x, go = _data(s, 70 + idx)  # same on every rank
             b0, b1 = batch_slice(s.B, rank, world)
             local = oracle.Shape(b1 - b0, s.P, s.F, s.iH, s.iW, s.kH, s.kW, s.padH, s.padW)
             ref_w = oracle.acc_grad_weight(s, x, go, 2.0)
             ref_b = oracle.acc_grad_bias(s, go, 2.0)
             for allreduce in ("spectrum", "spatial"):
-                gw, gb = _grads(local, np.ascontiguousarray(x[b0:b1]), np.ascontiguousarray(go[b0:b1]), 2.0,
-                                allreduce, (uid, rank, world), device=f"cuda:{rank}")
-                worst = max(worst, _rel(gw, ref_w), _rel(gb, ref_b))
+                for accumulate in (False, True):
+                    gw, gb = _grads(local, np.ascontiguousarray(x[b0:b1]), np.ascontiguousarray(go[b0:b1]), 2.0,
+                                    allreduce, (uid, rank, world), accumulate=accumulate, device=f"cuda:{rank}")
+                    worst = max(worst, _rel(gw, ref_w + (1.0 if accumulate else 0.0)),
+                                _rel(gb, ref_b + (2.0 if accumulate else 0.0)))
+                    cases += 1
+        import gc
+        gc.collect()  # the modules detach from the communicator before it is shut down
+        rc = capi.lib().fbfftconv_comm_shutdown()
         with open(os.path.join(out_dir, f"rank{rank}"), "w") as f:
-            f.write(repr(worst))
+            f.write(repr((worst, cases, rc)))
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_two_ranks_sum_the_gradient(tmp_path):
-    world = 2
+@pytest.mark.parametrize("world", [2, 3, 4, 8])
+def test_ranks_sum_the_gradient(tmp_path, world):
+    """Every rank ends with the gradient of the whole batch, as the reference's data-parallel
+    test asserts of its replicas (test/test_DataParallel.lua:73-159)."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
     for rank in range(world):
-        worst = float(open(tmp_path / f"rank{rank}").read())
+        worst, cases, rc = eval(open(tmp_path / f"rank{rank}").read())
+        assert cases == 4 * len(RANK_SHAPES)
+        assert rc == 0, f"rank {rank}: communicator still attached at shutdown"
         assert worst <= PASS_TOL, f"rank {rank}: {worst}"
+    print(f"world {world}: {4 * len(RANK_SHAPES)} cases per rank, worst relative error "
+          f"{max(eval(open(tmp_path / f'rank{r}').read())[0] for r in range(world)):.2e}")
