@@ -41,7 +41,7 @@ LAYERS = {
 }
 PASSES = ("updateOutput", "updateGradInput", "accGradParameters")
 STAGES = ("fft_a", "fft_b", "contract", "allreduce", "ifft", "bias")
-METRIC = "direct-conv-equivalent TFLOP/s, updateOutput+updateGradInput+accGradParameters"
+METRIC = "direct-conv-equivalent TFLOP/s, 3 passes (fwd+bwd+accGrad)"
 PARITY_TOL = 1e-4  # max|x - ref| <= PARITY_TOL * max|ref| against the fp64 direct convolution
 
 
@@ -198,10 +198,9 @@ def workload_config(name, L, gpus, allreduce="spectrum", reuse="none"):
     return {
         "workload": f"{name}: {B}x{P}x{iH}x{iW} input, {F} filters {kH}x{kW}, pad {pH}, FFT {fft_size(L)}; step = 3 passes",
         "global_batch": B,
-        "parallelism": (f"batch over {gpus} ranks, gradWeight "
-                        + ("spectrum" if allreduce == "spectrum" else "(spatial)") + " summed by NCCL")
-        if gpus > 1 else "single GPU",
-        "l2": "inputs > L2" if step_bytes(L) > (126 << 20) else "inputs fit L2 (warm); per-layer rows follow a flush",
+        "parallelism": (f"batch/{gpus} ranks, gradWeight " + ("spectrum" if allreduce == "spectrum" else "(spatial)")
+                        + " NCCL-summed") if gpus > 1 else "single GPU",
+        "l2": "inputs > L2" if step_bytes(L) > (126 << 20) else "inputs fit L2 (warm); layers_step_ms after flush",
         "memory_reuse": reuse,
     }
 
@@ -462,7 +461,6 @@ def run_gpu_arm(args):
     barrier()
     elapsed_ms = max_over_ranks(ev0.elapsed_time(ev1))
     launches = capi.kernel_launches() - launches0
-    clocks = sampler.stop() if rank == 0 else None
     prof = read_profile(run.handle())
     capi.check(lib.fbfftconv_profile_enable(run.handle(), 0))
     device_status = int(lib.fbfftconv_tensor_core_status(0))
@@ -482,7 +480,7 @@ def run_gpu_arm(args):
     if fl and fl / by > ridge:
         achieved = fl / secs / 1e12
         roofline = {"bound": "tensor", "kernel": f'{top["kernel"]} of {top["pass"]}', "achieved": achieved,
-                    "peak": tensor_peak_3xtf32(pk), "peak_source": pk["source"] + " bf16 / 2 (TF32) / 3 (3xTF32)",
+                    "peak": tensor_peak_3xtf32(pk), "peak_source": pk["source"] + " bf16/6 (3xTF32)",
                     "unit": "TFLOP/s", "frac": achieved / tensor_peak_3xtf32(pk), "traffic": None,
                     "algorithmic_flops_per_launch": fl}
     else:
@@ -497,6 +495,8 @@ def run_gpu_arm(args):
     # ---- e2e: host buffers through the *_host entry points ----------------------
     e2e = measure_e2e(torch, lib, run, L, local_b, world, barrier, max_over_ranks,
                       steps=max(1, min(args.steps, 5)))
+
+    clocks = sampler.stop() if rank == 0 else None  # sampled from the warm-up to the end of the e2e leg
 
     # ---- parity of what was timed, on sampled planes (not timed) -------------------
     parity = None
@@ -562,10 +562,10 @@ def run_gpu_arm(args):
         dt2, kind = cpu_reference_step(L, threads, items, filters, seed=1)
         dt = min(dt, dt2)
         cpu = {"value": sig(sample_flops(L, items, filters) / dt / 1e12), "unit": "TFLOP/s",
-               "cores": min(threads, items), "host_cores": threads, "kind": kind,
+               "cores": min(threads, items), "kind": kind,
                "one_thread_value": sig(sample_flops(L, items1, filters1) / dt1 / 1e12),
                "sample": f"{items}/{L[0]} batch x {filters}/{L[2]} filters, {dt:.1f} s; 1 thread: {items1} x {filters1}, "
-                         f"{dt1:.1f} s; scaled linearly"}
+                         f"{dt1:.1f} s; linear"}
 
     if rank == 0:
         detail = {"kernels": kernels, "layers": layers, "roofline": roofline, "e2e": e2e, "parity": parity,

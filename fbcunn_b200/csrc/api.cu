@@ -307,8 +307,10 @@ FftParams forward_params(const float* real, float2* spec, int d1, int d2, int h,
   return p;
 }
 
+// layout as in forward_params: 0 = spectrum [bin][d1][d2], 1 = [bin][d2][d1], 2 = plane-major [d1][d2][bin];
+// the real tensor is (d1, d2, h, w) and bias has d2 entries in every case.
 FftParams inverse_params(const float2* spec, float* real, const float* bias, int d1, int d2, int h,
-                         int w, int off_y, int off_x, int accumulate, bool plane_major, int fft_size) {
+                         int w, int off_y, int off_x, int accumulate, int layout, int fft_size) {
   FftParams p{};
   p.real_out = real;
   p.spec = const_cast<float2*>(spec);
@@ -317,17 +319,33 @@ FftParams inverse_params(const float2* spec, float* real, const float* bias, int
   p.w = w;
   p.off_y = off_y;
   p.off_x = off_x;
-  p.n_rows = d1;
-  p.n_inner = d2;
-  p.real_row_stride = d2;
-  p.real_inner_stride = 1;
+  if (layout != 1) {
+    p.n_rows = d1;
+    p.n_inner = d2;
+    p.real_row_stride = d2;
+    p.real_inner_stride = 1;
+  } else {
+    p.n_rows = d2;
+    p.n_inner = d1;
+    p.real_row_stride = 1;
+    p.real_inner_stride = d2;
+    p.bias_by_row = 1;
+  }
   p.accumulate = accumulate;
-  set_spectrum_layout(p, fft_size, plane_major);
+  set_spectrum_layout(p, fft_size, layout == 2);
   return p;
 }
 
+// With a small batch (a shard of a data-parallel step) the batch goes on the column side of the
+// tensor-core contraction, whose tile narrows to 16 / 32 / 64 columns, and the filters or input
+// planes fill the 128 rows of the MMA; the product then comes out transposed ([bin][f][b] instead of
+// [bin][b][f]) and the inverse transform reads it that way.  At 128 images nothing changes.
+bool batch_on_columns(int batch, int other) { return batch <= 64 && other > batch; }
+
+// An operand is [bins][rows][pad4(k)], or -- `mn` set -- [bins][k][pad4(rows)]: the spectra are written
+// once, plane index innermost, and a pass whose sum runs over the outer plane index reads them that way.
 int contract(const float2* a, const float2* b, float2* c, int bins, int m, int n, int k, float alpha,
-             int conj_a, int conj_b, bool simt, cudaStream_t s) {
+             int conj_a, int conj_b, bool simt, cudaStream_t s, bool a_mn = false, bool b_mn = false) {
   ContractParams p{};
   p.a = a;
   p.b = b;
@@ -336,11 +354,14 @@ int contract(const float2* a, const float2* b, float2* c, int bins, int m, int n
   p.m = m;
   p.n = n;
   p.k = k;
-  p.lda = p.ldb = pad4(k);
+  p.lda = a_mn ? pad4(m) : pad4(k);
+  p.ldb = b_mn ? pad4(n) : pad4(k);
   p.ldc = pad4(n);
   p.alpha = alpha;
   p.conj_a = conj_a;
   p.conj_b = conj_b;
+  p.a_mn = a_mn;
+  p.b_mn = b_mn;
   if (!simt && contract_tc_supported(p)) {
     FBF_CUDA(launch_contract_tc(p, s));
   } else {
@@ -477,7 +498,7 @@ int fbfftconv_create(const fbfftconv_desc* desc, fbfftconv_handle** out) {
   h->bytes_small = align256((B * F + F) * sizeof(float));
   // local gradWeight + gradBias where they are summed or gathered across ranks in the spatial domain
   h->bytes_small += align256((F * P * d.kernel_h * d.kernel_w + F) * sizeof(float));
-  h->bytes_gi = (h->plane_major && (d.flags & FBFFTCONV_REUSE_INPUT)) ? h->bytes_in : 0;
+  h->bytes_gi = (d.flags & FBFFTCONV_REUSE_INPUT) ? h->bytes_in : 0;
   h->bytes_total = h->bytes_in + h->bytes_out + h->bytes_w + h->bytes_small + h->bytes_gi;
   *out = h;
   return FBFFTCONV_OK;
@@ -549,6 +570,7 @@ int fbfftconv_update_output(fbfftconv_handle* h, const float* input, const float
   const bool simt = (d.flags & FBFFTCONV_CONTRACT_SIMT) || thin_contraction(B, F, P);
   const int pass = FBFFTCONV_PASS_UPDATE_OUTPUT;
   const bool pm = h->plane_major;
+  const bool flip = !pm && !simt && batch_on_columns(B, F);
   const float norm = 1.0f / (float)(h->N * h->N);
   // I^[bin][b][p], W^[bin][f][p]   (plane-major: I^[b][p][bin], W^[f][p][bin])
   {
@@ -570,17 +592,20 @@ int fbfftconv_update_output(fbfftconv_handle* h, const float* input, const float
     StageTimer t(h, pass, FBFFTCONV_STAGE_CONTRACT, s);
     if (pm) {
       FBF_CUDA(launch_stream_expand(h->buf_in(), h->buf_w(), h->buf_out(), B, F, P, h->bins, norm, s));
+    } else if (flip) {  // O^[f][b] = 1/N^2 sum_p conj(W^[f][p]) I^[b][p]
+      FBF_TRY(contract(h->buf_w(), h->buf_in(), h->buf_out(), h->bins, F, B, P, norm, 1, 0, simt, s));
     } else {
       FBF_TRY(contract(h->buf_in(), h->buf_w(), h->buf_out(), h->bins, B, F, P, norm, 0, 1, simt, s));
     }
   }
   {
     StageTimer t(h, pass, FBFFTCONV_STAGE_IFFT, s);
-    FBF_CUDA(launch_inverse(inverse_params(h->buf_out(), output, bias, B, F, h->oH, h->oW, 0, 0, 0, pm, h->N), h->N, s));
+    FBF_CUDA(launch_inverse(inverse_params(h->buf_out(), output, bias, B, F, h->oH, h->oW, 0, 0, 0,
+                                           pm ? 2 : (flip ? 1 : 0), h->N), h->N, s));
   }
-  // what the buffers hold now (plane-major spectra have one layout for all passes)
-  h->have_input_spec = pm;
-  h->have_weight_spec = pm;
+  // what the buffers hold now (every pass reads a tensor's spectrum in the one layout it is written in)
+  h->have_input_spec = true;
+  h->have_weight_spec = true;
   h->have_grad_output_spec = false;  // buf_out holds the output spectrum
   return FBFFTCONV_OK;
 }
@@ -601,40 +626,43 @@ int fbfftconv_update_grad_input(fbfftconv_handle* h, const float* grad_output, c
   const bool simt = (d.flags & FBFFTCONV_CONTRACT_SIMT) || thin_contraction(B, P, F);
   const int pass = FBFFTCONV_PASS_UPDATE_GRAD_INPUT;
   const bool pm = h->plane_major;
+  const bool flip = !pm && !simt && batch_on_columns(B, P);
   const float norm = 1.0f / (float)(h->N * h->N);
-  // O'^[bin][b][f], W^[bin][p][f] (weight planes transposed on the fly)
+  // O'^[bin][b][f], W^[bin][f][p] (the sum over f reads W^ with f as the row index)
   {
     Fork fork(h, s, forward_tiles(h->N, B, F, h->oH, h->oW, 0, 0, false),
-              forward_tiles(h->N, F, P, d.kernel_h, d.kernel_w, 0, 0, !pm));
+              forward_tiles(h->N, F, P, d.kernel_h, d.kernel_w, 0, 0, false));
     {
       StageTimer t(h, pass, FBFFTCONV_STAGE_FFT_A, s);
       FBF_CUDA(launch_forward(forward_params(grad_output, h->buf_out(), B, F, h->oH, h->oW, 0, 0, pm ? 2 : 0, h->N), h->N, s));
     }
-    h->have_grad_output_spec = pm;
-    if (!(pm && (d.flags & FBFFTCONV_REUSE_WEIGHT) && h->have_weight_spec)) {
+    h->have_grad_output_spec = true;
+    if (!((d.flags & FBFFTCONV_REUSE_WEIGHT) && h->have_weight_spec)) {
       StageTimer t(h, pass, FBFFTCONV_STAGE_FFT_B, fork.second());
       if (fork.active) h->overlapped[pass][FBFFTCONV_STAGE_FFT_B] = true;
-      FBF_CUDA(launch_forward(forward_params(weight, h->buf_w(), F, P, d.kernel_h, d.kernel_w, 0, 0, pm ? 2 : 1, h->N), h->N, fork.second()));
-      h->have_weight_spec = pm;
+      FBF_CUDA(launch_forward(forward_params(weight, h->buf_w(), F, P, d.kernel_h, d.kernel_w, 0, 0, pm ? 2 : 0, h->N), h->N, fork.second()));
+      h->have_weight_spec = true;
     }
     FBF_CUDA(fork.join());
   }
   // with REUSE_INPUT the input spectrum stays in its buffer for accGradParameters
   float2* gi = h->buf_gi();
   if (gi == h->buf_in()) h->have_input_spec = false;
-  // I'^[bin][b][p] = 1/N^2 sum_f O'^[b][f] W^[p][f]
+  // I'^[bin][b][p] = 1/N^2 sum_f O'^[b][f] W^[f][p]
   {
     StageTimer t(h, pass, FBFFTCONV_STAGE_CONTRACT, s);
     if (pm) {  // I'^[b][p] = sum_f O'^[b][f] W^[f][p]
       FBF_CUDA(launch_stream_reduce(h->buf_out(), h->buf_w(), gi, B, F, P, F, 1, false, h->bins, norm, s));
+    } else if (flip) {  // I'^[p][b] = 1/N^2 sum_f W^[f][p] O'^[b][f]
+      FBF_TRY(contract(h->buf_w(), h->buf_out(), gi, h->bins, P, B, F, norm, 0, 0, simt, s, true, false));
     } else {
-      FBF_TRY(contract(h->buf_out(), h->buf_w(), gi, h->bins, B, P, F, norm, 0, 0, simt, s));
+      FBF_TRY(contract(h->buf_out(), h->buf_w(), gi, h->bins, B, P, F, norm, 0, 0, simt, s, false, true));
     }
   }
   {
     StageTimer t(h, pass, FBFFTCONV_STAGE_IFFT, s);
     FBF_CUDA(launch_inverse(inverse_params(gi, grad_input, nullptr, B, P, d.input_h, d.input_w,
-                                           d.pad_h, d.pad_w, 0, pm, h->N), h->N, s));
+                                           d.pad_h, d.pad_w, 0, pm ? 2 : (flip ? 1 : 0), h->N), h->N, s));
   }
   return FBFFTCONV_OK;
 }
@@ -658,20 +686,20 @@ int fbfftconv_acc_grad_parameters(fbfftconv_handle* h, const float* input, const
   const int accumulate = (d.flags & FBFFTCONV_ACCUMULATE_GRADS) ? 1 : 0;
   const int pass = FBFFTCONV_PASS_ACC_GRAD_PARAMETERS;
   const bool pm = h->plane_major;
-  // O'^[bin][f][b], I^[bin][p][b]: the batch is the contraction index here
+  // O'^[bin][b][f], I^[bin][b][p]: the batch, the row index of both, is the contraction index here
   {
-    Fork fork(h, s, forward_tiles(h->N, B, F, h->oH, h->oW, 0, 0, !pm),
-              forward_tiles(h->N, B, P, d.input_h, d.input_w, d.pad_h, d.pad_w, !pm));
-    if (!(pm && (d.flags & FBFFTCONV_REUSE_OUTPUT) && h->have_grad_output_spec)) {
+    Fork fork(h, s, forward_tiles(h->N, B, F, h->oH, h->oW, 0, 0, false),
+              forward_tiles(h->N, B, P, d.input_h, d.input_w, d.pad_h, d.pad_w, false));
+    if (!((d.flags & FBFFTCONV_REUSE_OUTPUT) && h->have_grad_output_spec)) {
       StageTimer t(h, pass, FBFFTCONV_STAGE_FFT_A, s);
-      FBF_CUDA(launch_forward(forward_params(grad_output, h->buf_out(), B, F, h->oH, h->oW, 0, 0, pm ? 2 : 1, h->N), h->N, s));
-      h->have_grad_output_spec = pm;
+      FBF_CUDA(launch_forward(forward_params(grad_output, h->buf_out(), B, F, h->oH, h->oW, 0, 0, pm ? 2 : 0, h->N), h->N, s));
+      h->have_grad_output_spec = true;
     }
-    if (!(pm && (d.flags & FBFFTCONV_REUSE_INPUT) && h->have_input_spec)) {
+    if (!((d.flags & FBFFTCONV_REUSE_INPUT) && h->have_input_spec)) {
       StageTimer t(h, pass, FBFFTCONV_STAGE_FFT_B, fork.second());
       if (fork.active) h->overlapped[pass][FBFFTCONV_STAGE_FFT_B] = true;
-      FBF_CUDA(launch_forward(forward_params(input, h->buf_in(), B, P, d.input_h, d.input_w, d.pad_h, d.pad_w, pm ? 2 : 1, h->N), h->N, fork.second()));
-      h->have_input_spec = pm;
+      FBF_CUDA(launch_forward(forward_params(input, h->buf_in(), B, P, d.input_h, d.input_w, d.pad_h, d.pad_w, pm ? 2 : 0, h->N), h->N, fork.second()));
+      h->have_input_spec = true;
     }
     FBF_CUDA(fork.join());
   }
@@ -697,24 +725,24 @@ int fbfftconv_acc_grad_parameters(fbfftconv_handle* h, const float* input, const
                             api->ReduceScatter;
   float* bias_part =
       (spatial || scatter || scatter_bins) ? local_w + n_weight : reinterpret_cast<float*>(h->buf_w()) + spec_floats;
-  // W'^[bin][f][p] = scale/N^2 sum_b conj(O'^[f][b]) I^[p][b]
+  // W'^[bin][f][p] = scale/N^2 sum_b conj(O'^[b][f]) I^[b][p]
   {
     StageTimer t(h, pass, FBFFTCONV_STAGE_CONTRACT, s);
     const float norm = scale / (float)(h->N * h->N);
     if (pm) {  // W'^[f][p] = sum_b conj(O'^[b][f]) I^[b][p]
       FBF_CUDA(launch_stream_reduce(h->buf_out(), h->buf_in(), h->buf_w(), F, B, P, 1, F, true, h->bins, norm, s));
     } else {
-      FBF_TRY(contract(h->buf_out(), h->buf_in(), h->buf_w(), h->bins, F, P, B, norm, 1, 0, simt, s));
+      FBF_TRY(contract(h->buf_out(), h->buf_in(), h->buf_w(), h->bins, F, P, B, norm, 1, 0, simt, s, true, true));
     }
   }
   if (grad_bias) {
     StageTimer t(h, pass, FBFFTCONV_STAGE_BIAS, s);
-    // bin (0,0) of O'^[bin][f][b] is the plain sum of gradOutput plane (b, f): its real
+    // bin (0,0) of O'^[bin][b][f] is the plain sum of gradOutput plane (b, f): its real
     // parts, summed over b, are the bias gradient (src/ConvolutionBias.cu:61-97).
     // (plane-major: element (b, f, bin 0) sits at ((b*F + f) * bins) complex values)
     const float* dc = reinterpret_cast<const float*>(h->buf_out());
-    const long long ld = pm ? 2LL * h->bins : 2LL * pad4(B);
-    const long long dc_step = pm ? 2LL * F * h->bins : 2;
+    const long long ld = pm ? 2LL * h->bins : 2;
+    const long long dc_step = pm ? 2LL * F * h->bins : 2LL * pad4(F);
     if (h->comm)
       FBF_CUDA(launch_row_sum(dc, bias_part, F, B, ld, dc_step, scale, 0, s));
     else
@@ -732,7 +760,7 @@ int fbfftconv_acc_grad_parameters(fbfftconv_handle* h, const float* input, const
     {
       StageTimer t(h, pass, FBFFTCONV_STAGE_IFFT, s);
       FBF_CUDA(launch_inverse(inverse_params(reinterpret_cast<const float2*>(mine), local_w + (size_t)h->rank * slice,
-                                             nullptr, F / h->nranks, P, d.kernel_h, d.kernel_w, 0, 0, 0, true, h->N),
+                                             nullptr, F / h->nranks, P, d.kernel_h, d.kernel_w, 0, 0, 0, 2, h->N),
                               h->N, s));
     }
     {
@@ -762,7 +790,7 @@ int fbfftconv_acc_grad_parameters(fbfftconv_handle* h, const float* input, const
       FBF_CUDA(cudaMemsetAsync(mine + chunk, 0, (size_t)(h->nranks - 1 - h->rank) * chunk * sizeof(float), s));
     {
       StageTimer t(h, pass, FBFFTCONV_STAGE_IFFT, s);
-      FBF_CUDA(launch_inverse(inverse_params(h->buf_w(), local_w, nullptr, F, P, d.kernel_h, d.kernel_w, 0, 0, 0, false,
+      FBF_CUDA(launch_inverse(inverse_params(h->buf_w(), local_w, nullptr, F, P, d.kernel_h, d.kernel_w, 0, 0, 0, 0,
                                              h->N), h->N, s));
     }
     {
@@ -779,7 +807,7 @@ int fbfftconv_acc_grad_parameters(fbfftconv_handle* h, const float* input, const
   if (!scatter && !scatter_bins) {
     StageTimer t(h, pass, FBFFTCONV_STAGE_IFFT, s);
     FBF_CUDA(launch_inverse(inverse_params(h->buf_w(), spatial ? local_w : grad_weight, nullptr, F, P, d.kernel_h,
-                                           d.kernel_w, 0, 0, spatial ? 0 : accumulate, pm, h->N), h->N, s));
+                                           d.kernel_w, 0, 0, spatial ? 0 : accumulate, pm ? 2 : 0, h->N), h->N, s));
   }
   if (spatial) {
     StageTimer t(h, pass, FBFFTCONV_STAGE_ALLREDUCE, s);
@@ -1147,7 +1175,7 @@ int fbfftconv_ifft2d(const void* spectrum, float* real, const float* bias, int d
   if (d1 <= 0 || d2 <= 0 || h <= 0 || w <= 0 || off_y < 0 || off_x < 0 || h + off_y > fft_size ||
       w + off_x > fft_size || d1 > 65535 || d2 > 65535)
     return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "window of %dx%d at (%d,%d) does not fit %d", h, w, off_y, off_x, fft_size);
-  FBF_CUDA(launch_inverse(inverse_params(static_cast<const float2*>(spectrum), real, bias, d1, d2, h, w, off_y, off_x, accumulate != 0, plane_major != 0, fft_size),
+  FBF_CUDA(launch_inverse(inverse_params(static_cast<const float2*>(spectrum), real, bias, d1, d2, h, w, off_y, off_x, accumulate != 0, plane_major != 0 ? 2 : 0, fft_size),
                           fft_size, static_cast<cudaStream_t>(stream)));
   return FBFFTCONV_OK;
 }
@@ -1180,9 +1208,10 @@ int fbfftconv_transpose_mm(const void* a, const void* b, void* c, int bins, int 
   if (!a || !b || !c) return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "null argument");
   if (bins <= 0 || m <= 0 || n <= 0 || k <= 0 || bins > 65535)
     return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "bad contraction sizes");
+  if ((conj_a & ~3) || (conj_b & ~3)) return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "operand flags are 0..3");
   return contract(static_cast<const float2*>(a), static_cast<const float2*>(b), static_cast<float2*>(c),
-                  bins, m, n, k, alpha, conj_a != 0, conj_b != 0, use_simt != 0,
-                  static_cast<cudaStream_t>(stream));
+                  bins, m, n, k, alpha, conj_a & 1, conj_b & 1, use_simt != 0,
+                  static_cast<cudaStream_t>(stream), (conj_a & 2) != 0, (conj_b & 2) != 0);
 }
 
 int fbfftconv_update_output_bias(float* output, const float* bias, int batch, int planes, int h,
@@ -1204,6 +1233,13 @@ int fbfftconv_acc_grad_parameters_bias(const float* grad_output, float* grad_bia
 }
 
 int fbfftconv_tensor_core_status(int reset) { return contract_tc_error(reset != 0); }
+
+int fbfftconv_tensor_core_wait_selftest(fbfftconv_stream stream) {
+  const int r = contract_tc_wait_probe(static_cast<cudaStream_t>(stream));
+  if (r < 0) return fail(FBFFTCONV_ERR_CUDA, "wait self-test could not run: %s", cudaGetErrorString(cudaGetLastError()));
+  if (r != 1) return fail(FBFFTCONV_ERR_CUDA, "wait self-test: the bounded wait did not give up");
+  return FBFFTCONV_OK;
+}
 
 // ---- per-kernel timing ---------------------------------------------------------
 

@@ -2,8 +2,10 @@
 //
 //   C[bin][m][n] = alpha * sum_k opA(A[bin][m][k]) * opB(B[bin][n][k])
 //
-// Both operands are read with the contraction index contiguous, which is how the
-// FFT kernels lay the spectra out, so no transpose pass exists anywhere.  Stands
+// An operand is read either with the contraction index contiguous ([rows][k]) or with it
+// as the row index ([k][rows]): the FFT kernels write every spectrum once, plane index
+// innermost, and each pass reads it whichever way its sum runs, so no transpose pass
+// exists anywhere.  Stands
 // where the reference calls transposeMM (src/MM.cu:14-24, :54-73) or, in its cuBLAS
 // variant, cgeam + cgemm(Batched) (src/CuBLASWrapper.cpp:113-125, :266-280, :437-452).
 // This is the exact-fp32 path: it serves as the numerical yardstick of the
@@ -43,8 +45,8 @@ contract_simt_kernel(const __grid_constant__ ContractParams p) {
   const int tid = threadIdx.x;
   const int tx = tid % TX, ty = tid / TX;
 
-  const float2* A = p.a + (long long)bin * p.m * p.lda;
-  const float2* B = p.b + (long long)bin * p.n * p.ldb;
+  const float2* A = p.a + (long long)bin * (p.a_mn ? p.k : p.m) * p.lda;
+  const float2* B = p.b + (long long)bin * (p.b_mn ? p.k : p.n) * p.ldb;
   float2* C = p.c + (long long)bin * p.m * p.ldc;
 
   // loaders: one float4 (two complex) per slot; a tile has rows*4 slots
@@ -53,10 +55,19 @@ contract_simt_kernel(const __grid_constant__ ContractParams p) {
   constexpr int A_SLOTS = BM * 4, B_SLOTS = BN * 4;
   constexpr int A_PER = (A_SLOTS + THREADS - 1) / THREADS, B_PER = (B_SLOTS + THREADS - 1) / THREADS;
 
+  // [rows][k] operand: two neighbouring k of one row.  [k][rows] operand: two neighbouring rows of one k
+  // (the leading dimension is a multiple of 4 and its padding is zero, so a pair never straddles it).
   auto fetch = [&](const float2* base, int rows, int ld, int r, int k) -> float4 {
     if (r < rows && k < ld) return *reinterpret_cast<const float4*>(base + (long long)r * ld + k);
     return make_float4(0.f, 0.f, 0.f, 0.f);
   };
+  auto fetch_mn = [&](const float2* base, int depth, int ld, int r, int k) -> float4 {
+    if (k < depth && r < ld) return *reinterpret_cast<const float4*>(base + (long long)k * ld + r);
+    return make_float4(0.f, 0.f, 0.f, 0.f);
+  };
+  // slot -> (row, k) of its first complex value: [rows][k]: 4 slots per row, each two k;
+  // [k][rows]: rows/2 slots per k, each two rows
+  constexpr int A_HALF = BM / 2 > 0 ? BM / 2 : 1, B_HALF = BN / 2;
 
   float2 acc[TM][TN];
 #pragma unroll
@@ -69,12 +80,22 @@ contract_simt_kernel(const __grid_constant__ ContractParams p) {
 #pragma unroll
     for (int i = 0; i < A_PER; ++i) {
       const int slot = tid + i * THREADS;
-      ra[i] = slot < A_SLOTS ? fetch(A, p.m, p.lda, m0 + (slot >> 2), k0 + (slot & 3) * 2) : make_float4(0, 0, 0, 0);
+      if (slot >= A_SLOTS)
+        ra[i] = make_float4(0, 0, 0, 0);
+      else if (p.a_mn)
+        ra[i] = fetch_mn(A, p.k, p.lda, m0 + (slot % A_HALF) * 2, k0 + slot / A_HALF);
+      else
+        ra[i] = fetch(A, p.m, p.lda, m0 + (slot >> 2), k0 + (slot & 3) * 2);
     }
 #pragma unroll
     for (int i = 0; i < B_PER; ++i) {
       const int slot = tid + i * THREADS;
-      rb[i] = slot < B_SLOTS ? fetch(B, p.n, p.ldb, n0 + (slot >> 2), k0 + (slot & 3) * 2) : make_float4(0, 0, 0, 0);
+      if (slot >= B_SLOTS)
+        rb[i] = make_float4(0, 0, 0, 0);
+      else if (p.b_mn)
+        rb[i] = fetch_mn(B, p.k, p.ldb, n0 + (slot % B_HALF) * 2, k0 + slot / B_HALF);
+      else
+        rb[i] = fetch(B, p.n, p.ldb, n0 + (slot >> 2), k0 + (slot & 3) * 2);
     }
   };
   auto stash = [&](int buf) {
@@ -82,18 +103,30 @@ contract_simt_kernel(const __grid_constant__ ContractParams p) {
     for (int i = 0; i < A_PER; ++i) {
       const int slot = tid + i * THREADS;
       if (slot < A_SLOTS) {
-        const int r = slot >> 2, c = (slot & 3) * 2;
-        As[buf][c][r] = make_float2(ra[i].x, sa * ra[i].y);
-        As[buf][c + 1][r] = make_float2(ra[i].z, sa * ra[i].w);
+        if (p.a_mn) {
+          const int r = (slot % A_HALF) * 2, c = slot / A_HALF;
+          As[buf][c][r] = make_float2(ra[i].x, sa * ra[i].y);
+          As[buf][c][r + 1] = make_float2(ra[i].z, sa * ra[i].w);
+        } else {
+          const int r = slot >> 2, c = (slot & 3) * 2;
+          As[buf][c][r] = make_float2(ra[i].x, sa * ra[i].y);
+          As[buf][c + 1][r] = make_float2(ra[i].z, sa * ra[i].w);
+        }
       }
     }
 #pragma unroll
     for (int i = 0; i < B_PER; ++i) {
       const int slot = tid + i * THREADS;
       if (slot < B_SLOTS) {
-        const int r = slot >> 2, c = (slot & 3) * 2;
-        Bs[buf][c][r] = make_float2(rb[i].x, sb * rb[i].y);
-        Bs[buf][c + 1][r] = make_float2(rb[i].z, sb * rb[i].w);
+        if (p.b_mn) {
+          const int r = (slot % B_HALF) * 2, c = slot / B_HALF;
+          Bs[buf][c][r] = make_float2(rb[i].x, sb * rb[i].y);
+          Bs[buf][c][r + 1] = make_float2(rb[i].z, sb * rb[i].w);
+        } else {
+          const int r = slot >> 2, c = (slot & 3) * 2;
+          Bs[buf][c][r] = make_float2(rb[i].x, sb * rb[i].y);
+          Bs[buf][c + 1][r] = make_float2(rb[i].z, sb * rb[i].w);
+        }
       }
     }
   };

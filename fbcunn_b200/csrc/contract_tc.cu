@@ -16,44 +16,24 @@
 // 3xTF32: x = hi + lo with hi = x truncated to the 10-bit TF32 mantissa and
 // lo = x - hi (exact), and  A*B ~= Ahi*Bhi + Alo*Bhi + Ahi*Blo.
 //
-// One thread block computes a 128 x 64 (complex) tile of one bin.  Warp roles:
-//   warp 0      TMA producer: raw fp32 tiles of A (128 rows) and B (64 rows), 32 floats
-//               (16 complex k) per stage
-//   warp 1      allocates tensor memory; one lane issues the MMAs
-//   warps 2..9  converters (split, rotate, write the 128-byte-swizzled K-major operand
-//               tiles), then the epilogue (tcgen05.ld, scale, store)
-// Every wait on an mbarrier is bounded; on a time-out the block raises a flag, stops
-// issuing work, waits (bounded) for copies in flight, frees its tensor memory and
+// The kernel itself (persistent blocks, tiles of 128 rows x 16 / 32 / 64 / 128 complex
+// columns, TMA producer / MMA issuer / converter / epilogue warps) is in
+// contract_tc_wide.inc; this file holds the PTX wrappers it is written in and the host
+// side.  Every wait on an mbarrier is bounded; on a time-out the block raises a flag,
+// stops issuing work, waits (bounded) for copies in flight, frees its tensor memory and
 // returns, and the host sees the error code.
 #include <cuda.h>
 
+#include <atomic>
 #include <cstdint>
 #include <cstdlib>
+#include <mutex>
 
 #include "kernels.h"
 
 namespace fbfft {
 
 namespace {
-
-constexpr int BM = 128;            // rows of A per tile
-constexpr int BNC = 64;            // complex columns (rows of B) per tile
-constexpr int UMMA_N = 2 * BNC;    // real accumulator columns
-constexpr int KB_FLOATS = 32;      // floats of K per stage: one 128-byte swizzle row
-constexpr int RAW_STAGES = 3;
-constexpr int CONV_STAGES = 2;
-constexpr int CONVERTER_WARPS = 8;
-constexpr int CONVERTER_THREADS = 32 * CONVERTER_WARPS;
-constexpr int THREADS = 64 + CONVERTER_THREADS;
-
-constexpr int RAW_A_BYTES = BM * KB_FLOATS * 4;     // 16 KB
-constexpr int RAW_B_BYTES = BNC * KB_FLOATS * 4;    //  8 KB
-constexpr int RAW_STAGE_BYTES = RAW_A_BYTES + RAW_B_BYTES;
-constexpr int OP_A_BYTES = BM * KB_FLOATS * 4;      // 16 KB per hi / lo
-constexpr int OP_B_BYTES = UMMA_N * KB_FLOATS * 4;  // 16 KB per hi / lo
-constexpr int CONV_STAGE_BYTES = 2 * OP_A_BYTES + 2 * OP_B_BYTES;  // 64 KB
-constexpr int SMEM_TILES = CONV_STAGES * CONV_STAGE_BYTES + RAW_STAGES * RAW_STAGE_BYTES;
-constexpr int SMEM_BYTES = SMEM_TILES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 
 constexpr uint32_t kSpinLimit = 1u << 21;  // polls of ~0.1 us each: a fraction of a second
 constexpr uint32_t kWaitHintNs = 2000;     // one suspended wait
@@ -101,9 +81,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity, ui
 }
 // Bounded wait.  Returns false (and raises the block's abort flag) on a time-out or
 // when another role has already given up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code,
+                                          uint32_t limit = kWaitLimit) {
   if (mbar_test(bar, parity)) return true;
-  for (uint32_t spin = 0; spin < kWaitLimit; ++spin) {
+  for (uint32_t spin = 0; spin < limit; ++spin) {
     if (mbar_try_wait(bar, parity, kWaitHintNs)) return true;
     if (*abort_flag) return false;
   }
@@ -149,23 +130,6 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                : "memory");
 }
-__device__ __forceinline__ void tmem_load_32cols(uint32_t taddr, float (&v)[32]) {
-  uint32_t r[32];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-}
-
 __device__ __forceinline__ void tmem_load_16cols_nowait(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
@@ -189,38 +153,12 @@ __device__ __forceinline__ void tmem_load_16complex(uint32_t re_addr, uint32_t i
   }
 }
 
-// K-major operand tile with 128-byte rows, 128-byte swizzle, 8-row groups 1024 bytes
-// apart: start address, LBO = 1, SBO = 64 (both in 16-byte units), version 1, layout 2.
-__device__ __forceinline__ uint64_t operand_desc(uint32_t smem_addr) {
-  uint64_t d = (smem_addr >> 4) & 0x3FFFu;
-  d |= uint64_t(1) << 16;
-  d |= uint64_t(1024 >> 4) << 32;
-  d |= uint64_t(1) << 46;
-  d |= uint64_t(2) << 61;
-  return d;
-}
-// fp32 accumulator, TF32 operands, both K-major, M = 128, N = UMMA_N
-constexpr uint32_t kInstrDesc = (1u << 4) | (2u << 7) | (2u << 10) | (uint32_t(UMMA_N >> 3) << 17) |
-                                (uint32_t(BM >> 4) << 24);
-
 __device__ __forceinline__ float tf32_hi(float x) { return __uint_as_float(__float_as_uint(x) & 0xFFFFE000u); }
 
 __device__ __forceinline__ void split4(const float4 x, float4& hi, float4& lo) {
   hi = make_float4(tf32_hi(x.x), tf32_hi(x.y), tf32_hi(x.z), tf32_hi(x.w));
   lo = make_float4(tf32_hi(x.x - hi.x), tf32_hi(x.y - hi.y), tf32_hi(x.z - hi.z), tf32_hi(x.w - hi.w));
 }
-// byte offset of 16-byte chunk `c` of row `r` in a 128-byte-swizzled tile
-__device__ __forceinline__ int swizzled(int r, int c) { return r * 128 + ((c ^ (r & 7)) << 4); }
-
-struct TcParams {
-  float2* c;
-  int m, n, ldc;        // complex sizes
-  int k_floats;         // 2 * lda
-  float alpha;
-  float s_b1_im;        // -sa*sb
-  float s_b2_re, s_b2_im;  // sb, sa
-};
-
 // One accumulator block -- 32 rows (one per lane) x 32 floats in registers -- to global memory
 // through a 4 KB shared staging tile, so that a store instruction writes four 128-byte row
 // segments instead of 32 scattered 16-byte pieces.  Chunks are XOR-swizzled by the row:
@@ -243,174 +181,23 @@ __device__ __forceinline__ void store_block_coalesced(char* stage, const float (
   __syncwarp();
 }
 
-__global__ void __launch_bounds__(THREADS, 1)
-contract_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                   const __grid_constant__ TcParams p) {
-  extern __shared__ char smem_raw[];
-  char* smem = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  char* conv = smem;                                  // CONV_STAGES x {Ahi, Alo, Bhi, Blo}
-  char* raw = smem + CONV_STAGES * CONV_STAGE_BYTES;  // RAW_STAGES x {A, B}
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SMEM_TILES);
-  uint64_t* full_raw = bars;                    // [RAW_STAGES]
-  uint64_t* empty_raw = bars + RAW_STAGES;      // [RAW_STAGES]
-  uint64_t* full_conv = bars + 2 * RAW_STAGES;  // [CONV_STAGES]
-  uint64_t* empty_conv = full_conv + CONV_STAGES;
-  uint64_t* accum_full = empty_conv + CONV_STAGES;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_full + 1);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+#include "contract_tc_wide.inc"
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int bin = blockIdx.z;
-  const int m0 = blockIdx.y * BM;
-  const int n0 = blockIdx.x * BNC;
-  const int kblocks = (p.k_floats + KB_FLOATS - 1) / KB_FLOATS;
-
+// Exercises the give-up path of mbar_wait without TMA or tensor memory: one thread waits on a
+// barrier that nothing will ever complete, with a limit of a few suspended waits (microseconds),
+// and the kernel returns normally with the sticky code set.
+constexpr int kWaitProbeCode = 99;
+__global__ void wait_probe_kernel(int* gave_up) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
   if (threadIdx.x == 0) {
-    for (int i = 0; i < RAW_STAGES; ++i) {
-      mbar_init(&full_raw[i], 1);
-      mbar_init(&empty_raw[i], CONVERTER_WARPS);
-    }
-    for (int i = 0; i < CONV_STAGES; ++i) {
-      mbar_init(&full_conv[i], CONVERTER_WARPS);
-      mbar_init(&empty_conv[i], 1);
-    }
-    mbar_init(accum_full, 1);
-    *abort_flag = 0;
+    mbar_init(&bar, 1);
+    abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  if (warp == 1) tmem_alloc(tmem_slot, UMMA_N);
-  tc_fence_before_sync();
-  __syncthreads();
-  tc_fence_after_sync();
-  const uint32_t tmem_base = *tmem_slot;
-
-  if (warp == 0) {
-    // ---------------- TMA producer ----------------
-    if (lane == 0) {
-      int issued = 0;
-      for (int kb = 0; kb < kblocks; ++kb) {
-        const int s = kb % RAW_STAGES;
-        if (kb >= RAW_STAGES && !mbar_wait(&empty_raw[s], ((kb / RAW_STAGES) - 1) & 1, abort_flag, 1)) break;
-        char* dst = raw + s * RAW_STAGE_BYTES;
-        mbar_arrive_expect_tx(&full_raw[s], RAW_STAGE_BYTES);
-        tma_load_3d(dst, &map_a, &full_raw[s], kb * KB_FLOATS, m0, bin);
-        tma_load_3d(dst + RAW_A_BYTES, &map_b, &full_raw[s], kb * KB_FLOATS, n0, bin);
-        issued = kb + 1;
-      }
-      if (*abort_flag) {
-        // copies already issued must land before this block's shared memory goes away
-        for (int kb = (issued > RAW_STAGES ? issued - RAW_STAGES : 0); kb < issued; ++kb) {
-          const int s = kb % RAW_STAGES;
-          for (uint32_t spin = 0; spin < kSpinLimit; ++spin)
-            if (mbar_test(&full_raw[s], (kb / RAW_STAGES) & 1)) break;
-        }
-      }
-    }
-  } else if (warp == 1) {
-    // ---------------- MMA issuer ----------------
-    if (lane == 0) {
-      bool ok = true;
-      for (int kb = 0; kb < kblocks && ok; ++kb) {
-        const int cs = kb % CONV_STAGES;
-        ok = mbar_wait(&full_conv[cs], (kb / CONV_STAGES) & 1, abort_flag, 2);
-        if (!ok) break;
-        tc_fence_after_sync();
-        const uint32_t base = smem_u32(conv + cs * CONV_STAGE_BYTES);
-        const uint32_t a_hi = base, a_lo = base + OP_A_BYTES;
-        const uint32_t b_hi = base + 2 * OP_A_BYTES, b_lo = b_hi + OP_B_BYTES;
-#pragma unroll
-        for (int kk = 0; kk < KB_FLOATS / 8; ++kk) {
-          const uint32_t off = kk * 32;  // 8 TF32 values = 32 bytes along K inside the swizzle row
-          umma_tf32(tmem_base, operand_desc(a_hi + off), operand_desc(b_hi + off), kInstrDesc, (kb | kk) != 0);
-          umma_tf32(tmem_base, operand_desc(a_lo + off), operand_desc(b_hi + off), kInstrDesc, 1);
-          umma_tf32(tmem_base, operand_desc(a_hi + off), operand_desc(b_lo + off), kInstrDesc, 1);
-        }
-        umma_commit(&empty_conv[cs]);  // arrives when the MMAs above have read their operands
-      }
-      if (ok) umma_commit(accum_full);
-    }
-  } else {
-    // ---------------- converters, then epilogue ----------------
-    const int ct = threadIdx.x - 64;  // 0..CONVERTER_THREADS-1
-    bool ok = true;
-    for (int kb = 0; kb < kblocks && ok; ++kb) {
-      const int s = kb % RAW_STAGES, cs = kb % CONV_STAGES;
-      ok = mbar_wait(&full_raw[s], (kb / RAW_STAGES) & 1, abort_flag, 3);
-      if (ok && kb >= CONV_STAGES) ok = mbar_wait(&empty_conv[cs], ((kb / CONV_STAGES) - 1) & 1, abort_flag, 4);
-      if (!ok) break;
-      const char* ra = raw + s * RAW_STAGE_BYTES;
-      const char* rbt = ra + RAW_A_BYTES;
-      char* a_hi = conv + cs * CONV_STAGE_BYTES;
-      char* a_lo = a_hi + OP_A_BYTES;
-      char* b_hi = a_lo + OP_A_BYTES;
-      char* b_lo = b_hi + OP_B_BYTES;
-      // A: 128 rows x 8 chunks of 16 bytes; consecutive threads take consecutive chunks
-#pragma unroll
-      for (int i = 0; i < (BM * 8) / CONVERTER_THREADS; ++i) {
-        const int idx = ct + i * CONVERTER_THREADS;
-        const int r = idx >> 3, c = idx & 7;
-        const float4 x = *reinterpret_cast<const float4*>(ra + r * 128 + c * 16);
-        float4 hi, lo;
-        split4(x, hi, lo);
-        const int o = swizzled(r, c);
-        *reinterpret_cast<float4*>(a_hi + o) = hi;
-        *reinterpret_cast<float4*>(a_lo + o) = lo;
-      }
-      // B: 64 rows x 8 chunks; each chunk (re0, im0, re1, im1) makes one chunk of row 2n and of row 2n+1
-#pragma unroll
-      for (int i = 0; i < (BNC * 8) / CONVERTER_THREADS; ++i) {
-        const int idx = ct + i * CONVERTER_THREADS;
-        const int r = idx >> 3, c = idx & 7;
-        const float4 x = *reinterpret_cast<const float4*>(rbt + r * 128 + c * 16);
-        const float4 b1 = make_float4(x.x, p.s_b1_im * x.y, x.z, p.s_b1_im * x.w);
-        const float4 b2 = make_float4(p.s_b2_re * x.y, p.s_b2_im * x.x, p.s_b2_re * x.w, p.s_b2_im * x.z);
-        float4 hi, lo;
-        split4(b1, hi, lo);
-        int o = swizzled(2 * r, c);
-        *reinterpret_cast<float4*>(b_hi + o) = hi;
-        *reinterpret_cast<float4*>(b_lo + o) = lo;
-        split4(b2, hi, lo);
-        o = swizzled(2 * r + 1, c);
-        *reinterpret_cast<float4*>(b_hi + o) = hi;
-        *reinterpret_cast<float4*>(b_lo + o) = lo;
-      }
-      fence_generic_to_async_smem();  // operand tiles become visible to the tensor core
-      __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&full_conv[cs]);
-        mbar_arrive(&empty_raw[s]);
-      }
-    }
-    if (ok) ok = mbar_wait(accum_full, 0, abort_flag, 5);
-    ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld below needs the whole warp
-    if (ok) {
-      tc_fence_after_sync();
-      // tensor-memory lanes 32*(warp%4) .. +31 belong to this warp; lane = tile row.  The
-      // warps that share a quarter split the accumulator columns between them.
-      const int quarter = warp & 3;
-      const int share = (warp - 2) >> 2;
-      constexpr int kColBlocks = UMMA_N / 32, kShares = CONVERTER_WARPS / 4;
-      const int row0 = m0 + quarter * 32;
-      float2* cblock = p.c + ((long long)bin * p.m + row0) * p.ldc + n0;
-      // every load has landed and every MMA has read its operands: the raw stages are free
-      char* stage = raw + (warp - 2) * 4096;
-#pragma unroll 1
-      for (int cb = share * (kColBlocks / kShares); cb < (share + 1) * (kColBlocks / kShares); ++cb) {
-        float v[32];
-        tmem_load_32cols(tmem_base + (uint32_t(quarter * 32) << 16) + cb * 32, v);
-        store_block_coalesced(stage, v, p.alpha, lane, cblock + cb * 16, p.ldc, p.m - row0, p.ldc - (n0 + cb * 16));
-      }
-    }
-  }
-  tc_fence_before_sync();
-  __syncthreads();
-  if (warp == 1) {
-    tc_fence_after_sync();
-    tmem_dealloc(tmem_base, UMMA_N);
+    const bool done = mbar_wait(&bar, 0, &abort_flag, kWaitProbeCode, 4);
+    *gave_up = (!done && abort_flag == kWaitProbeCode) ? 1 : 0;
   }
 }
-
-#include "contract_tc_wide.inc"
 
 // ---- host side -----------------------------------------------------------------
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -429,13 +216,13 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// [bins][rows][k_floats] fp32, box {32 floats, box_rows, 1}; out-of-range elements read as zero.
-bool make_map(CUtensorMap* map, const void* base, int k_floats, int rows, int bins, int box_rows,
-              int box_floats = KB_FLOATS) {
+// [bins][rows][inner_floats] fp32, box {box_floats, box_rows, 1}; out-of-range elements read as zero.
+bool make_map(CUtensorMap* map, const void* base, int inner_floats, int rows, int bins, int box_rows,
+              int box_floats) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
-  const cuuint64_t dims[3] = {(cuuint64_t)k_floats, (cuuint64_t)rows, (cuuint64_t)bins};
-  const cuuint64_t strides[2] = {(cuuint64_t)k_floats * 4, (cuuint64_t)k_floats * 4 * (cuuint64_t)rows};
+  const cuuint64_t dims[3] = {(cuuint64_t)inner_floats, (cuuint64_t)rows, (cuuint64_t)bins};
+  const cuuint64_t strides[2] = {(cuuint64_t)inner_floats * 4, (cuuint64_t)inner_floats * 4 * (cuuint64_t)rows};
   const cuuint32_t box[3] = {(cuuint32_t)box_floats, (cuuint32_t)box_rows, 1};
   const cuuint32_t elem[3] = {1, 1, 1};
   return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), dims, strides, box, elem,
@@ -451,19 +238,67 @@ bool contract_tc_supported(const ContractParams& p) {
          (p.lda & 3) == 0 && (p.ldb & 3) == 0 && (p.ldc & 3) == 0;
 }
 
-// Wide persistent kernel for shapes with at least 96 complex columns.
-cudaError_t launch_contract_tc_wide(const ContractParams& p, cudaStream_t stream) {
+namespace {
+
+// Tensor maps are encoded once per (base, sizes) and kept: the passes of a layer call with the same
+// buffers step after step, and an encode plus a copy of 128 bytes per operand would otherwise sit in
+// front of every launch of a launch-bound layer.
+struct MapKey {
+  const void* base;
+  int inner_floats, rows, bins, box_rows, box_floats;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && inner_floats == o.inner_floats && rows == o.rows && bins == o.bins &&
+           box_rows == o.box_rows && box_floats == o.box_floats;
+  }
+};
+// Map of one operand with `rows` rows of the tile dimension (tile of `tile_rows`) and depth k:
+// stored [bins][rows][ld] (ld >= k) or, transposed, [bins][k][ld] (ld >= rows).
+MapKey operand_key(const void* base, int rows, int k, int ld, int bins, int tile_rows, bool mn) {
+  if (mn) return MapKey{base, 2 * ld, k, bins, wide::WKB / 2, 2 * tile_rows};
+  return MapKey{base, 2 * ld, rows, bins, tile_rows, wide::WKB};
+}
+struct MapCache {
+  static constexpr int kSlots = 32;
+  std::mutex mutex;
+  MapKey keys[kSlots] = {};
+  CUtensorMap maps[kSlots];
+  bool used[kSlots] = {};
+  int next = 0;
+  bool get(const MapKey& key, CUtensorMap* out) {
+    std::lock_guard<std::mutex> lock(mutex);
+    for (int i = 0; i < kSlots; ++i)
+      if (used[i] && keys[i] == key) {
+        *out = maps[i];
+        return true;
+      }
+    CUtensorMap m;
+    if (!make_map(&m, key.base, key.inner_floats, key.rows, key.bins, key.box_rows, key.box_floats)) return false;
+    const int slot = next;
+    next = (next + 1) % kSlots;
+    keys[slot] = key;
+    maps[slot] = m;
+    used[slot] = true;
+    *out = m;
+    return true;
+  }
+};
+MapCache g_maps;
+
+template <int WBNC, bool A_MN, bool B_MN>
+cudaError_t launch_wide_as(const ContractParams& p, cudaStream_t stream) {
   using namespace wide;
+  using TL = WideTile<WBNC>;
   CUtensorMap map_a, map_b;
-  if (!make_map(&map_a, p.a, 2 * p.lda, p.m, p.bins, WBM, WKB) ||
-      !make_map(&map_b, p.b, 2 * p.ldb, p.n, p.bins, WBNC, WKB))
+  if (!g_maps.get(operand_key(p.a, p.m, p.k, p.lda, p.bins, WBM, p.a_mn != 0), &map_a) ||
+      !g_maps.get(operand_key(p.b, p.n, p.k, p.ldb, p.bins, WBNC, p.b_mn != 0), &map_b))
     return cudaErrorInvalidValue;
   WideParams t;
   t.c = p.c;
   t.m = p.m;
   t.n = p.n;
   t.ldc = p.ldc;
-  t.k_floats = 2 * p.lda;
+  // depth in floats: the padded row length of a [rows][k] operand (its padding is zero), 2k otherwise
+  t.k_floats = !p.a_mn ? 2 * p.lda : (!p.b_mn ? 2 * p.ldb : 2 * p.k);
   t.m_tiles = (p.m + WBM - 1) / WBM;
   t.n_tiles = (p.ldc + WBNC - 1) / WBNC;
   const long long total = (long long)t.m_tiles * t.n_tiles * p.bins;
@@ -474,38 +309,57 @@ cudaError_t launch_contract_tc_wide(const ContractParams& p, cudaStream_t stream
   t.s_b1_im = -sa * sb;
   t.s_b2_re = sb;
   t.s_b2_im = sa;
-  cudaError_t e = cudaFuncSetAttribute(contract_tc_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, W_SMEM_BYTES);
-  if (e != cudaSuccess) return e;
+  // the opt-in to large dynamic shared memory is per device and function: once is enough
+  constexpr int kMaxDevices = 64;
+  static std::atomic<bool> opted_in[kMaxDevices];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) dev = 0;
+  if (!opted_in[dev].load(std::memory_order_acquire)) {
+    cudaError_t e = cudaFuncSetAttribute(contract_tc_wide_kernel<WBNC, A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         TL::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    opted_in[dev].store(true, std::memory_order_release);
+  }
   const int sms = sm_count();
   const int grid = (int)(total < sms ? total : sms);
-  contract_tc_wide_kernel<<<grid, W_THREADS, W_SMEM_BYTES, stream>>>(map_a, map_b, t);
+  contract_tc_wide_kernel<WBNC, A_MN, B_MN><<<grid, W_THREADS, TL::SMEM_BYTES, stream>>>(map_a, map_b, t);
   count_launch();
   return cudaGetLastError();
 }
 
+template <int WBNC>
+cudaError_t launch_wide(const ContractParams& p, cudaStream_t stream) {
+  if (p.a_mn) return p.b_mn ? launch_wide_as<WBNC, true, true>(p, stream) : launch_wide_as<WBNC, true, false>(p, stream);
+  return p.b_mn ? launch_wide_as<WBNC, false, true>(p, stream) : launch_wide_as<WBNC, false, false>(p, stream);
+}
+
+}  // namespace
+
+// The tile's column count follows the problem's: the smallest of 16 / 32 / 64 / 128 complex columns
+// that covers it, 128 beyond.
 cudaError_t launch_contract_tc(const ContractParams& p, cudaStream_t stream) {
   if (!contract_tc_supported(p)) return cudaErrorInvalidValue;
-  if (p.ldc >= 96) return launch_contract_tc_wide(p, stream);
-  CUtensorMap map_a, map_b;
-  if (!make_map(&map_a, p.a, 2 * p.lda, p.m, p.bins, BM) || !make_map(&map_b, p.b, 2 * p.ldb, p.n, p.bins, BNC))
-    return cudaErrorInvalidValue;
-  TcParams t;
-  t.c = p.c;
-  t.m = p.m;
-  t.n = p.n;
-  t.ldc = p.ldc;
-  t.k_floats = 2 * p.lda;
-  t.alpha = p.alpha;
-  const float sa = p.conj_a ? -1.f : 1.f, sb = p.conj_b ? -1.f : 1.f;
-  t.s_b1_im = -sa * sb;
-  t.s_b2_re = sb;
-  t.s_b2_im = sa;
-  cudaError_t e = cudaFuncSetAttribute(contract_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-  if (e != cudaSuccess) return e;
-  dim3 grid((p.ldc + BNC - 1) / BNC, (p.m + BM - 1) / BM, p.bins);
-  contract_tc_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(map_a, map_b, t);
-  count_launch();
-  return cudaGetLastError();
+  if (p.ldc <= 16) return launch_wide<16>(p, stream);
+  if (p.ldc <= 32) return launch_wide<32>(p, stream);
+  if (p.ldc <= 64) return launch_wide<64>(p, stream);
+  return launch_wide<128>(p, stream);
+}
+
+// Runs wait_probe_kernel and returns 1 when the wait gave up as designed, 0 when it did not,
+// negative on a CUDA error.  Leaves the sticky code (kWaitProbeCode) for contract_tc_error.
+int contract_tc_wait_probe(cudaStream_t stream) {
+  int* flag = nullptr;
+  if (cudaMalloc(&flag, sizeof(int)) != cudaSuccess) return -1;
+  int result = -1;
+  if (cudaMemsetAsync(flag, 0xFF, sizeof(int), stream) == cudaSuccess) {
+    wait_probe_kernel<<<1, 32, 0, stream>>>(flag);
+    count_launch();
+    if (cudaGetLastError() == cudaSuccess && cudaStreamSynchronize(stream) == cudaSuccess &&
+        cudaMemcpy(&result, flag, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess)
+      result = -1;
+  }
+  cudaFree(flag);
+  return result;
 }
 
 int contract_tc_error(bool reset) {

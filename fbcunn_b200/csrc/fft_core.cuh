@@ -43,8 +43,22 @@ namespace fbfft {
 // ---------------------------------------------------------------------------
 // complex helpers and twiddles
 // ---------------------------------------------------------------------------
-FBF_HD float2 cadd(float2 a, float2 b) { return make_float2(a.x + b.x, a.y + b.y); }
-FBF_HD float2 csub(float2 a, float2 b) { return make_float2(a.x - b.x, a.y - b.y); }
+// Complex add / subtract as one packed f32x2 instruction on the device (sm_100 has two-wide fp32
+// add / mul / fma on register pairs; a float2 that came from an 8-byte load already is one).
+FBF_HD float2 cadd(float2 a, float2 b) {
+#if defined(__CUDA_ARCH__) && defined(FBF_PACKED)
+  return __fadd2_rn(a, b);
+#else
+  return make_float2(a.x + b.x, a.y + b.y);
+#endif
+}
+FBF_HD float2 csub(float2 a, float2 b) {
+#if defined(__CUDA_ARCH__) && defined(FBF_PACKED)
+  return __ffma2_rn(b, make_float2(-1.f, -1.f), a);
+#else
+  return make_float2(a.x - b.x, a.y - b.y);
+#endif
+}
 FBF_HD float2 cmul(float2 a, float2 b) {
   return make_float2(a.x * b.x - a.y * b.y, a.x * b.y + a.y * b.x);
 }
@@ -311,7 +325,8 @@ struct FftParams {
                           //   bin-major   [bins][n_rows][kc]:      spec_bin = n_rows*kc, spec_row = kc, spec_inner = 1
                           //   plane-major [n_rows][n_inner][bins]: spec_bin = 1, spec_row = n_inner*bins, spec_inner = bins
   long long spec_bin, spec_row, spec_inner;
-  const float* bias;      // inverse only: added per inner index, may be null
+  const float* bias;      // inverse only: added per inner index (per row when bias_by_row), may be null
+  int bias_by_row;
   int h, w;               // extent of the real planes
   int off_y, off_x;       // forward: placement offset; inverse: crop origin
   int n_rows, n_inner;    // valid rows / planes along inner
@@ -522,7 +537,7 @@ struct Inverse {
     for (int t = group; t < T; t += ngroups) {
       const int inner = inner0 + t;
       if (inner >= p.n_inner) break;
-      const float bias = p.bias ? p.bias[inner] : 0.f;
+      const float bias = p.bias ? p.bias[p.bias_by_row ? row : inner] : 0.f;
       float* dst = plane_ptr(p, g, row, inner);
       const int shift = phase16(dst);
       const float* src = stage + t * g.pitch1 + shift;
@@ -878,7 +893,7 @@ struct CoopInverse {
 #pragma unroll
       for (int n2 = 0; n2 < N2; ++n2) u[n2] = src[n2];
       fft_inreg<N2, true>(u);
-      const float bias = p.bias ? p.bias[inner] : 0.f;
+      const float bias = p.bias ? p.bias[p.bias_by_row ? row : inner] : 0.f;
       float* da = base + t * tstride + (long long)j * g.we + (k1 - p.off_x);
       float* db = da + (long long)g.hh * g.we;
 #pragma unroll

@@ -27,13 +27,14 @@ cudaError_t launch_fft1d(bool inverse, const float* real_in, float* real_out, fl
 cudaError_t launch_inverse(const FftParams& p, int N, cudaStream_t stream);
 
 struct ContractParams {
-  const float2* a;   // [bins][m][lda]
-  const float2* b;   // [bins][n][ldb]
+  const float2* a;   // [bins][m][lda], lda >= k;  with a_mn: [bins][k][lda], lda >= m
+  const float2* b;   // [bins][n][ldb], ldb >= k;  with b_mn: [bins][k][ldb], ldb >= n
   float2* c;         // [bins][m][ldc]
-  int bins, m, n, k; // k counts valid complex columns; lda/ldb >= k, zero padded
+  int bins, m, n, k; // complex sizes; padding up to the leading dimensions is zero
   int lda, ldb, ldc; // multiples of 4
   float alpha;
   int conj_a, conj_b;
+  int a_mn, b_mn;    // operand stored with the contraction index as the row ("MN-major")
 };
 cudaError_t launch_contract_simt(const ContractParams& p, cudaStream_t stream);
 // Tensor-core (tcgen05, 3xTF32) contraction.  contract_tc_error returns the first
@@ -42,6 +43,9 @@ cudaError_t launch_contract_simt(const ContractParams& p, cudaStream_t stream);
 bool contract_tc_supported(const ContractParams& p);
 cudaError_t launch_contract_tc(const ContractParams& p, cudaStream_t stream);
 int contract_tc_error(bool reset);
+// Makes one bounded wait run out on purpose (a barrier nothing completes, a limit of microseconds):
+// 1 = the wait gave up and left its code (99) for contract_tc_error, 0 = it did not, < 0 = CUDA error.
+int contract_tc_wait_probe(cudaStream_t stream);
 
 // Plane-major ([plane][bin]) streaming contractions for <= 4 input planes (contract_stream.cu):
 //   expand: z[u][v] = alpha * sum_p x[u][p] * conj(y[v][p])

@@ -66,11 +66,10 @@ enum {
    *   REUSE_WEIGHT  updateGradInput takes the weight spectrum of the last updateOutput,
    *   REUSE_INPUT   accGradParameters takes the input spectrum of the last updateOutput,
    *   REUSE_OUTPUT  accGradParameters takes the gradOutput spectrum of the last updateGradInput.
-   * A spectrum is taken over only where both passes read it in the same layout, which is
-   * the case for the plane-major buffers of layers with <= 4 input planes at transform sizes
-   * 64 / 128; elsewhere each pass needs its operands contiguous along its own contraction
-   * index, the transform is as cheap as the transposition a cached spectrum would need, and
-   * the flags have no effect. */
+   * Every tensor's spectrum is written once, in one layout, and each pass reads it whichever way
+   * its sum runs, so a spectrum can be taken over by any later pass of the step.  With REUSE_INPUT
+   * the gradInput spectrum gets a buffer of its own (the input spectrum must survive
+   * updateGradInput). */
   FBFFTCONV_REUSE_INPUT = 16,
   FBFFTCONV_REUSE_OUTPUT = 32,
   FBFFTCONV_REUSE_WEIGHT = 64
@@ -204,9 +203,11 @@ int fbfftconv_ifft1d(const void* spectrum, float* real, long long rows, int n, i
 
 /* Replaces transposeMMFFI (fbcunn/FFTCDefs.lua:7-14, src/MM.cu:54-73) on bin-major
  * operands: for every bin  C[m][n] = alpha * sum_k opA(A[m][k]) * opB(B[n][k]),
- * op = complex conjugate when the flag is set.  A is [bins][m][k_padded],
- * B [bins][n][k_padded], C [bins][m][n_padded].  use_simt != 0 forces the fp32
- * CUDA-core kernel. */
+ * C [bins][m][n_padded].  conj_a / conj_b are flag sets per operand: bit 0 = use the complex
+ * conjugate; bit 1 = the operand is stored with the contraction index as the row index,
+ * A as [bins][k][m_padded] (B as [bins][k][n_padded]) instead of [bins][m][k_padded]
+ * ([bins][n][k_padded]) -- the reference's 't' / 'c' operand forms on plane-major data.
+ * Padding (up to a multiple of 4) must be zero.  use_simt != 0 forces the fp32 CUDA-core kernel. */
 int fbfftconv_transpose_mm(const void* a, const void* b, void* c, int bins, int m, int n, int k,
                            float alpha, int conj_a, int conj_b, int use_simt,
                            fbfftconv_stream stream);
@@ -217,6 +218,12 @@ int fbfftconv_transpose_mm(const void* a, const void* b, void* c, int bins, int 
  * device anyway, check it themselves and return FBFFTCONV_ERR_CUDA; callers of the
  * device-pointer passes, which never wait, poll it where they synchronise. */
 int fbfftconv_tensor_core_status(int reset);
+/* Self-test of that give-up path (no counterpart in the reference, whose kernels never wait on
+ * one another): launches one thread that waits on a barrier nothing will ever complete, with a
+ * limit of a few microseconds.  Returns FBFFTCONV_OK when the wait gave up as designed; the
+ * device code 99 is then what fbfftconv_tensor_core_status reports until it is reset, and the
+ * context stays usable. */
+int fbfftconv_tensor_core_wait_selftest(fbfftconv_stream stream);
 /* Replaces updateOutputBiasFFI (fbcunn/FFTCDefs.lua:4, src/ConvolutionBias.cu:39-51). */
 int fbfftconv_update_output_bias(float* output, const float* bias, int batch, int planes, int h,
                                  int w, fbfftconv_stream stream);

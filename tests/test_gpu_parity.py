@@ -132,21 +132,35 @@ def test_ifft2d_crop_bias_and_round_trip(N):
 # contraction and bias kernels
 # ---------------------------------------------------------------------------
 @pytest.mark.parametrize("use_simt", [1, 0])
+@pytest.mark.parametrize("mn_a,mn_b", [(0, 0), (0, 1), (1, 0), (1, 1)])
 @pytest.mark.parametrize("conj_a,conj_b", [(0, 1), (0, 0), (1, 0)])
-def test_transpose_mm(use_simt, conj_a, conj_b):
+def test_transpose_mm(use_simt, conj_a, conj_b, mn_a, mn_b):
+    """mn_x: the operand is handed over stored [bins][k][rows] (contraction index as the row
+    index), the way updateGradInput reads the weight spectrum and accGradParameters both of its
+    operands."""
     rng = np.random.default_rng(3)
     for (bins, m, n, k) in [(5, 7, 9, 3), (3, 64, 64, 8), (2, 130, 70, 21), (1, 1, 1, 1), (4, 16, 128, 128),
-                            (3, 130, 3, 96), (2, 96, 4, 128), (3, 128, 384, 384), (2, 300, 200, 77)]:
+                            (3, 130, 3, 96), (2, 96, 4, 128), (3, 128, 384, 384), (2, 300, 200, 77),
+                            # tiles of 16 / 32 / 64 complex columns (batch shards on the column side)
+                            (4, 384, 16, 384), (3, 200, 24, 40), (2, 384, 48, 64), (2, 129, 33, 17)]:
         kp, npad = (k + 3) // 4 * 4, (n + 3) // 4 * 4
         a = np.zeros((bins, m, kp), np.complex64)
         b = np.zeros((bins, n, kp), np.complex64)
         a[:, :, :k] = rng.standard_normal((bins, m, k)) + 1j * rng.standard_normal((bins, m, k))
         b[:, :, :k] = rng.standard_normal((bins, n, k)) + 1j * rng.standard_normal((bins, n, k))
         c = torch.full((bins, m, npad), float("nan"), dtype=torch.complex64, device="cuda")
-        da, db = torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda()
+
+        def stored(x, rows, mn):
+            if not mn:
+                return torch.from_numpy(x).cuda()
+            t = np.zeros((bins, k, (rows + 3) // 4 * 4), np.complex64)
+            t[:, :, :rows] = x[:, :, :k].transpose(0, 2, 1)
+            return torch.from_numpy(t).cuda()
+
+        da, db = stored(a, m, mn_a), stored(b, n, mn_b)
         capi.check(capi.lib().fbfftconv_transpose_mm(
             ctypes.c_void_p(da.data_ptr()), ctypes.c_void_p(db.data_ptr()), ctypes.c_void_p(c.data_ptr()),
-            bins, m, n, k, ctypes.c_float(0.25), conj_a, conj_b, use_simt,
+            bins, m, n, k, ctypes.c_float(0.25), conj_a | (mn_a << 1), conj_b | (mn_b << 1), use_simt,
             ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
         a64 = a.astype(np.complex128).conj() if conj_a else a.astype(np.complex128)
         b64 = b.astype(np.complex128).conj() if conj_b else b.astype(np.complex128)
@@ -157,6 +171,7 @@ def test_transpose_mm(use_simt, conj_a, conj_b):
         tol = 2e-6 if use_simt else 1e-5
         assert capi.lib().fbfftconv_tensor_core_status(1) == 0, "a bounded wait ran out on the device"
         assert np.abs(got - ref).max() <= tol * np.abs(ref).max(), (bins, m, n, k)
+        assert np.all(c.cpu().numpy()[:, :, n:] == 0), "the padding columns of C are written as zero"
 
 
 def test_bias_kernels():
@@ -264,8 +279,9 @@ def _stage_launches(m):
 @pytest.mark.parametrize("plane_major", [True, False])
 def test_spectrum_reuse_across_the_passes_of_a_step(plane_major):
     """memoryReusePolicy of the reference (fbcunn/SpatialConvolutionFFT.lua:405-416): the backward
-    passes take over spectra of the earlier passes.  Results must not change; where the layouts
-    coincide (plane-major layers) the transforms are really skipped, elsewhere they are redone."""
+    passes take over spectra of the earlier passes.  Results must not change, and the transforms
+    are really skipped in both frequency layouts (a spectrum is written once and every pass reads
+    it whichever way its sum runs)."""
     s = oracle.Shape(4, 3, 6, 50, 44, 5, 6, 1, 0) if plane_major else oracle.Shape(4, 8, 6, 20, 18, 3, 4, 1, 0)
     x, w, go, b = _data(s, 991, bias=True)
     m = SpatialConvolutionFBFFT(s.P, s.F, s.kW, s.kH, 1, 1, s.padW, s.padH, "all")
@@ -288,10 +304,9 @@ def test_spectrum_reuse_across_the_passes_of_a_step(plane_major):
     n = _stage_launches(m)
     FFT_A, FFT_B = 0, 1
     assert n[(0, FFT_A)] == 2 and n[(0, FFT_B)] == 2 and n[(1, FFT_A)] == 2
-    skipped = 0 if plane_major else 2
-    assert n[(1, FFT_B)] == skipped, "weight spectrum of updateOutput"
-    assert n[(2, FFT_A)] == skipped, "gradOutput spectrum of updateGradInput"
-    assert n[(2, FFT_B)] == skipped, "input spectrum of updateOutput"
+    assert n[(1, FFT_B)] == 0, "weight spectrum of updateOutput"
+    assert n[(2, FFT_A)] == 0, "gradOutput spectrum of updateGradInput"
+    assert n[(2, FFT_B)] == 0, "input spectrum of updateOutput"
     # accGradParameters on its own (nothing to take over) still transforms what it needs
     m2 = SpatialConvolutionFBFFT(s.P, s.F, s.kW, s.kH, 1, 1, s.padW, s.padH, "all")
     m2.accGradParameters(dx, dgo, 0.8)
