@@ -253,9 +253,9 @@ struct MapKey {
 };
 // Map of one operand with `rows` rows of the tile dimension (tile of `tile_rows`) and depth k:
 // stored [bins][rows][ld] (ld >= k) or, transposed, [bins][k][ld] (ld >= rows).
-MapKey operand_key(const void* base, int rows, int k, int ld, int bins, int tile_rows, bool mn) {
-  if (mn) return MapKey{base, 2 * ld, k, bins, wide::WKB / 2, 2 * tile_rows};
-  return MapKey{base, 2 * ld, rows, bins, tile_rows, wide::WKB};
+MapKey operand_key(const void* base, int rows, int k, int ld, int bins, int tile_rows, int kb_floats, bool mn) {
+  if (mn) return MapKey{base, 2 * ld, k, bins, kb_floats / 2, 2 * tile_rows};
+  return MapKey{base, 2 * ld, rows, bins, tile_rows, kb_floats};
 }
 struct MapCache {
   static constexpr int kSlots = 32;
@@ -289,8 +289,8 @@ cudaError_t launch_wide_as(const ContractParams& p, cudaStream_t stream) {
   using namespace wide;
   using TL = WideTile<WBNC>;
   CUtensorMap map_a, map_b;
-  if (!g_maps.get(operand_key(p.a, p.m, p.k, p.lda, p.bins, WBM, p.a_mn != 0), &map_a) ||
-      !g_maps.get(operand_key(p.b, p.n, p.k, p.ldb, p.bins, WBNC, p.b_mn != 0), &map_b))
+  if (!g_maps.get(operand_key(p.a, p.m, p.k, p.lda, p.bins, WBM, TL::KB, p.a_mn != 0), &map_a) ||
+      !g_maps.get(operand_key(p.b, p.n, p.k, p.ldb, p.bins, WBNC, TL::KB, p.b_mn != 0), &map_b))
     return cudaErrorInvalidValue;
   WideParams t;
   t.c = p.c;
