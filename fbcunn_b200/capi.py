@@ -28,6 +28,7 @@ ALLREDUCE_SPATIAL = 8
 REUSE_INPUT = 16
 REUSE_OUTPUT = 32
 REUSE_WEIGHT = 64
+EXCHANGE_NCCL = 128
 
 
 class Desc(ctypes.Structure):
@@ -74,6 +75,8 @@ _SIGNATURES = {
     "fbfftconv_transpose_mm": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p]),
     "fbfftconv_tensor_core_status": (c_int, [c_int]),
     "fbfftconv_tensor_core_wait_selftest": (c_int, [c_void_p]),
+    "fbfftconv_peer_exchange_status": (c_int, [c_void_p, c_int]),
+    "fbfftconv_peer_exchange_wait_selftest": (c_int, [c_void_p]),
     "fbfftconv_update_output_bias": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "fbfftconv_acc_grad_parameters_bias": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p]),
     "fbfftconv_acc_grad_parameters_bias_noalloc": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p]),

@@ -154,12 +154,26 @@ struct fbfftconv_handle {
   ncclComm_t comm = nullptr;
   std::string comm_key;
   int rank = 0, nranks = 1;
+  // sums over peer memory (peer.cu): set up at the first accGradParameters with a communicator
+  bool peer_tried = false, peer_ready = false;
+  PeerTable peers{};
+  unsigned char* peer_block = nullptr;  // flag slots, block counter, staging of the handle exchange
+  void* peer_mapped[2 * kMaxPeers] = {};  // cudaIpcOpenMemHandle results, to be closed
+  int n_peer_mapped = 0;
+  unsigned peer_epoch = 0;
 
   float2* buf_in() const { return reinterpret_cast<float2*>(ws); }
   float2* buf_out() const { return reinterpret_cast<float2*>(ws + bytes_in); }
   float2* buf_w() const { return reinterpret_cast<float2*>(ws + bytes_in + bytes_out); }
   float* small() const { return reinterpret_cast<float*>(ws + bytes_in + bytes_out + bytes_w); }
   // gradInput spectrum when the input spectrum has to survive updateGradInput
+  // vector summed across ranks after the inverse transform: gradWeight (or this rank's part of it)
+  // followed by the bias gradient; and the block the sum over peers is delivered to
+  float* vec_in() const { return small() + align_floats(((size_t)d.batch * d.n_output_plane + d.n_output_plane)); }
+  float* vec_out() const {
+    return vec_in() + align_floats((size_t)d.n_output_plane * d.n_input_plane * d.kernel_h * d.kernel_w + d.n_output_plane);
+  }
+  static size_t align_floats(size_t n) { return ((n * sizeof(float) + 255) & ~size_t(255)) / sizeof(float); }
   float2* buf_gi() const {
     return bytes_gi ? reinterpret_cast<float2*>(ws + bytes_in + bytes_out + bytes_w + bytes_small) : buf_in();
   }
@@ -408,7 +422,127 @@ int check_tensor_core_status() {
   return FBFFTCONV_OK;
 }
 
+void close_peers(fbfftconv_handle* h) {
+  for (int i = 0; i < h->n_peer_mapped; ++i) cudaIpcCloseMemHandle(h->peer_mapped[i]);
+  h->n_peer_mapped = 0;
+  if (h->peer_block) cudaFree(h->peer_block);
+  h->peer_block = nullptr;
+  h->peer_tried = h->peer_ready = false;
+  cudaGetLastError();
+}
+
+// What a rank publishes to the others: how to map its scratch and its flag block, and where in the
+// scratch the blocks of the exchange lie (a rank's layout follows its own batch share).
+struct PeerEntry {
+  cudaIpcMemHandle_t ws, block;
+  unsigned long long off_spec, off_in, off_out;
+  int ok;
+  int pad[9];
+};
+static_assert(sizeof(PeerEntry) == 192, "entry size is part of the exchange");
+constexpr size_t kPeerBlockBytes = 8192;  // [0, 1024): flags, counter; [1024, ...): exchange staging
+constexpr size_t kPeerStaging = 1024;
+constexpr size_t kPeerVerdict = 4096;
+
+// Collective over the communicator: every rank with a communicator calls it at the same point (the
+// first accGradParameters).  Afterwards peer_ready is the same on all ranks: true only if every rank
+// could export its blocks and map everybody else's; otherwise the NCCL exchange is used.  Waits for
+// the stream once.
+int ensure_peers(fbfftconv_handle* h, NcclApi* api, cudaStream_t s) {
+  if (h->peer_tried) return FBFFTCONV_OK;
+  h->peer_tried = true;
+  h->peer_ready = false;
+  if (!h->comm || h->nranks < 2) return FBFFTCONV_OK;
+  const char* env = getenv("FBFFTCONV_PEER_EXCHANGE");
+  bool mine = h->nranks <= kMaxPeers && h->ws_owned && api->AllGather && !(h->d.flags & FBFFTCONV_EXCHANGE_NCCL) &&
+              !(env && env[0] == '0');
+  void* block = nullptr;
+  cudaError_t e = cudaMalloc(&block, kPeerBlockBytes);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(FBFFTCONV_ERR_NOMEM, "flag block of the peer exchange: %s", cudaGetErrorString(e));
+  }
+  h->peer_block = static_cast<unsigned char*>(block);
+  FBF_CUDA(cudaMemsetAsync(block, 0, kPeerBlockBytes, s));
+  if (!api->AllGather || h->nranks * sizeof(PeerEntry) > kPeerVerdict - kPeerStaging) {
+    // no way to agree: every rank sees the same condition and stays on NCCL
+    return FBFFTCONV_OK;
+  }
+  PeerEntry me{};
+  if (mine) {
+    mine = cudaIpcGetMemHandle(&me.ws, h->ws) == cudaSuccess && cudaIpcGetMemHandle(&me.block, block) == cudaSuccess;
+    cudaGetLastError();
+  }
+  me.ok = mine ? 1 : 0;
+  me.off_spec = reinterpret_cast<char*>(h->buf_w()) - h->ws;
+  me.off_in = reinterpret_cast<char*>(h->vec_in()) - h->ws;
+  me.off_out = reinterpret_cast<char*>(h->vec_out()) - h->ws;
+  unsigned char* staging = h->peer_block + kPeerStaging;
+  FBF_CUDA(cudaMemcpyAsync(staging + h->rank * sizeof(PeerEntry), &me, sizeof(me), cudaMemcpyHostToDevice, s));
+  ncclResult_t r = api->AllGather(staging + h->rank * sizeof(PeerEntry), staging, sizeof(PeerEntry), ncclChar, h->comm, s);
+  if (r != ncclSuccess) return nccl_fail(api, r, "ncclAllGather(peer handles)");
+  std::vector<PeerEntry> all(h->nranks);
+  FBF_CUDA(cudaMemcpyAsync(all.data(), staging, h->nranks * sizeof(PeerEntry), cudaMemcpyDeviceToHost, s));
+  FBF_CUDA(cudaStreamSynchronize(s));
+  bool everyone = true;
+  for (const PeerEntry& p : all) everyone = everyone && p.ok == 1;
+  // map the peers (every rank tries only if every rank exported), then agree on the outcome
+  int mapped_ok = everyone ? 1 : 0;
+  PeerTable t{};
+  t.rank = h->rank;
+  t.nranks = h->nranks;
+  t.spin_limit = 0;  // default
+  t.counter = reinterpret_cast<unsigned*>(h->peer_block + 512);
+  for (int q = 0; q < h->nranks && mapped_ok; ++q) {
+    char* base;
+    unsigned char* blk;
+    if (q == h->rank) {
+      base = h->ws;
+      blk = h->peer_block;
+    } else {
+      void* pw = nullptr;
+      void* pb = nullptr;
+      if (cudaIpcOpenMemHandle(&pw, all[q].ws, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+        cudaGetLastError();
+        mapped_ok = 0;
+        break;
+      }
+      h->peer_mapped[h->n_peer_mapped++] = pw;
+      if (cudaIpcOpenMemHandle(&pb, all[q].block, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+        cudaGetLastError();
+        mapped_ok = 0;
+        break;
+      }
+      h->peer_mapped[h->n_peer_mapped++] = pb;
+      base = static_cast<char*>(pw);
+      blk = static_cast<unsigned char*>(pb);
+    }
+    t.spec[q] = base + all[q].off_spec;
+    t.vec_in[q] = base + all[q].off_in;
+    t.vec_out[q] = base + all[q].off_out;
+    t.flags[q] = reinterpret_cast<unsigned*>(blk);
+  }
+  int* verdict = reinterpret_cast<int*>(h->peer_block + kPeerVerdict);
+  FBF_CUDA(cudaMemcpyAsync(verdict, &mapped_ok, sizeof(int), cudaMemcpyHostToDevice, s));
+  r = api->AllReduce(verdict, verdict, 1, ncclInt, ncclMin, h->comm, s);
+  if (r != ncclSuccess) return nccl_fail(api, r, "ncclAllReduce(peer mapping)");
+  int agreed = 0;
+  FBF_CUDA(cudaMemcpyAsync(&agreed, verdict, sizeof(int), cudaMemcpyDeviceToHost, s));
+  FBF_CUDA(cudaStreamSynchronize(s));
+  if (agreed == 1) {
+    h->peers = t;
+    h->peer_ready = true;
+    h->peer_epoch = 1;  // the flag slots start at 0: the first barrier must wait for a real signal
+  } else {
+    for (int i = 0; i < h->n_peer_mapped; ++i) cudaIpcCloseMemHandle(h->peer_mapped[i]);
+    h->n_peer_mapped = 0;
+    cudaGetLastError();
+  }
+  return FBFFTCONV_OK;
+}
+
 void release_comm(fbfftconv_handle* h) {
+  close_peers(h);
   if (!h->comm) return;
   std::lock_guard<std::mutex> lock(g_comm_mutex);
   auto it = g_comms.find(h->comm_key);
@@ -497,7 +631,7 @@ int fbfftconv_create(const fbfftconv_desc* desc, fbfftconv_handle** out) {
   h->bytes_w = align256(bins * mx(F * pad4(P), P * pad4(F)) * sizeof(float2) + F * sizeof(float));
   h->bytes_small = align256((B * F + F) * sizeof(float));
   // local gradWeight + gradBias where they are summed or gathered across ranks in the spatial domain
-  h->bytes_small += align256((F * P * d.kernel_h * d.kernel_w + F) * sizeof(float));
+  h->bytes_small += 2 * align256((F * P * d.kernel_h * d.kernel_w + F) * sizeof(float));  // vec_in, vec_out
   h->bytes_gi = (d.flags & FBFFTCONV_REUSE_INPUT) ? h->bytes_in : 0;
   h->bytes_total = h->bytes_in + h->bytes_out + h->bytes_w + h->bytes_small + h->bytes_gi;
   *out = h;
@@ -547,6 +681,11 @@ int fbfftconv_set_workspace(fbfftconv_handle* h, void* device_ptr, size_t bytes)
   }
   h->ws = static_cast<char*>(device_ptr);
   h->ws_owned = false;
+  {
+    DeviceGuard g;
+    g.enter(h->device);
+    close_peers(h);  // mappings of the old block are stale; the exchange goes back to NCCL for this handle
+  }
   // the new block holds no spectra yet: nothing of an earlier pass can be taken over
   h->have_input_spec = h->have_grad_output_spec = h->have_weight_spec = false;
   return FBFFTCONV_OK;
@@ -706,12 +845,17 @@ int fbfftconv_acc_grad_parameters(fbfftconv_handle* h, const float* input, const
   h->have_weight_spec = false;  // the weight buffer receives the gradient spectrum below
   NcclApi* api = h->comm ? nccl_api() : nullptr;
   if (h->comm && !api) return fail(FBFFTCONV_ERR_COMM, "libnccl is not loadable");
+  if (h->comm) FBF_TRY(ensure_peers(h, api, s));
+  // Sums over peer memory replace the NCCL calls below wherever the exchange is a reduce-scatter plus a
+  // small sum (and for the spatial sum); the same choice is made on every rank.
+  const bool peer = h->comm && h->peer_ready;
+  const size_t vec4 = ((size_t)F * P * d.kernel_h * d.kernel_w + F + 3) / 4;  // float4s of [gradWeight | gradBias]
   const bool spatial = h->comm && (d.flags & FBFFTCONV_ALLREDUCE_SPATIAL);
   const size_t spec_floats = (size_t)h->bins * F * (pm ? P : pad4(P)) * 2;
   const size_t n_weight = (size_t)F * P * d.kernel_h * d.kernel_w;
   // Across ranks the bias gradient travels behind whatever the weight gradient is summed
   // as: behind its spectrum, or behind the local spatial gradient.
-  float* local_w = h->small() + align256(((size_t)B * F + F) * sizeof(float)) / sizeof(float);
+  float* local_w = h->vec_in();
   // Plane-major spectra are contiguous per filter, so the sum across ranks can be a reduce-scatter
   // by filters (half the bytes of an all-reduce): every rank inverts its own filters and the
   // spatial slices (a few hundred KB) are gathered.  Still the frequency-domain sum.
@@ -754,8 +898,15 @@ int fbfftconv_acc_grad_parameters(fbfftconv_handle* h, const float* input, const
     float* mine = reinterpret_cast<float*>(h->buf_w()) + (size_t)h->rank * chunk;
     {
       StageTimer t(h, pass, FBFFTCONV_STAGE_ALLREDUCE, s);
-      ncclResult_t r = api->ReduceScatter(h->buf_w(), mine, chunk, ncclFloat, ncclSum, h->comm, s);
-      if (r != ncclSuccess) return nccl_fail(api, r, "ncclReduceScatter(gradWeight spectrum)");
+      if (peer) {
+        FBF_CUDA(launch_peer_reduce(h->peers, h->peer_epoch, (size_t)h->rank * chunk / 4, chunk / 4, s));
+        h->peer_epoch += 2;
+        // this rank's filters will be the only non-zero part of the vector summed below
+        FBF_CUDA(cudaMemsetAsync(local_w, 0, n_weight * sizeof(float), s));
+      } else {
+        ncclResult_t r = api->ReduceScatter(h->buf_w(), mine, chunk, ncclFloat, ncclSum, h->comm, s);
+        if (r != ncclSuccess) return nccl_fail(api, r, "ncclReduceScatter(gradWeight spectrum)");
+      }
     }
     {
       StageTimer t(h, pass, FBFFTCONV_STAGE_IFFT, s);
@@ -763,7 +914,13 @@ int fbfftconv_acc_grad_parameters(fbfftconv_handle* h, const float* input, const
                                              nullptr, F / h->nranks, P, d.kernel_h, d.kernel_w, 0, 0, 0, 2, h->N),
                               h->N, s));
     }
-    {
+    if (peer) {
+      StageTimer t(h, pass, FBFFTCONV_STAGE_ALLREDUCE, s);
+      if (!grad_bias) FBF_CUDA(cudaMemsetAsync(bias_part, 0, F * sizeof(float), s));
+      FBF_CUDA(launch_peer_allreduce(h->peers, h->peer_epoch, vec4, s));
+      h->peer_epoch += 2;
+      FBF_CUDA(launch_copy_or_add(h->vec_out(), grad_weight, (long long)n_weight, accumulate, s));
+    } else {
       StageTimer t(h, pass, FBFFTCONV_STAGE_ALLREDUCE, s);
       ncclResult_t r = api->GroupStart();
       if (r == ncclSuccess)
@@ -781,8 +938,13 @@ int fbfftconv_acc_grad_parameters(fbfftconv_handle* h, const float* input, const
     float* mine = all + (size_t)h->rank * chunk;
     {
       StageTimer t(h, pass, FBFFTCONV_STAGE_ALLREDUCE, s);
-      ncclResult_t r = api->ReduceScatter(all, mine, chunk, ncclFloat, ncclSum, h->comm, s);
-      if (r != ncclSuccess) return nccl_fail(api, r, "ncclReduceScatter(gradWeight spectrum)");
+      if (peer) {
+        FBF_CUDA(launch_peer_reduce(h->peers, h->peer_epoch, (size_t)h->rank * chunk / 4, chunk / 4, s));
+        h->peer_epoch += 2;
+      } else {
+        ncclResult_t r = api->ReduceScatter(all, mine, chunk, ncclFloat, ncclSum, h->comm, s);
+        if (r != ncclSuccess) return nccl_fail(api, r, "ncclReduceScatter(gradWeight spectrum)");
+      }
     }
     // the other ranks' bins still hold this rank's partial products
     if (h->rank > 0) FBF_CUDA(cudaMemsetAsync(all, 0, (size_t)h->rank * chunk * sizeof(float), s));
@@ -795,9 +957,16 @@ int fbfftconv_acc_grad_parameters(fbfftconv_handle* h, const float* input, const
     }
     {
       StageTimer t(h, pass, FBFFTCONV_STAGE_ALLREDUCE, s);
-      ncclResult_t r = api->AllReduce(local_w, local_w, n_weight + bias_floats, ncclFloat, ncclSum, h->comm, s);
-      if (r != ncclSuccess) return nccl_fail(api, r, "ncclAllReduce(gradWeight partial transforms)");
-      FBF_CUDA(launch_copy_or_add(local_w, grad_weight, (long long)n_weight, accumulate, s));
+      if (peer) {
+        if (!grad_bias) FBF_CUDA(cudaMemsetAsync(bias_part, 0, F * sizeof(float), s));
+        FBF_CUDA(launch_peer_allreduce(h->peers, h->peer_epoch, vec4, s));
+        h->peer_epoch += 2;
+        FBF_CUDA(launch_copy_or_add(h->vec_out(), grad_weight, (long long)n_weight, accumulate, s));
+      } else {
+        ncclResult_t r = api->AllReduce(local_w, local_w, n_weight + bias_floats, ncclFloat, ncclSum, h->comm, s);
+        if (r != ncclSuccess) return nccl_fail(api, r, "ncclAllReduce(gradWeight partial transforms)");
+        FBF_CUDA(launch_copy_or_add(local_w, grad_weight, (long long)n_weight, accumulate, s));
+      }
     }
   } else if (h->comm && !spatial) {
     StageTimer t(h, pass, FBFFTCONV_STAGE_ALLREDUCE, s);
@@ -809,15 +978,24 @@ int fbfftconv_acc_grad_parameters(fbfftconv_handle* h, const float* input, const
     FBF_CUDA(launch_inverse(inverse_params(h->buf_w(), spatial ? local_w : grad_weight, nullptr, F, P, d.kernel_h,
                                            d.kernel_w, 0, 0, spatial ? 0 : accumulate, pm ? 2 : 0, h->N), h->N, s));
   }
+  const bool summed_by_peers = peer && (scatter || scatter_bins || spatial);
   if (spatial) {
     StageTimer t(h, pass, FBFFTCONV_STAGE_ALLREDUCE, s);
-    ncclResult_t r = api->AllReduce(local_w, local_w, n_weight + bias_floats, ncclFloat, ncclSum, h->comm, s);
-    if (r != ncclSuccess) return nccl_fail(api, r, "ncclAllReduce(gradWeight)");
-    FBF_CUDA(launch_copy_or_add(local_w, grad_weight, (long long)n_weight, accumulate, s));
+    if (peer) {
+      if (!grad_bias) FBF_CUDA(cudaMemsetAsync(bias_part, 0, F * sizeof(float), s));
+      FBF_CUDA(launch_peer_allreduce(h->peers, h->peer_epoch, vec4, s));
+      h->peer_epoch += 2;
+      FBF_CUDA(launch_copy_or_add(h->vec_out(), grad_weight, (long long)n_weight, accumulate, s));
+    } else {
+      ncclResult_t r = api->AllReduce(local_w, local_w, n_weight + bias_floats, ncclFloat, ncclSum, h->comm, s);
+      if (r != ncclSuccess) return nccl_fail(api, r, "ncclAllReduce(gradWeight)");
+      FBF_CUDA(launch_copy_or_add(local_w, grad_weight, (long long)n_weight, accumulate, s));
+    }
   }
   if (h->comm && grad_bias) {
     StageTimer t(h, pass, FBFFTCONV_STAGE_BIAS, s);
-    FBF_CUDA(launch_copy_or_add(bias_part, grad_bias, F, accumulate, s));
+    // summed over peers the bias gradient arrives behind gradWeight in the delivered vector
+    FBF_CUDA(launch_copy_or_add(summed_by_peers ? h->vec_out() + n_weight : bias_part, grad_bias, F, accumulate, s));
   }
   return FBFFTCONV_OK;
 }
@@ -1233,6 +1411,23 @@ int fbfftconv_acc_grad_parameters_bias(const float* grad_output, float* grad_bia
 }
 
 int fbfftconv_tensor_core_status(int reset) { return contract_tc_error(reset != 0); }
+
+int fbfftconv_peer_exchange_status(fbfftconv_handle* h, int reset) {
+  if (!h) return -1;
+  DeviceGuard g;
+  if (g.enter(h->device) != cudaSuccess) return -1;
+  const int code = peer_error(reset != 0);
+  if (code != 0) return code < 0 ? -1 : 100 + code;  // 100 + (1 + rank that did not arrive)
+  return h->peer_ready ? 1 : 0;
+}
+
+int fbfftconv_peer_exchange_wait_selftest(fbfftconv_stream stream) {
+  const int r = peer_wait_probe(static_cast<cudaStream_t>(stream));
+  if (r < 0) return fail(FBFFTCONV_ERR_CUDA, "wait self-test could not run: %s", cudaGetErrorString(cudaGetLastError()));
+  if (r != 1) return fail(FBFFTCONV_ERR_CUDA, "wait self-test: the bounded wait did not give up");
+  peer_error(true);  // the code it leaves (1) belongs to the test, not to an exchange
+  return FBFFTCONV_OK;
+}
 
 int fbfftconv_tensor_core_wait_selftest(fbfftconv_stream stream) {
   const int r = contract_tc_wait_probe(static_cast<cudaStream_t>(stream));

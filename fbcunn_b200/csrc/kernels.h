@@ -65,6 +65,31 @@ cudaError_t launch_copy_or_add(const float* src, float* dst, long long n, int ac
 cudaError_t launch_row_sum(const float* src, float* dst, int rows, int count, long long ld, long long step,
                            float scale, int accumulate, cudaStream_t stream);
 
+// ---- sums across ranks over peer memory (peer.cu) ------------------------------------------
+constexpr int kMaxPeers = 8;  // the GPUs of one NVSwitch box
+// What one rank knows of all ranks (index = rank; the own entries are local addresses, the others
+// CUDA IPC mappings): the weight-gradient spectrum, the vector that is summed after the inverse
+// transform and the block the sum is delivered to, and the flag array of the barriers.
+struct PeerTable {
+  char* spec[kMaxPeers];
+  char* vec_in[kMaxPeers];
+  char* vec_out[kMaxPeers];
+  unsigned* flags[kMaxPeers];  // kMaxPeers slots each: slot r = last epoch rank r has signalled
+  unsigned* counter;           // local, zero: counts the blocks that reached a kernel's end barrier
+  int rank, nranks;
+  unsigned spin_limit;         // polls before a wait gives up; 0 = the default (about ten seconds)
+};
+// Each launch is a collective: every rank calls it with the same epoch (which then advances by 2).
+// reduce: this rank's share [first4, first4 + count4) of spec (float4 units) becomes the sum over ranks.
+// allreduce: vec_out[i] = sum over ranks of vec_in[i], i < n4 float4s, on every rank.
+cudaError_t launch_peer_reduce(const PeerTable& t, unsigned epoch, size_t first4, size_t count4, cudaStream_t stream);
+cudaError_t launch_peer_allreduce(const PeerTable& t, unsigned epoch, size_t n4, cudaStream_t stream);
+// First non-zero code since the last reset: 1 + the rank a bounded wait gave up on.  Waits for the device.
+int peer_error(bool reset);
+// Makes one bounded wait on a peer flag run out on purpose: 1 = it gave up (code 1 left for
+// peer_error), 0 = it did not, < 0 = CUDA error.
+int peer_wait_probe(cudaStream_t stream);
+
 // Records `message` as the calling thread's last error (what fbfftconv_last_error
 // returns) and hands `code` back, for entry points that live outside api.cu.
 int report_error(int code, const char* message);

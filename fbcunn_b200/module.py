@@ -52,7 +52,7 @@ class SpatialConvolutionFBFFT:
 
     def __init__(self, nInputPlane, nOutputPlane, kW, kH, dW=1, dH=1, padLeft=0, padUp=0,
                  memoryReusePolicy=None, numCudaStreams=None, *, device="cuda", accumulate=False,
-                 contraction: str = "auto", allreduce: str = "spectrum"):
+                 contraction: str = "auto", allreduce: str = "spectrum", exchange: str = "auto"):
         for v in (nInputPlane, nOutputPlane, kW, kH, dW, dH, padLeft, padUp):
             assert _is_number(v), "constructor arguments must be numbers"
         assert memoryReusePolicy is None or isinstance(memoryReusePolicy, (str, list, tuple))
@@ -89,6 +89,9 @@ class SpatialConvolutionFBFFT:
         # gradWeight spectrum before the inverse transform, or gradWeight itself after it
         assert allreduce in ("spectrum", "spatial")
         self._allreduce = allreduce
+        # who carries that sum: the library's kernels over peer memory where they apply ("auto"), or NCCL only
+        assert exchange in ("auto", "nccl")
+        self._exchange = exchange
         shape_w = (self.nOutputPlane, self.nInputPlane, self.kH, self.kW)
         self.weight = torch.empty(shape_w, dtype=torch.float32, device=self.device)
         self.bias = torch.empty(self.nOutputPlane, dtype=torch.float32, device=self.device)
@@ -216,6 +219,11 @@ class SpatialConvolutionFBFFT:
         if self._handle is not None:
             self._init_comm()
 
+    def peerExchangeStatus(self, reset: bool = False) -> int:
+        """1 = accGradParameters sums over peer memory, 0 = over NCCL (or not run yet), 100 + c = a
+        bounded wait of the exchange gave up on rank c - 1 (fbfftconv_peer_exchange_status)."""
+        return int(capi.lib().fbfftconv_peer_exchange_status(self._handle, int(reset))) if self._handle is not None else 0
+
     @staticmethod
     def makeUniqueId() -> bytes:
         buf = ctypes.create_string_buffer(128)
@@ -253,6 +261,7 @@ class SpatialConvolutionFBFFT:
                 (capi.CONTRACT_SIMT if self._contraction == "simt" else 0) | \
                 (capi.BIN_MAJOR_ONLY if self._contraction == "bin_major" else 0) | \
                 (capi.ALLREDUCE_SPATIAL if self._allreduce == "spatial" else 0) | \
+                (capi.EXCHANGE_NCCL if self._exchange == "nccl" else 0) | \
                 (capi.REUSE_INPUT if memoryReuseInput in self.memoryReusePolicy else 0) | \
                 (capi.REUSE_OUTPUT if memoryReuseOutput in self.memoryReusePolicy else 0) | \
                 (capi.REUSE_WEIGHT if memoryReuseWeight in self.memoryReusePolicy else 0)

@@ -72,7 +72,10 @@ enum {
    * updateGradInput). */
   FBFFTCONV_REUSE_INPUT = 16,
   FBFFTCONV_REUSE_OUTPUT = 32,
-  FBFFTCONV_REUSE_WEIGHT = 64
+  FBFFTCONV_REUSE_WEIGHT = 64,
+  /* with a communicator attached, keep the whole weight-gradient exchange on NCCL instead of the
+   * sums over peer memory described at fbfftconv_comm_init (must be the same on every rank) */
+  FBFFTCONV_EXCHANGE_NCCL = 128
 };
 
 /* Constructor arguments of nn.SpatialConvolutionFBFFT
@@ -258,11 +261,30 @@ int fbfftconv_acc_grad_parameters_bias_noalloc(const float* grad_output, float* 
  * fbfftconv_comm_init.  Handles that name the same id share one communicator; it stays
  * alive (an id cannot be used twice) until fbfftconv_comm_shutdown, which destroys every
  * communicator no handle is attached to.  fbfftconv_comm_destroy detaches one handle.
- * libnccl is loaded at run time on the first call. */
+ * libnccl is loaded at run time on the first call.
+ *
+ * How the weight gradient is summed.  Up to 8 ranks (the GPUs of one NVSwitch box) whose scratch the
+ * library allocated itself map one another's scratch (CUDA IPC) at the first accGradParameters -- a
+ * collective step that waits for the stream once, so make that first call before any stream capture
+ * -- and the sum is then done by the library's own kernels over peer memory: every rank reads its
+ * share of the gradient spectrum from all ranks over NVLink, sums it in rank order, inverts it, and
+ * the small spatial parts are summed and delivered the same way; ranks meet at flag barriers in peer
+ * memory whose waits are bounded (about ten seconds), after which the kernel gives up and
+ * fbfftconv_peer_exchange_status reports it.  NCCL carries the exchange instead when the ranks do not
+ * divide the filters (plane-major layers) or the bins (bin-major layers), when a rank could not map a
+ * peer (all ranks then agree on NCCL), with caller-owned scratch (fbfftconv_set_workspace), with
+ * FBFFTCONV_EXCHANGE_NCCL, or with FBFFTCONV_PEER_EXCHANGE=0 in the environment of every rank. */
 int fbfftconv_comm_unique_id(void* id128);
 int fbfftconv_comm_init(fbfftconv_handle* h, const void* id128, int rank, int nranks);
 int fbfftconv_comm_destroy(fbfftconv_handle* h);
 int fbfftconv_comm_shutdown(void);
+/* 1 = this handle sums over peer memory, 0 = it uses NCCL (or has no communicator, or has not run
+ * accGradParameters yet); 100 + c = a bounded wait of the exchange gave up on rank c - 1 since the
+ * last reset (results of that call are incomplete); -1 = the query failed.  Waits for the device. */
+int fbfftconv_peer_exchange_status(fbfftconv_handle* h, int reset);
+/* Self-test of that give-up path without a second rank: one block waits for a flag nothing sets,
+ * with a limit of a few polls.  FBFFTCONV_OK when the wait gave up as designed. */
+int fbfftconv_peer_exchange_wait_selftest(fbfftconv_stream stream);
 
 /* ---- per-kernel timing ---------------------------------------------------------
  * With profiling enabled every kernel (and collective) a pass enqueues is bracketed

@@ -89,8 +89,9 @@ def test_workspace_accounting(lib):
     expect = bins * 8 * (128 * 384 + 128 * 384 + 384 * 384)
     got = lib.fbfftconv_workspace_bytes(h)
     # three spectra, the bias partial sums (B*F + F floats), the weight and bias gradient in the spatial
-    # domain for the sums across ranks (F*P*kH*kW + F floats, + F behind the spectrum), and alignment
-    small = (128 * 384 + 384) * 4 + (384 * 384 * 9 + 2 * 384) * 4
+    # domain for the sums across ranks, once as each rank's contribution and once as the delivered sum
+    # (2 x (F*P*kH*kW + F) floats, + F behind the spectrum), and alignment
+    small = (128 * 384 + 384) * 4 + 2 * (384 * 384 * 9 + 2 * 384) * 4
     assert expect <= got <= expect + small + 8 * 256
     assert lib.fbfftconv_spectrum_bytes(16, 128, 384) == bins * 128 * 384 * 8
     assert lib.fbfftconv_spectrum_bytes(16, 128, 3) == bins * 128 * 4 * 8

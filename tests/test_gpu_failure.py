@@ -59,6 +59,14 @@ def test_bounded_wait_gives_up_and_the_context_survives():
     assert _contraction_error() <= 1e-5
 
 
+def test_peer_flag_wait_gives_up():
+    """The flag barriers of the weight-gradient exchange over peer memory bound their waits the same
+    way; one rank, a flag nothing sets, a limit of a few polls."""
+    lib = capi.lib()
+    capi.check(lib.fbfftconv_peer_exchange_wait_selftest(_stream()))
+    assert _contraction_error() <= 1e-5
+
+
 def test_host_and_foreign_pointers_are_refused():
     """THCudaTensor_checkGPU of the reference's bindings (src/fft/SpatialConvolutionCuFFTHost.cpp:33-66)."""
     lib = capi.lib()

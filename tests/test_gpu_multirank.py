@@ -42,9 +42,9 @@ def _data(s, seed):
     return x, go
 
 
-def _grads(s, x, go, scale, allreduce, comm, accumulate=False, device="cuda"):
+def _grads(s, x, go, scale, allreduce, comm, accumulate=False, device="cuda", exchange="auto", status=None):
     m = SpatialConvolutionFBFFT(s.P, s.F, s.kW, s.kH, 1, 1, s.padW, s.padH, device=device,
-                                allreduce=allreduce, accumulate=accumulate)
+                                allreduce=allreduce, accumulate=accumulate, exchange=exchange)
     if comm is not None:
         m.attachCommunicator(*comm)
     dx = torch.from_numpy(x).to(device)
@@ -53,7 +53,13 @@ def _grads(s, x, go, scale, allreduce, comm, accumulate=False, device="cuda"):
         m.gradWeight.fill_(1.0)
         m.gradBias.fill_(2.0)
     m.accGradParameters(dx, dgo, scale)
+    m.accGradParameters(dx, dgo, scale)  # a second call: the exchange's buffers and epochs must be reusable
+    if accumulate:  # two calls added twice
+        m.gradWeight.sub_(1.0).div_(2.0).add_(1.0)
+        m.gradBias.sub_(2.0).div_(2.0).add_(2.0)
     torch.cuda.synchronize()
+    if status is not None:
+        status.append(m.peerExchangeStatus())
     return m.gradWeight.cpu().numpy(), m.gradBias.cpu().numpy()
 
 
@@ -105,25 +111,27 @@ def _worker(rank, world, port, out_dir):
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         uid = share_unique_id(dist, SpatialConvolutionFBFFT.makeUniqueId, device="cpu")
-        worst, cases = 0.0, 0
+        worst, cases, status = 0.0, 0, []
         for idx, s in enumerate(RANK_SHAPES):
             x, go = _data(s, 70 + idx)  # same on every rank
             b0, b1 = batch_slice(s.B, rank, world)
             local = oracle.Shape(b1 - b0, s.P, s.F, s.iH, s.iW, s.kH, s.kW, s.padH, s.padW)
             ref_w = oracle.acc_grad_weight(s, x, go, 2.0)
             ref_b = oracle.acc_grad_bias(s, go, 2.0)
-            for allreduce in ("spectrum", "spatial"):
-                for accumulate in (False, True):
-                    gw, gb = _grads(local, np.ascontiguousarray(x[b0:b1]), np.ascontiguousarray(go[b0:b1]), 2.0,
-                                    allreduce, (uid, rank, world), accumulate=accumulate, device=f"cuda:{rank}")
-                    worst = max(worst, _rel(gw, ref_w + (1.0 if accumulate else 0.0)),
-                                _rel(gb, ref_b + (2.0 if accumulate else 0.0)))
-                    cases += 1
+            for exchange in ("auto", "nccl"):
+                for allreduce in ("spectrum", "spatial"):
+                    for accumulate in (False, True):
+                        gw, gb = _grads(local, np.ascontiguousarray(x[b0:b1]), np.ascontiguousarray(go[b0:b1]), 2.0,
+                                        allreduce, (uid, rank, world), accumulate=accumulate, device=f"cuda:{rank}",
+                                        exchange=exchange, status=status)
+                        worst = max(worst, _rel(gw, ref_w + (1.0 if accumulate else 0.0)),
+                                    _rel(gb, ref_b + (2.0 if accumulate else 0.0)))
+                        cases += 1
         import gc
         gc.collect()  # the modules detach from the communicator before it is shut down
         rc = capi.lib().fbfftconv_comm_shutdown()
         with open(os.path.join(out_dir, f"rank{rank}"), "w") as f:
-            f.write(repr((worst, cases, rc)))
+            f.write(repr((worst, cases, rc, status)))
     finally:
         dist.destroy_process_group()
 
@@ -135,10 +143,18 @@ def test_ranks_sum_the_gradient(tmp_path, world):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
-    for rank in range(world):
-        worst, cases, rc = eval(open(tmp_path / f"rank{rank}").read())
-        assert cases == 4 * len(RANK_SHAPES)
+    results = [eval(open(tmp_path / f"rank{rank}").read()) for rank in range(world)]
+    for rank, (worst, cases, rc, status) in enumerate(results):
+        assert cases == 8 * len(RANK_SHAPES)
         assert rc == 0, f"rank {rank}: communicator still attached at shutdown"
         assert worst <= PASS_TOL, f"rank {rank}: {worst}"
-    print(f"world {world}: {4 * len(RANK_SHAPES)} cases per rank, worst relative error "
-          f"{max(eval(open(tmp_path / f'rank{r}').read())[0] for r in range(world)):.2e}")
+        assert all(st in (0, 1) for st in status), f"rank {rank}: a wait of the peer exchange gave up: {status}"
+        assert status == results[0][3], "every rank must make the same choice of exchange"
+        # "nccl" handles never use peer memory; "auto" handles do on a box whose GPUs can map one another
+        per_shape = 8
+        for i, st in enumerate(status):
+            if (i % per_shape) >= per_shape // 2:
+                assert st == 0
+    over_peers = sum(results[0][3])
+    print(f"world {world}: {8 * len(RANK_SHAPES)} cases per rank, {over_peers} of them summed over peer memory, "
+          f"worst relative error {max(r[0] for r in results):.2e}")
