@@ -392,7 +392,9 @@ bool thin_contraction(int m, int n, int k) {
   return n <= 4 || k < 8;
 }
 
-bool valid_fft_size(int n) { return n == 8 || n == 16 || n == 32 || n == 64 || n == 128; }
+// sizes of the stand-alone transforms (nn.FFTWrapper, test/test_FFTModule.lua:170-260); a convolution never
+// picks less than 8
+bool valid_fft_size(int n) { return n == 2 || n == 4 || n == 8 || n == 16 || n == 32 || n == 64 || n == 128; }
 
 // What the reference's bindings check before they launch (THCudaTensor_checkGPU over all tensors,
 // src/fft/SpatialConvolutionCuFFTHost.cpp:33-66): every tensor lives in device memory of the
@@ -1336,7 +1338,7 @@ int fbfftconv_host_sync(fbfftconv_handle* h) {
 int fbfftconv_fft2d(const float* real, void* spectrum, int d1, int d2, int h, int w, int fft_size,
                     int pad_u, int pad_l, int transposed, fbfftconv_stream stream) {
   if (!real || !spectrum) return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "null argument");
-  if (!valid_fft_size(fft_size)) return fail(FBFFTCONV_ERR_UNSUPPORTED_SIZE, "transform size %d not in {8,16,32,64,128}", fft_size);
+  if (!valid_fft_size(fft_size)) return fail(FBFFTCONV_ERR_UNSUPPORTED_SIZE, "transform size %d not in {2,4,8,16,32,64,128}", fft_size);
   if (d1 <= 0 || d2 <= 0 || h <= 0 || w <= 0 || pad_u < 0 || pad_l < 0 || h + pad_u > fft_size ||
       w + pad_l > fft_size || d1 > 65535 || d2 > 65535)
     return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "plane of %dx%d at (%d,%d) does not fit %d", h, w, pad_u, pad_l, fft_size);
@@ -1349,7 +1351,7 @@ int fbfftconv_ifft2d(const void* spectrum, float* real, const float* bias, int d
                      int w, int fft_size, int off_y, int off_x, int accumulate, int plane_major,
                      fbfftconv_stream stream) {
   if (!real || !spectrum) return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "null argument");
-  if (!valid_fft_size(fft_size)) return fail(FBFFTCONV_ERR_UNSUPPORTED_SIZE, "transform size %d not in {8,16,32,64,128}", fft_size);
+  if (!valid_fft_size(fft_size)) return fail(FBFFTCONV_ERR_UNSUPPORTED_SIZE, "transform size %d not in {2,4,8,16,32,64,128}", fft_size);
   if (d1 <= 0 || d2 <= 0 || h <= 0 || w <= 0 || off_y < 0 || off_x < 0 || h + off_y > fft_size ||
       w + off_x > fft_size || d1 > 65535 || d2 > 65535)
     return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "window of %dx%d at (%d,%d) does not fit %d", h, w, off_y, off_x, fft_size);
@@ -1358,10 +1360,29 @@ int fbfftconv_ifft2d(const void* spectrum, float* real, const float* bias, int d
   return FBFFTCONV_OK;
 }
 
+int fbfftconv_fft2d_reference_layout(const float* real, void* frequency, void* scratch, int planes, int h, int w,
+                                     int fft_size, int pad_u, int pad_l, fbfftconv_stream stream) {
+  if (!scratch || !frequency) return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "null argument");
+  FBF_TRY(fbfftconv_fft2d(real, scratch, 1, planes, h, w, fft_size, pad_u, pad_l, 0, stream));
+  FBF_CUDA(launch_spectrum_layout(true, static_cast<const float2*>(scratch), static_cast<float2*>(frequency), planes,
+                                  pad4(planes), fft_size, static_cast<cudaStream_t>(stream)));
+  return FBFFTCONV_OK;
+}
+
+int fbfftconv_ifft2d_reference_layout(const void* frequency, float* real, void* scratch, int planes, int h, int w,
+                                      int fft_size, int off_y, int off_x, fbfftconv_stream stream) {
+  if (!scratch || !frequency || !real) return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "null argument");
+  if (!valid_fft_size(fft_size)) return fail(FBFFTCONV_ERR_UNSUPPORTED_SIZE, "transform size %d not in {2,4,8,16,32,64,128}", fft_size);
+  if (planes <= 0 || planes > 65535) return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "between 1 and 65535 planes");
+  FBF_CUDA(launch_spectrum_layout(false, static_cast<const float2*>(frequency), static_cast<float2*>(scratch), planes,
+                                  pad4(planes), fft_size, static_cast<cudaStream_t>(stream)));
+  return fbfftconv_ifft2d(scratch, real, nullptr, 1, planes, h, w, fft_size, off_y, off_x, 0, 0, stream);
+}
+
 int fbfftconv_fft1d(const float* real, void* spectrum, long long rows, int n, int fft_size,
                     int pad_left, fbfftconv_stream stream) {
   if (!real || !spectrum) return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "null argument");
-  if (!valid_fft_size(fft_size)) return fail(FBFFTCONV_ERR_UNSUPPORTED_SIZE, "transform size %d not in {8,16,32,64,128}", fft_size);
+  if (!valid_fft_size(fft_size)) return fail(FBFFTCONV_ERR_UNSUPPORTED_SIZE, "transform size %d not in {2,4,8,16,32,64,128}", fft_size);
   if (rows <= 0 || n <= 0 || pad_left < 0 || n + pad_left > fft_size)
     return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "row of %d floats at %d does not fit %d", n, pad_left, fft_size);
   FBF_CUDA(launch_fft1d(false, real, nullptr, static_cast<float2*>(spectrum), rows, n, fft_size, pad_left,
@@ -1372,7 +1393,7 @@ int fbfftconv_fft1d(const float* real, void* spectrum, long long rows, int n, in
 int fbfftconv_ifft1d(const void* spectrum, float* real, long long rows, int n, int fft_size,
                      int offset, fbfftconv_stream stream) {
   if (!real || !spectrum) return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "null argument");
-  if (!valid_fft_size(fft_size)) return fail(FBFFTCONV_ERR_UNSUPPORTED_SIZE, "transform size %d not in {8,16,32,64,128}", fft_size);
+  if (!valid_fft_size(fft_size)) return fail(FBFFTCONV_ERR_UNSUPPORTED_SIZE, "transform size %d not in {2,4,8,16,32,64,128}", fft_size);
   if (rows <= 0 || n <= 0 || offset < 0 || n + offset > fft_size)
     return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "window of %d floats at %d does not fit %d", n, offset, fft_size);
   FBF_CUDA(launch_fft1d(true, nullptr, real, static_cast<float2*>(const_cast<void*>(spectrum)), rows, n, fft_size,

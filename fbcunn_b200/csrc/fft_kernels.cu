@@ -302,6 +302,8 @@ cudaError_t dispatch_tile(bool inverse, const FftParams& p, int T, cudaStream_t 
 
 cudaError_t dispatch(bool inverse, const FftParams& p, int N, int T, cudaStream_t s) {
   switch (N) {
+    case 2: return dispatch_tile<2>(inverse, p, T, s);
+    case 4: return dispatch_tile<4>(inverse, p, T, s);
     case 8: return dispatch_tile<8>(inverse, p, T, s);
     case 16: return dispatch_tile<16>(inverse, p, T, s);
     case 32: return dispatch_tile<32>(inverse, p, T, s);
@@ -414,6 +416,8 @@ cudaError_t launch_fft1d(bool inverse, const float* real_in, float* real_out, fl
     if (T == 0) return cudaErrorInvalidConfiguration;
     cudaError_t e;
     switch (N) {
+      case 2: e = dispatch_1d_tile<2>(inverse, p, T, stream); break;
+      case 4: e = dispatch_1d_tile<4>(inverse, p, T, stream); break;
       case 8: e = dispatch_1d_tile<8>(inverse, p, T, stream); break;
       case 16: e = dispatch_1d_tile<16>(inverse, p, T, stream); break;
       case 32: e = dispatch_1d_tile<32>(inverse, p, T, stream); break;
@@ -424,6 +428,85 @@ cudaError_t launch_fft1d(bool inverse, const float* real_in, float* real_out, fl
     if (e != cudaSuccess) return e;
   }
   return cudaSuccess;
+}
+
+namespace {
+
+// The reference's 2-D frequency tensor (planes, N/2+1, N, 2) holds, for 8 <= N <= 32, rows ky <= N/2
+// of the full spectrum (element [ky][kx] = X[ky][kx] for every kx), and for the other sizes the half
+// spectrum along x stored transposed (element [kx][ky] = X[ky][kx], kx <= N/2)
+// (test/test_FFTModule.lua:310-342).  The library's half spectrum is [bin = ky*(N/2+1) + kx][plane],
+// kx <= N/2; the missing half follows from X[ky][kx] = conj(X[-ky][-kx]).
+__global__ void __launch_bounds__(256)
+spectrum_to_reference_kernel(const float2* __restrict__ spec, float2* __restrict__ ref, long long planes, int kc,
+                             int N, int transposed) {
+  const int KX = N / 2 + 1;
+  const long long per_plane = (long long)KX * N;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < planes * per_plane;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long p = i / per_plane;
+    const int r = (int)(i - p * per_plane);
+    const int a = r / N, b = r - a * N;  // element [a][b] of the reference tensor, a <= N/2
+    int ky, kx;
+    bool conj = false;
+    if (transposed) {
+      kx = a;
+      ky = b;
+    } else {
+      ky = a;
+      kx = b;
+      if (kx > N / 2) {
+        ky = (N - ky) % N;
+        kx = N - kx;
+        conj = true;
+      }
+    }
+    float2 v = spec[((long long)ky * KX + kx) * kc + p];
+    if (conj) v.y = -v.y;
+    ref[i] = v;
+  }
+}
+
+__global__ void __launch_bounds__(256)
+reference_to_spectrum_kernel(const float2* __restrict__ ref, float2* __restrict__ spec, long long planes, int kc,
+                             int N, int transposed) {
+  const int KX = N / 2 + 1;
+  const long long bins = (long long)KX * N;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < bins * kc;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long bin = i / kc;
+    const long long p = i - bin * kc;
+    float2 v = make_float2(0.f, 0.f);  // the padding planes of the library's layout are zero
+    if (p < planes) {
+      const int ky = (int)(bin / KX), kx = (int)(bin - (long long)ky * KX);
+      const float2* plane = ref + p * bins;
+      if (transposed) {
+        v = plane[kx * N + ky];
+      } else if (ky <= N / 2) {
+        v = plane[ky * N + kx];
+      } else {  // X[ky][kx] = conj(X[N-ky][(N-kx) % N])
+        v = plane[(N - ky) * N + (N - kx) % N];
+        v.y = -v.y;
+      }
+    }
+    spec[i] = v;
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_spectrum_layout(bool to_reference, const float2* src, float2* dst, long long planes, int kc, int N,
+                                   cudaStream_t stream) {
+  const bool transposed = N < 8 || N > 32;
+  const long long total = to_reference ? planes * (N / 2 + 1) * N : (long long)(N / 2 + 1) * N * kc;
+  const long long want = (total + 255) / 256, cap = (long long)sm_count() * 16;
+  const int blocks = (int)(want < 1 ? 1 : want < cap ? want : cap);
+  if (to_reference)
+    spectrum_to_reference_kernel<<<blocks, 256, 0, stream>>>(src, dst, planes, kc, N, transposed);
+  else
+    reference_to_spectrum_kernel<<<blocks, 256, 0, stream>>>(src, dst, planes, kc, N, transposed);
+  count_launch();
+  return cudaGetLastError();
 }
 
 }  // namespace fbfft

@@ -25,6 +25,10 @@ cudaError_t launch_forward(const FftParams& p, int N, cudaStream_t stream);
 cudaError_t launch_fft1d(bool inverse, const float* real_in, float* real_out, float2* spec, long long rows, int n,
                          int N, int offset, cudaStream_t stream);
 cudaError_t launch_inverse(const FftParams& p, int N, cudaStream_t stream);
+// Between the library's half spectrum [bin][plane (padded to kc)] and the reference's 2-D frequency
+// tensor (planes, N/2+1, N, 2) (nn.FFTWrapper, test/test_FFTModule.lua:310-342).
+cudaError_t launch_spectrum_layout(bool to_reference, const float2* src, float2* dst, long long planes, int kc, int N,
+                                   cudaStream_t stream);
 
 struct ContractParams {
   const float2* a;   // [bins][m][lda], lda >= k;  with a_mn: [bins][k][lda], lda >= m

@@ -397,20 +397,20 @@ class FFTWrapper:
         assert frequency.shape[-3] == n_fft // 2 + 1
         h, w = time.shape[-2:]
         planes = time.numel() // (h * w)
-        spec = self.frequency_tensor(1, planes, n_fft, device=time.device)
-        capi.check(capi.lib().fbfftconv_fft2d(_ptr(time), _ptr(spec), 1, planes, h, w, n_fft, self.padUp,
-                                              self.padLeft, 0, stream))
-        s = self.to_plane_major(spec, planes, n_fft)[0]            # planes, ky, kx (kx <= N/2)
-        if self._half_along_rows(n_fft):
-            # X[ky][kx] for ky <= N/2 and every kx: the columns beyond N/2 by Hermitian symmetry
-            idx = (n_fft - torch.arange(n_fft, device=time.device)) % n_fft
-            upper = s[:, idx][:, :, idx[n_fft // 2 + 1:]].conj()    # X[-ky][-kx], kx > N/2
-            full = torch.cat([s, upper], dim=2)                       # planes, ky, all kx
-            out = full[:, :n_fft // 2 + 1, :]
-        else:
-            out = s.transpose(1, 2)                                   # planes, kx, ky
-        frequency.copy_(torch.view_as_real(out.contiguous()).reshape(frequency.shape))
+        scratch = self._scratch(planes, n_fft, time.device)
+        capi.check(capi.lib().fbfftconv_fft2d_reference_layout(
+            _ptr(time), _ptr(frequency), _ptr(scratch), planes, h, w, n_fft, self.padUp, self.padLeft, stream))
         return frequency
+
+    def _scratch(self, planes, n_fft, device):
+        """The library's own half spectrum of `planes` planes (a kernel converts it to / from the
+        reference's tensor); kept between calls of the same size."""
+        need = int(capi.lib().fbfftconv_spectrum_bytes(n_fft, 1, planes))
+        buf = getattr(self, "_scratch_buf", None)
+        if buf is None or buf.numel() < need or buf.device != torch.device(device):
+            buf = torch.empty(need, dtype=torch.uint8, device=device)
+            self._scratch_buf = buf
+        return buf
 
     def ffti_reference_layout(self, time: torch.Tensor, frequency: torch.Tensor, batchDims: int):
         assert 1 <= batchDims <= 2 and time.is_cuda and time.dtype == torch.float32 and time.is_contiguous()
@@ -426,15 +426,7 @@ class FFTWrapper:
         n_fft = frequency.shape[-2]
         h, w = time.shape[-2:]
         planes = time.numel() // (h * w)
-        f = torch.view_as_complex(frequency.reshape(planes, n_fft // 2 + 1, n_fft, 2))
-        if self._half_along_rows(n_fft):
-            # S[ky][kx], kx <= N/2: rows beyond N/2 by Hermitian symmetry
-            idx = (n_fft - torch.arange(n_fft, device=time.device)) % n_fft
-            lower = f[:, idx[n_fft // 2 + 1:]][:, :, idx].conj()      # X[ky > N/2][kx] = conj(X[-ky][-kx])
-            s = torch.cat([f, lower], dim=1)[:, :, :n_fft // 2 + 1]
-        else:
-            s = f.transpose(1, 2)
-        spec = self.from_plane_major(s.reshape(1, planes, n_fft, n_fft // 2 + 1).contiguous(), n_fft)
-        capi.check(capi.lib().fbfftconv_ifft2d(_ptr(spec), _ptr(time), None, 1, planes, h, w, n_fft, self.padUp,
-                                               self.padLeft, 0, 0, stream))
+        scratch = self._scratch(planes, n_fft, time.device)
+        capi.check(capi.lib().fbfftconv_ifft2d_reference_layout(
+            _ptr(frequency), _ptr(time), _ptr(scratch), planes, h, w, n_fft, self.padUp, self.padLeft, stream))
         return time

@@ -193,12 +193,23 @@ int fbfftconv_fft2d(const float* real, void* spectrum, int d1, int d2, int h, in
 int fbfftconv_ifft2d(const void* spectrum, float* real, const float* bias, int d1, int d2, int h,
                      int w, int fft_size, int off_y, int off_x, int accumulate, int plane_major,
                      fbfftconv_stream stream);
+/* The same 2-D transforms on the reference's frequency tensor (planes, N/2+1, N, 2) complex fp32
+ * (nn.FFTWrapper with two FFT dimensions, fbcunn/FFTWrapper.lua:53-132): for 8 <= N <= 32 element
+ * [ky][kx] = X[ky][kx], ky <= N/2, every kx; for the other sizes the half spectrum along x stored
+ * transposed, element [kx][ky] = X[ky][kx], kx <= N/2 (test/test_FFTModule.lua:310-342).  `planes`
+ * real planes of h x w (at most 65535); `scratch` holds fbfftconv_spectrum_bytes(fft_size, 1, planes)
+ * bytes for the library's own layout; a kernel converts between the two. */
+int fbfftconv_fft2d_reference_layout(const float* real, void* frequency, void* scratch, int planes, int h, int w,
+                                     int fft_size, int pad_u, int pad_l, fbfftconv_stream stream);
+int fbfftconv_ifft2d_reference_layout(const void* frequency, float* real, void* scratch, int planes, int h, int w,
+                                      int fft_size, int off_y, int off_x, fbfftconv_stream stream);
 /* Replaces FFTWrapper_fft / FFTWrapper_ffti for the 1-D batched case
  * (src/fft/FFTWrapperLua.cpp:209-272, fbfft1dHost in src/fft/FBFFTHost.cpp:119-160): `rows`
  * contiguous rows of n floats, each placed at `pad_left` of a zero line of fft_size, ->
  * spectrum[row][k], k in [0, fft_size/2], complex fp32: the reference's (batch, N/2+1, 2)
  * tensor.  The inverse is un-normalised and keeps columns [offset, offset + n).
- * fft_size in {8, 16, 32, 64, 128}. */
+ * fft_size in {2, 4, 8, 16, 32, 64, 128} (so are the 2-D stand-alone transforms; a convolution
+ * handle never picks less than 8). */
 int fbfftconv_fft1d(const float* real, void* spectrum, long long rows, int n, int fft_size,
                     int pad_left, fbfftconv_stream stream);
 int fbfftconv_ifft1d(const void* spectrum, float* real, long long rows, int n, int fft_size,

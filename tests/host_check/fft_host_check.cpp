@@ -204,6 +204,8 @@ int dispatch_t(bool inverse, const FftParams& p, int T, int oh, int ow) {
 
 int dispatch(bool inverse, const FftParams& p, int N, int T, int oh, int ow) {
   switch (N) {
+    case 2: return dispatch_t<2>(inverse, p, T, oh, ow);
+    case 4: return dispatch_t<4>(inverse, p, T, oh, ow);
     case 8: return dispatch_t<8>(inverse, p, T, oh, ow);
     case 16: return dispatch_t<16>(inverse, p, T, oh, ow);
     case 32: return dispatch_t<32>(inverse, p, T, oh, ow);
@@ -243,6 +245,8 @@ int hostcheck_fft1d(int inverse, float* real, float* spec, int N, int T, int h, 
   p.n_rows = 1; p.n_inner = planes; p.kc = planes;
   p.real_row_stride = 0; p.real_inner_stride = 1;
   switch (N) {
+    case 2: return dispatch_1d_t<2>(inverse != 0, p, T);
+    case 4: return dispatch_1d_t<4>(inverse != 0, p, T);
     case 8: return dispatch_1d_t<8>(inverse != 0, p, T);
     case 16: return dispatch_1d_t<16>(inverse != 0, p, T);
     case 32: return dispatch_1d_t<32>(inverse != 0, p, T);

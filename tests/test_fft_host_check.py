@@ -31,7 +31,7 @@ def _bin_major(spec_plane_major):
     return spec_plane_major.transpose(2, 3, 0, 1).reshape(half * n, d1, d2)
 
 
-CASES = [(N, T) for N in (8, 16, 32, 64, 128) for T in (1, 2, 4, 8, 16)
+CASES = [(N, T) for N in (2, 4, 8, 16, 32, 64, 128) for T in (1, 2, 4, 8, 16)
          if (T <= (8 if N == 64 else 2) if N > 32 else (N // 2 + 1) * T <= 512)]
 
 
@@ -39,7 +39,9 @@ CASES = [(N, T) for N in (8, 16, 32, 64, 128) for T in (1, 2, 4, 8, 16)
 def test_forward(hc, N, T):
     rng = np.random.default_rng(N * 100 + T)
     ran = 0
-    for (h, w, pu, pl) in [(N, N, 0, 0), (3, 3, 0, 0), (N - 3, N - 5, 1, 2), (1, 1, 0, 0)]:
+    for (h, w, pu, pl) in [(N, N, 0, 0), (3, 3, 0, 0), (N - 3, N - 5, 1, 2), (1, 1, 0, 0), (N - 1, N - 1, 1, 0)]:
+        if h < 1 or w < 1 or h + pu > N or w + pl > N:
+            continue  # the two smallest sizes cannot hold every window
         if hc.hostcheck_forward_smem_bytes(N, T, h, w, pu, pl) > 227 * 1024:
             continue
         assert hc.hostcheck_forward_threads(N, T, h, w, pu, pl) > 0
@@ -66,7 +68,10 @@ def test_forward(hc, N, T):
 @pytest.mark.parametrize("N,T", CASES)
 def test_inverse(hc, N, T):
     rng = np.random.default_rng(N * 100 + T + 7)
-    for (oh, ow, oy, ox) in [(N, N, 0, 0), (3, 3, 0, 0), (N - 3, N - 5, 1, 2), (N - 4, N - 4, 0, 0), (1, 1, 2, 3)]:
+    for (oh, ow, oy, ox) in [(N, N, 0, 0), (3, 3, 0, 0), (N - 3, N - 5, 1, 2), (N - 4, N - 4, 0, 0), (1, 1, 2, 3),
+                             (N - 1, N - 1, 1, 0), (1, 1, 1, 1)]:
+        if oh < 1 or ow < 1 or oh + oy > N or ow + ox > N:
+            continue
         if hc.hostcheck_inverse_smem_bytes(N, T, oh, ow) > 227 * 1024:
             continue
         assert hc.hostcheck_inverse_threads(N, T, oh, ow) > 0
@@ -113,11 +118,13 @@ def test_plane_major_layout(hc, N, T):
     assert np.abs(out / (N * N) - x).max() <= 5e-6 * np.abs(x).max()
 
 
-@pytest.mark.parametrize("N,T", [(8, 16), (16, 4), (32, 16), (64, 2), (64, 8), (128, 1), (128, 2)])
+@pytest.mark.parametrize("N,T", [(2, 16), (4, 16), (4, 2), (8, 16), (16, 4), (32, 16), (64, 2), (64, 8), (128, 1), (128, 2)])
 def test_1d_transforms(hc, N, T):
     """The batched 1-D kernels (row phases + plain store / load of the column buffer) against numpy."""
     rng = np.random.default_rng(N + T)
-    for (h, n, off, planes) in [(N, N, 0, 3), (5, N - 3, 2, 2), (1, 1, 0, 1), (N, 7, 0, 5)]:
+    for (h, n, off, planes) in [(N, N, 0, 3), (5, N - 3, 2, 2), (1, 1, 0, 1), (N, 7, 0, 5), (N, N - 1, 1, 4)]:
+        if h > N or n < 1 or n + off > N:
+            continue
         if hc.hostcheck_forward_smem_bytes(N, T, h, n, 0, off) > 227 * 1024:
             continue
         x = rng.standard_normal((planes * h, n)).astype(np.float32)

@@ -18,8 +18,12 @@ def _complex(t):
     return a[..., 0] + 1j * a[..., 1]
 
 
-@pytest.mark.parametrize("n", [8, 16, 32, 64, 128])
-@pytest.mark.parametrize("batch", [(4,), (3, 5), (1000,)])
+# the sizes of the reference's own test list (test/test_FFTModule.lua:170-260)
+SIZES = [2, 4, 8, 16, 32, 64, 128]
+
+
+@pytest.mark.parametrize("n", SIZES)
+@pytest.mark.parametrize("batch", [(1,), (4,), (3, 5), (127,), (437,), (1000,)])
 def test_1d(n, batch):
     rng = np.random.default_rng(n + len(batch))
     x = rng.standard_normal(batch + (n,)).astype(np.float32)
@@ -46,8 +50,8 @@ def test_1d_short_rows_are_zero_padded():
     assert np.abs(_complex(freq) - ref).max() <= TOL * np.abs(ref).max()
 
 
-@pytest.mark.parametrize("n", [8, 16, 32, 64, 128])
-@pytest.mark.parametrize("batch", [(3,), (2, 3)])
+@pytest.mark.parametrize("n", SIZES)
+@pytest.mark.parametrize("batch", [(1,), (3,), (9,), (2, 3), (128,)])
 def test_2d_reference_layout(n, batch):
     rng = np.random.default_rng(10 * n + len(batch))
     x = rng.standard_normal(batch + (n, n)).astype(np.float32)
