@@ -72,6 +72,14 @@ _SIGNATURES = {
     "fbfftconv_ifft2d": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "fbfftconv_fft1d": (c_int, [c_void_p, c_void_p, ctypes.c_longlong, c_int, c_int, c_int, c_void_p]),
     "fbfftconv_ifft1d": (c_int, [c_void_p, c_void_p, ctypes.c_longlong, c_int, c_int, c_int, c_void_p]),
+    "fbfftconv_tiled_create": (c_int, [POINTER(Desc), c_int, c_int, POINTER(c_void_p)]),
+    "fbfftconv_tiled_destroy": (c_int, [c_void_p]),
+    "fbfftconv_tiled_inner": (c_void_p, [c_void_p]),
+    "fbfftconv_tiled_workspace_bytes": (c_size_t, [c_void_p]),
+    "fbfftconv_tiled_geometry": (c_int, [c_void_p, POINTER(c_int32)]),
+    "fbfftconv_tiled_update_output": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "fbfftconv_tiled_update_grad_input": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "fbfftconv_tiled_acc_grad_parameters": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p]),
     "fbfftconv_fft2d_reference_layout": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "fbfftconv_ifft2d_reference_layout": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "fbfftconv_transpose_mm": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p]),

@@ -399,7 +399,7 @@ bool valid_fft_size(int n) { return n == 2 || n == 4 || n == 8 || n == 16 || n =
 // What the reference's bindings check before they launch (THCudaTensor_checkGPU over all tensors,
 // src/fft/SpatialConvolutionCuFFTHost.cpp:33-66): every tensor lives in device memory of the
 // module's GPU.  A host pointer, or memory of another GPU, is refused instead of launched on.
-int check_device_pointer(const fbfftconv_handle* h, const void* ptr, const char* name) {
+int check_device_pointer(int device, const void* ptr, const char* name) {
   if (!ptr) return FBFFTCONV_OK;  // optional arguments; the required ones were checked for null
   cudaPointerAttributes attr{};
   cudaError_t e = cudaPointerGetAttributes(&attr, ptr);
@@ -410,8 +410,8 @@ int check_device_pointer(const fbfftconv_handle* h, const void* ptr, const char*
   if (attr.type == cudaMemoryTypeManaged) return FBFFTCONV_OK;
   if (attr.type != cudaMemoryTypeDevice)
     return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "%s is not a device pointer (use the *_host entry points for host buffers)", name);
-  if (attr.device != h->device)
-    return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "%s lives on device %d, the handle on device %d", name, attr.device, h->device);
+  if (attr.device != device)
+    return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "%s lives on device %d, the handle on device %d", name, attr.device, device);
   return FBFFTCONV_OK;
 }
 
@@ -559,6 +559,9 @@ void release_comm(fbfftconv_handle* h) {
 
 namespace fbfft {
 int report_error(int code, const char* message) { return fail(code, "%s", message); }
+int validate_device_pointer(int device, const void* ptr, const char* name) {
+  return check_device_pointer(device, ptr, name);
+}
 }  // namespace fbfft
 
 extern "C" {
@@ -700,10 +703,10 @@ int fbfftconv_update_output(fbfftconv_handle* h, const float* input, const float
   if (!h || !input || !weight || !output) return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "null argument");
   DeviceGuard g;
   FBF_CUDA(g.enter(h->device));
-  FBF_TRY(check_device_pointer(h, input, "input"));
-  FBF_TRY(check_device_pointer(h, weight, "weight"));
-  FBF_TRY(check_device_pointer(h, bias, "bias"));
-  FBF_TRY(check_device_pointer(h, output, "output"));
+  FBF_TRY(check_device_pointer(h->device, input, "input"));
+  FBF_TRY(check_device_pointer(h->device, weight, "weight"));
+  FBF_TRY(check_device_pointer(h->device, bias, "bias"));
+  FBF_TRY(check_device_pointer(h->device, output, "output"));
   FBF_TRY(ensure_workspace(h));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const fbfftconv_desc& d = h->d;
@@ -757,9 +760,9 @@ int fbfftconv_update_grad_input(fbfftconv_handle* h, const float* grad_output, c
     return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "null argument");
   DeviceGuard g;
   FBF_CUDA(g.enter(h->device));
-  FBF_TRY(check_device_pointer(h, grad_output, "gradOutput"));
-  FBF_TRY(check_device_pointer(h, weight, "weight"));
-  FBF_TRY(check_device_pointer(h, grad_input, "gradInput"));
+  FBF_TRY(check_device_pointer(h->device, grad_output, "gradOutput"));
+  FBF_TRY(check_device_pointer(h->device, weight, "weight"));
+  FBF_TRY(check_device_pointer(h->device, grad_input, "gradInput"));
   FBF_TRY(ensure_workspace(h));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const fbfftconv_desc& d = h->d;
@@ -815,10 +818,10 @@ int fbfftconv_acc_grad_parameters(fbfftconv_handle* h, const float* input, const
     return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "null argument");
   DeviceGuard g;
   FBF_CUDA(g.enter(h->device));
-  FBF_TRY(check_device_pointer(h, input, "input"));
-  FBF_TRY(check_device_pointer(h, grad_output, "gradOutput"));
-  FBF_TRY(check_device_pointer(h, grad_weight, "gradWeight"));
-  FBF_TRY(check_device_pointer(h, grad_bias, "gradBias"));
+  FBF_TRY(check_device_pointer(h->device, input, "input"));
+  FBF_TRY(check_device_pointer(h->device, grad_output, "gradOutput"));
+  FBF_TRY(check_device_pointer(h->device, grad_weight, "gradWeight"));
+  FBF_TRY(check_device_pointer(h->device, grad_bias, "gradBias"));
   FBF_TRY(ensure_workspace(h));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const fbfftconv_desc& d = h->d;

@@ -97,5 +97,8 @@ int peer_wait_probe(cudaStream_t stream);
 // Records `message` as the calling thread's last error (what fbfftconv_last_error
 // returns) and hands `code` back, for entry points that live outside api.cu.
 int report_error(int code, const char* message);
+// FBFFTCONV_OK when `ptr` is null or device (or managed) memory of `device`; otherwise records a
+// message naming `name` and returns FBFFTCONV_ERR_INVALID_ARGUMENT (or FBFFTCONV_ERR_CUDA).
+int validate_device_pointer(int device, const void* ptr, const char* name);
 
 }  // namespace fbfft

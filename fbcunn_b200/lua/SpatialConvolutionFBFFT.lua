@@ -17,7 +17,9 @@
      * the fields fbnn.SpatialConvolution reads and sets: printDebugLevel, cudnnDebug, success,
        autotuningPass, reportErrors, timeSteps (fbcunn/SpatialConvolutionFFT.lua:162-163, :259-268);
      * the second class name nn.SpatialConvolutionFBFFTGemm
-       (fbcunn/SpatialConvolutionFBFFTGemm.lua:18-66) over the same native path.
+       (fbcunn/SpatialConvolutionFBFFTGemm.lua:18-66) over the same native path;
+     * nn.SpatialConvolutionFFTTiled (fbcunn/SpatialConvolutionFFTTiled.lua:265-365) over the
+       library's tiled passes (fbfftconv_tiled_*), same constructor.
    Not kept: the class derives from nn.Module, not from the reference's nn.SpatialConvolutionFFT,
    so code that reaches into that base class's buffers, streams or FFTWrapper objects -- the
    reference's own SpatialConvolutionFFTTiled*.lua files do -- does not run on it.
@@ -46,6 +48,16 @@ int fbfftconv_update_grad_input(fbfftconv_handle* h, const float* grad_output, c
                                 float* grad_input, void* stream);
 int fbfftconv_acc_grad_parameters(fbfftconv_handle* h, const float* input, const float* grad_output,
                                   float* grad_weight, float* grad_bias, float scale, void* stream);
+typedef struct fbfftconv_tiled fbfftconv_tiled;
+int fbfftconv_tiled_create(const fbfftconv_desc* desc, int tile_h, int tile_w, fbfftconv_tiled** out);
+int fbfftconv_tiled_destroy(fbfftconv_tiled* t);
+fbfftconv_handle* fbfftconv_tiled_inner(fbfftconv_tiled* t);
+int fbfftconv_tiled_update_output(fbfftconv_tiled* t, const float* input, const float* weight, const float* bias,
+                                  float* output, void* stream);
+int fbfftconv_tiled_update_grad_input(fbfftconv_tiled* t, const float* grad_output, const float* weight,
+                                      float* grad_input, void* stream);
+int fbfftconv_tiled_acc_grad_parameters(fbfftconv_tiled* t, const float* input, const float* grad_output,
+                                        float* grad_weight, float* grad_bias, float scale, void* stream);
 int fbfftconv_comm_unique_id(void* id128);
 int fbfftconv_comm_init(fbfftconv_handle* h, const void* id128, int rank, int nranks);
 const char* fbfftconv_last_error(void);
@@ -256,4 +268,90 @@ local SpatialConvolutionFBFFTGemm, gemmParent =
 
 function SpatialConvolutionFBFFTGemm:__init(...)
    gemmParent.__init(self, ...)
+end
+
+-- nn.SpatialConvolutionFFTTiled(nInputPlane, nOutputPlane, kW, kH, dW, dH, padLeft, padUp,
+-- tileSizeW, tileSizeH, memoryReusePolicy, numCudaStreams), fbcunn/SpatialConvolutionFFTTiled.lua:265-365:
+-- the same three passes on tiles of the image (overlap-save), done by the library's tiled entry
+-- points; tile sizes default to 16 (:357-358).
+local SpatialConvolutionFFTTiled, tiledParent =
+   torch.class('nn.SpatialConvolutionFFTTiled', 'nn.SpatialConvolutionFBFFT')
+
+function SpatialConvolutionFFTTiled:__init(nInputPlane, nOutputPlane, kW, kH, dW, dH,
+                                           padLeft, padUp, tileSizeW, tileSizeH,
+                                           memoryReusePolicy, numCudaStreams)
+   assert(tileSizeW == nil or torch.type(tileSizeW) == 'number')
+   assert(tileSizeH == nil or torch.type(tileSizeH) == 'number')
+   tiledParent.__init(self, nInputPlane, nOutputPlane, kW, kH, dW, dH, padLeft, padUp,
+                      memoryReusePolicy, numCudaStreams)
+   self.tileSizeW = tileSizeW or 16
+   self.tileSizeH = tileSizeH or 16
+   assert(self.tileSizeH > self.kH - 1 and self.tileSizeW > self.kW - 1,
+          "tile size must exceed the kernel size minus one")
+end
+
+function SpatialConvolutionFFTTiled:prepareSizeAndBuffers(input)
+   assert(torch.type(input) == 'torch.CudaTensor', "CUDA support only!")
+   assert(input:dim() == 4, "2D convolutions on 4D tensors atm")
+   assert(input:isContiguous())
+   local flags = (self.accumulateGrads and FBFFTCONV_ACCUMULATE_GRADS or 0)
+      + (self.reuseInputs and FBFFTCONV_REUSE_INPUT or 0)
+      + (self.reuseOutputs and FBFFTCONV_REUSE_OUTPUT or 0)
+      + (self.reuseWeights and FBFFTCONV_REUSE_WEIGHT or 0)
+   local key = string.format('%d:%d:%d:%d:%d', cutorch.getDevice(),
+                             input:size(1), input:size(3), input:size(4), flags)
+   if self.handleKey ~= key then
+      self:cleanupBuffers()
+      local desc = ffi.new('fbfftconv_desc', {
+         input:size(1), self.nInputPlane, self.nOutputPlane,
+         input:size(3), input:size(4), self.kH, self.kW,
+         self.dH, self.dW, self.padUp, self.padLeft,
+         cutorch.getDevice() - 1,
+         flags})
+      local out = ffi.new('fbfftconv_tiled*[1]')
+      check(C.fbfftconv_tiled_create(desc, self.tileSizeH, self.tileSizeW, out))
+      self.tiled = ffi.gc(out[0], C.fbfftconv_tiled_destroy)
+      self.handle = C.fbfftconv_tiled_inner(self.tiled)   -- owned by the tiled handle
+      self.handleKey = key
+      if self.comm then
+         check(C.fbfftconv_comm_init(self.handle, self.comm.id, self.comm.rank, self.comm.nranks))
+      end
+   end
+end
+
+function SpatialConvolutionFFTTiled:updateOutputFFTImpl(input, reuseList, metaData)
+   self:prepareSizeAndBuffers(input)
+   local oH = input:size(3) + 2 * self.padUp - self.kH + 1
+   local oW = input:size(4) + 2 * self.padLeft - self.kW + 1
+   self.output = cudaResize(self.output, input:size(1), self.nOutputPlane, oH, oW)
+   local bias = nil
+   if not (metaData and metaData.skipBias) then bias = self.bias:data() end
+   check(C.fbfftconv_tiled_update_output(self.tiled, input:data(), self.weight:data(), bias,
+                                         self.output:data(), stream()))
+   return self.output
+end
+
+function SpatialConvolutionFFTTiled:updateGradInputFFTImpl(input, gradOutput, reuseList, metaData)
+   self:prepareSizeAndBuffers(input)
+   assert(gradOutput:isContiguous())
+   self.gradInput = cudaResize(self.gradInput, input:size())
+   check(C.fbfftconv_tiled_update_grad_input(self.tiled, gradOutput:data(), self.weight:data(),
+                                             self.gradInput:data(), stream()))
+   return self.gradInput
+end
+
+function SpatialConvolutionFFTTiled:accGradParametersFFTImpl(input, gradOutput, scale, reuseList, metaData)
+   self:prepareSizeAndBuffers(input)
+   assert(gradOutput:isContiguous())
+   local gradBias = nil
+   if not (metaData and metaData.skipBias) then gradBias = self.gradBias:data() end
+   check(C.fbfftconv_tiled_acc_grad_parameters(self.tiled, input:data(), gradOutput:data(),
+                                               self.gradWeight:data(), gradBias, scale or 1, stream()))
+end
+
+function SpatialConvolutionFFTTiled:cleanupBuffers()
+   self.handle = nil
+   self.tiled = nil       -- ffi.gc destroys the tiled handle and the untiled layer of the tiles with it
+   self.handleKey = nil
+   collectgarbage()
 end

@@ -254,10 +254,8 @@ class SpatialConvolutionFBFFT:
         uid, rank, nranks = self._comm
         capi.check(capi.lib().fbfftconv_comm_init(self._handle, ctypes.c_char_p(uid), rank, nranks))
 
-    def _prepare(self, input):
-        """prepareSizeAndBuffers: a native handle per (batch, image size)."""
-        B, _, iH, iW = input.shape
-        flags = (capi.ACCUMULATE_GRADS if self._accumulate else 0) | \
+    def _flags(self) -> int:
+        return (capi.ACCUMULATE_GRADS if self._accumulate else 0) | \
                 (capi.CONTRACT_SIMT if self._contraction == "simt" else 0) | \
                 (capi.BIN_MAJOR_ONLY if self._contraction == "bin_major" else 0) | \
                 (capi.ALLREDUCE_SPATIAL if self._allreduce == "spatial" else 0) | \
@@ -265,6 +263,11 @@ class SpatialConvolutionFBFFT:
                 (capi.REUSE_INPUT if memoryReuseInput in self.memoryReusePolicy else 0) | \
                 (capi.REUSE_OUTPUT if memoryReuseOutput in self.memoryReusePolicy else 0) | \
                 (capi.REUSE_WEIGHT if memoryReuseWeight in self.memoryReusePolicy else 0)
+
+    def _prepare(self, input):
+        """prepareSizeAndBuffers: a native handle per (batch, image size)."""
+        B, _, iH, iW = input.shape
+        flags = self._flags()
         key = (int(B), int(iH), int(iW), flags)
         if self._handle is not None and self._handle_key == key:
             return self._handle

@@ -6,23 +6,25 @@ disjoint tiles of (tileSize - k + 1) pixels, each of which depends on an input t
 tileSize pixels (overlap-save), so the transform size stays at tileSize whatever the image
 size -- which also lifts the 128-pixel limit of the untiled module.
 
-Here the tiles of one image are laid out as extra batch entries and go through the
-untiled native path in one call per pass:
+The work is the native library's (fbfftconv_tiled_* in include/fbfftconv.h): the tiles of one
+image become extra batch entries of one untiled pass,
 
     updateOutput        input tiles (overlapping)  -> output tiles (disjoint)
     updateGradInput     gradOutput tiles (disjoint) -> gradInput tiles, overlap-added
     accGradParameters   the sum over the batch inside the contraction is also the sum
                         over tiles, so gradWeight / gradBias come out complete
 
-Cutting and reassembling the tiles is data movement only and is done with torch copy
-kernels (unfold / fold); all arithmetic is the native library's.
+and cutting, assembling and the overlap-add are kernels of the library.  This class only
+owns the tensors and mirrors the reference's constructor and methods.
 """
 from __future__ import annotations
 
-import torch
-import torch.nn.functional as F
+import ctypes
 
-from .module import SpatialConvolutionFBFFT
+import torch
+
+from . import capi
+from .module import SpatialConvolutionFBFFT, _ptr, _stream
 
 
 class SpatialConvolutionFFTTiled(SpatialConvolutionFBFFT):
@@ -38,17 +40,10 @@ class SpatialConvolutionFFTTiled(SpatialConvolutionFBFFT):
         self.tileSizeW = int(tileSizeW or 16)
         assert self.tileSizeH > self.kH - 1 and self.tileSizeW > self.kW - 1, \
             "tile size must exceed the kernel size minus one"
-        # the tiles run through an unpadded module that shares this module's parameters
-        self._inner = SpatialConvolutionFBFFT(nInputPlane, nOutputPlane, kW, kH, 1, 1, 0, 0,
-                                              memoryReusePolicy, numCudaStreams, **kw)
-        self._share()
+        self._tiled = None
+        self._tiled_key = None
 
-    def _share(self):
-        inner = self._inner
-        inner.weight, inner.bias = self.weight, self.bias
-        inner.gradWeight, inner.gradBias = self.gradWeight, self.gradBias
-
-    # -- tiling geometry ---------------------------------------------------------------
+    # -- tiling geometry (what the native side computes; kept for callers that size buffers) --
     def _geometry(self, iH, iW):
         oH = iH + 2 * self.padUp - self.kH + 1
         oW = iW + 2 * self.padLeft - self.kW + 1
@@ -59,88 +54,74 @@ class SpatialConvolutionFFTTiled(SpatialConvolutionFBFFT):
         pH, pW = (nH - 1) * sH + tH, (nW - 1) * sW + tW      # padded input extent the tiles cover
         return oH, oW, tH, tW, sH, sW, nH, nW, pH, pW
 
-    def _input_tiles(self, input, geo):
-        """(B, P, iH, iW) -> (B * nH * nW, P, tH, tW), zero outside the image."""
-        oH, oW, tH, tW, sH, sW, nH, nW, pH, pW = geo
-        B, P, iH, iW = input.shape
-        padded = F.pad(input, (self.padLeft, pW - iW - self.padLeft, self.padUp, pH - iH - self.padUp))
-        t = padded.unfold(2, tH, sH).unfold(3, tW, sW)       # B, P, nH, nW, tH, tW
-        return t.permute(0, 2, 3, 1, 4, 5).reshape(B * nH * nW, P, tH, tW).contiguous()
-
-    def _output_tiles(self, grad_output, geo):
-        """(B, F, oH, oW) -> (B * nH * nW, F, sH, sW), zero outside the image."""
-        oH, oW, tH, tW, sH, sW, nH, nW, pH, pW = geo
-        B, Fo = grad_output.shape[:2]
-        padded = F.pad(grad_output, (0, nW * sW - oW, 0, nH * sH - oH))
-        t = padded.reshape(B, Fo, nH, sH, nW, sW).permute(0, 2, 4, 1, 3, 5)
-        return t.reshape(B * nH * nW, Fo, sH, sW).contiguous()
+    def _prepare_tiled(self, input):
+        B, _, iH, iW = input.shape
+        flags = self._flags()
+        key = (int(B), int(iH), int(iW), flags)
+        if self._tiled is not None and self._tiled_key == key:
+            return self._tiled
+        self.cleanupBuffers()
+        desc = capi.Desc(B, self.nInputPlane, self.nOutputPlane, iH, iW, self.kH, self.kW, self.dH, self.dW,
+                         self.padUp, self.padLeft,
+                         self.device.index if self.device.index is not None else torch.cuda.current_device(), flags)
+        t = ctypes.c_void_p()
+        capi.check(capi.lib().fbfftconv_tiled_create(ctypes.byref(desc), self.tileSizeH, self.tileSizeW,
+                                                     ctypes.byref(t)))
+        self._tiled, self._tiled_key = t, key
+        # the untiled layer of the tiles: communicator, profiling and status queries go to it
+        self._handle = ctypes.c_void_p(capi.lib().fbfftconv_tiled_inner(t))
+        self._handle_key = None
+        if self._comm is not None:
+            self._init_comm()
+        return t
 
     # -- passes ------------------------------------------------------------------------
     def updateOutput(self, input: torch.Tensor, skipBias: bool = False) -> torch.Tensor:
         self.timeSteps["updateOutput"] += 1
         self._check_input(input)
-        self._share()
-        geo = self._geometry(input.shape[2], input.shape[3])
-        oH, oW, tH, tW, sH, sW, nH, nW, pH, pW = geo
-        B = input.shape[0]
-        tiles = self._inner.updateOutput(self._input_tiles(input, geo), skipBias=True)
-        out = tiles.reshape(B, nH, nW, self.nOutputPlane, sH, sW).permute(0, 3, 1, 4, 2, 5)
-        out = out.reshape(B, self.nOutputPlane, nH * sH, nW * sW)[:, :, :oH, :oW]
-        # the bias goes on once, at the very end (fbcunn/SpatialConvolutionFFTTiled.lua:541-544)
-        self.output = out.contiguous() if skipBias else out + self.bias.view(1, -1, 1, 1)
+        t = self._prepare_tiled(input)
+        B, _, iH, iW = input.shape
+        oH, oW = self._geometry(iH, iW)[:2]
+        shape = (B, self.nOutputPlane, oH, oW)
+        if self.output is None or tuple(self.output.shape) != shape:
+            self.output = torch.empty(shape, dtype=torch.float32, device=self.device)
+        capi.check(capi.lib().fbfftconv_tiled_update_output(
+            t, _ptr(input), _ptr(self.weight), None if skipBias else _ptr(self.bias), _ptr(self.output),
+            _stream(self.device)))
         return self.output
 
     def updateGradInput(self, input: torch.Tensor, gradOutput: torch.Tensor) -> torch.Tensor:
         self.timeSteps["updateGradInput"] += 1
         self._check_input(input)
         self._check_grad_output(input, gradOutput)
-        self._share()
-        B, P, iH, iW = input.shape
-        geo = self._geometry(iH, iW)
-        oH, oW, tH, tW, sH, sW, nH, nW, pH, pW = geo
-        like = torch.empty((B * nH * nW, P, tH, tW), dtype=torch.float32, device=input.device)
-        gi = self._inner.updateGradInput(like, self._output_tiles(gradOutput, geo))   # B*nT, P, tH, tW
-        full = self._overlap_add(gi, B, P, geo)
-        self.gradInput = full[:, :, self.padUp:self.padUp + iH, self.padLeft:self.padLeft + iW].contiguous()
+        t = self._prepare_tiled(input)
+        if self.gradInput is None or self.gradInput.shape != input.shape:
+            self.gradInput = torch.empty_like(input)
+        capi.check(capi.lib().fbfftconv_tiled_update_grad_input(
+            t, _ptr(gradOutput), _ptr(self.weight), _ptr(self.gradInput), _stream(self.device)))
         return self.gradInput
-
-    @staticmethod
-    def _overlap_add(gi, B, P, geo):
-        """Sum of the gradInput tiles (B * nH * nW, P, tH, tW) at their places, steps (sH, sW)."""
-        oH, oW, tH, tW, sH, sW, nH, nW, pH, pW = geo
-        eh, ew = tH - sH, tW - sW                                 # rows / columns shared with the next tile
-        if eh > sH or ew > sW:                                    # a tile reaches beyond its neighbour
-            cols = gi.reshape(B, nH * nW, P * tH * tW).transpose(1, 2)
-            return F.fold(cols, (pH, pW), (tH, tW), stride=(sH, sW))
-        # a tile = its own block plus the strips it shares with the right / lower / diagonal
-        # neighbour: four strided adds instead of a scatter
-        full = gi.new_zeros((B, P, (nH + 1) * sH, (nW + 1) * sW))
-        blocks = full.unflatten(2, (nH + 1, sH)).unflatten(4, (nW + 1, sW))  # B, P, nH+1, sH, nW+1, sW (a view)
-        t = gi.reshape(B, nH, nW, P, tH, tW).permute(0, 3, 1, 4, 2, 5)       # B, P, nH, tH, nW, tW
-        blocks[:, :, :nH, :, :nW, :] = t[:, :, :, :sH, :, :sW]
-        if eh:
-            blocks[:, :, 1:, :eh, :nW, :] += t[:, :, :, sH:, :, :sW]
-        if ew:
-            blocks[:, :, :nH, :, 1:, :ew] += t[:, :, :, :sH, :, sW:]
-        if eh and ew:
-            blocks[:, :, 1:, :eh, 1:, :ew] += t[:, :, :, sH:, :, sW:]
-        return full
 
     def accGradParameters(self, input: torch.Tensor, gradOutput: torch.Tensor, scale=None,
                           skipBias: bool = False) -> None:
         self.timeSteps["accGradParameters"] += 1
+        scale = 1.0 if scale is None else float(scale)
         self._check_input(input)
         self._check_grad_output(input, gradOutput)
-        self._share()
-        geo = self._geometry(input.shape[2], input.shape[3])
-        self._inner.accGradParameters(self._input_tiles(input, geo), self._output_tiles(gradOutput, geo),
-                                      scale, skipBias=skipBias)
+        t = self._prepare_tiled(input)
+        capi.check(capi.lib().fbfftconv_tiled_acc_grad_parameters(
+            t, _ptr(input), _ptr(gradOutput), _ptr(self.gradWeight), None if skipBias else _ptr(self.gradBias),
+            ctypes.c_float(scale), _stream(self.device)))
 
     def cleanupBuffers(self):
-        super().cleanupBuffers()
-        inner = getattr(self, "_inner", None)
-        if inner is not None:
-            inner.cleanupBuffers()
+        if getattr(self, "_tiled", None) is not None:
+            capi.lib().fbfftconv_tiled_destroy(self._tiled)  # destroys the untiled layer of the tiles with it
+            self._tiled = None
+            self._tiled_key = None
+            self._handle = None
+            self._handle_key = None
 
     def attachCommunicator(self, unique_id: bytes, rank: int, nranks: int):
-        self._inner.attachCommunicator(unique_id, rank, nranks)
+        assert len(unique_id) == 128
+        self._comm = (bytes(unique_id), int(rank), int(nranks))
+        if self._tiled is not None:
+            self._init_comm()

@@ -71,11 +71,12 @@ def time_module(m, input, gradOutput, scale, inference_only, iters=3):
         stop.record()
         stop.synchronize()
         times[which] = start.elapsed_time(stop) / iters
+    # device memory the library allocated itself (torch does not see it)
     native = 0
-    for mod in (m, getattr(m, "_inner", None)):
-        h = getattr(mod, "_handle", None)
-        if h is not None:
-            native += int(capi.lib().fbfftconv_workspace_bytes(h))
+    if getattr(m, "_tiled", None) is not None:
+        native = int(capi.lib().fbfftconv_tiled_workspace_bytes(m._tiled))
+    elif getattr(m, "_handle", None) is not None:
+        native = int(capi.lib().fbfftconv_workspace_bytes(m._handle))
     return times, native + max(0, torch.cuda.memory_allocated() - before)
 
 
@@ -140,10 +141,8 @@ class SpatialConvolution:
 
     def _adopt(self):
         inst = self.bestModuleInst
-        for mod in (inst, getattr(inst, "_inner", None)):
-            if mod is not None:
-                mod.weight, mod.bias = self.weight, self.bias
-                mod.gradWeight, mod.gradBias = self.gradWeight, self.gradBias
+        inst.weight, inst.bias = self.weight, self.bias
+        inst.gradWeight, inst.gradBias = self.gradWeight, self.gradBias
 
     # -- nn.Module surface ----------------------------------------------------------------
     def updateOutput(self, input):

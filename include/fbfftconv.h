@@ -136,6 +136,34 @@ int fbfftconv_acc_grad_parameters(fbfftconv_handle* h, const float* input, const
                                   float* grad_weight, float* grad_bias, float scale,
                                   fbfftconv_stream stream);
 
+/* ---- the same passes on tiles of the image -----------------------------------
+ * Replaces nn.SpatialConvolutionFFTTiled (fbcunn/SpatialConvolutionFFTTiled.lua:265-365, :489-563,
+ * :601-683, :724-802): the output is cut into disjoint tiles of (tile - k + 1) pixels, each computed
+ * from an input tile of `tile` pixels (overlap-save), so the transform size follows the tile, not the
+ * image -- images beyond 128 pixels become possible, small kernels on large images transform less
+ * padding.  The tiles of an image are extra batch entries of one untiled pass (batch x tiles per image
+ * must not exceed 65535); cutting, assembling (with the bias, added once) and the overlap-add of
+ * updateGradInput are kernels of the library, and accGradParameters' sum over the batch is also the
+ * sum over tiles.  desc describes the whole layer (its flags apply to the untiled layer of the
+ * tiles); tile_h / tile_w are clipped to the padded image.  The tile buffers are allocated with
+ * cudaMalloc at the first pass.  fbfftconv_tiled_inner gives the untiled layer's handle (owned by the
+ * tiled one) for fbfftconv_comm_init, the profile and status queries. */
+typedef struct fbfftconv_tiled fbfftconv_tiled;
+int fbfftconv_tiled_create(const fbfftconv_desc* desc, int tile_h, int tile_w, fbfftconv_tiled** out);
+int fbfftconv_tiled_destroy(fbfftconv_tiled* t);
+fbfftconv_handle* fbfftconv_tiled_inner(fbfftconv_tiled* t);
+/* Device bytes the tiled passes need: the untiled layer's scratch plus the two tile buffers. */
+size_t fbfftconv_tiled_workspace_bytes(const fbfftconv_tiled* t);
+/* out = { input tile h, w; output tile (= step of the input tiles) h, w; tiles per image along h, w }
+ * (the geometry of fbcunn/SpatialConvolutionFFTTiled.lua:55-221 for disjoint output tiles). */
+int fbfftconv_tiled_geometry(const fbfftconv_tiled* t, int32_t out[6]);
+int fbfftconv_tiled_update_output(fbfftconv_tiled* t, const float* input, const float* weight, const float* bias,
+                                  float* output, fbfftconv_stream stream);
+int fbfftconv_tiled_update_grad_input(fbfftconv_tiled* t, const float* grad_output, const float* weight,
+                                      float* grad_input, fbfftconv_stream stream);
+int fbfftconv_tiled_acc_grad_parameters(fbfftconv_tiled* t, const float* input, const float* grad_output,
+                                        float* grad_weight, float* grad_bias, float scale, fbfftconv_stream stream);
+
 /* ---- the same passes with HOST buffers --------------------------------------
  * Copies the operands to the device, runs the pass and copies the result back on
  * `stream`, then waits for it.  Pinned host memory makes the copies asynchronous;

@@ -43,7 +43,8 @@ def test_blocks_balance():
 def _prototypes(text):
     """name -> list of parameter types with the parameter names dropped."""
     protos = {}
-    for ret, name, args in re.findall(r"\b(int|size_t|const char\s*\*)\s+(fbfftconv_[a-z0-9_]+)\s*\(([^)]*)\)\s*;", text):
+    for ret, name, args in re.findall(
+            r"\b(int|size_t|const char\s*\*|fbfftconv_handle\s*\*)\s+(fbfftconv_[a-z0-9_]+)\s*\(([^)]*)\)\s*;", text):
         types = []
         for a in [x.strip() for x in args.split(",")]:
             if a in ("void", ""):
@@ -93,6 +94,14 @@ def test_surface_of_the_reference_module():
     text = _lua_text()
     assert "torch.class('nn.SpatialConvolutionFBFFT'" in text
     assert "torch.class('nn.SpatialConvolutionFBFFTGemm', 'nn.SpatialConvolutionFBFFT')" in text
+    # the tiled class of the reference (fbcunn/SpatialConvolutionFFTTiled.lua:265-267) over the tiled entry points
+    assert "torch.class('nn.SpatialConvolutionFFTTiled', 'nn.SpatialConvolutionFBFFT')" in text
+    for method in ("__init", "updateOutputFFTImpl", "updateGradInputFFTImpl", "accGradParametersFFTImpl",
+                   "cleanupBuffers"):
+        assert re.search(r"function SpatialConvolutionFFTTiled:%s\(" % method, code), method
+    for call in ("fbfftconv_tiled_create", "fbfftconv_tiled_update_output", "fbfftconv_tiled_update_grad_input",
+                 "fbfftconv_tiled_acc_grad_parameters"):
+        assert "C." + call in code, call
     # skipBias must really switch the bias off: `x and nil or y` never does
     assert not re.search(r"and nil\)? or", code)
     assert code.count("metaData.skipBias") >= 2

@@ -51,7 +51,7 @@ def test_fastest_candidate_within_the_memory_limit_wins():
     m = SpatialConvolution(4, 4, 3, 3, 1, 1, 1, 1, 500, True, device="cpu", timer=timer)
     m._tune(x)
     assert m.bestLabel == "FFTTiled 16x16 reuse=none"          # forward time only: 2.0 is the best within the limit
-    assert m.bestModuleInst.weight is m.weight and m.bestModuleInst._inner.gradWeight is m.gradWeight
+    assert m.bestModuleInst.weight is m.weight and m.bestModuleInst.gradWeight is m.gradWeight
     with pytest.raises(ValueError):
         SpatialConvolution(4, 4, 3, 3, 2, 2, device="cpu")
 
