@@ -193,13 +193,13 @@ def step_bytes(L):
     return 4 * (B * P * iH * iW + B * F * oH * oW + F * P * kH * kW)
 
 
-def workload_config(name, L, gpus, allreduce="spectrum", reuse="none"):
+def workload_config(name, L, gpus, allreduce="spectrum", reuse="none", exchange="NCCL"):
     B, P, F, iH, iW, kH, kW, pH, pW, _ = L
     return {
         "workload": f"{name}: {B}x{P}x{iH}x{iW} input, {F} filters {kH}x{kW}, pad {pH}, FFT {fft_size(L)}; step = 3 passes",
         "global_batch": B,
         "parallelism": (f"batch/{gpus} ranks, gradWeight " + ("spectrum" if allreduce == "spectrum" else "(spatial)")
-                        + " NCCL-summed") if gpus > 1 else "single GPU",
+                        + f" summed over {exchange}") if gpus > 1 else "single GPU",
         "l2": "inputs > L2" if step_bytes(L) > (126 << 20) else "inputs fit L2 (warm); layers_step_ms after flush",
         "memory_reuse": reuse,
     }
@@ -468,6 +468,10 @@ def run_gpu_arm(args):
         raise SystemExit(f"tensor-core contraction reported device status {device_status}")
     ms_per_step = elapsed_ms / args.steps
     value = 3.0 * conv_flops(L) / (ms_per_step / 1e3) / 1e12
+    # who carried the weight-gradient sum: the library's kernels over peer memory (NVLink loads / stores), or NCCL
+    exchange = "peer memory" if world > 1 and run.m.peerExchangeStatus() == 1 else "NCCL"
+    if world > 1 and run.m.peerExchangeStatus() >= 100:
+        raise SystemExit(f"a bounded wait of the peer exchange gave up: status {run.m.peerExchangeStatus()}")
 
     kernels = kernel_table(L, local_b, prof, pk)
     top = max((k for k in kernels if k["kernel"] != "allreduce" and not k.get("overlapped")),
@@ -569,7 +573,7 @@ def run_gpu_arm(args):
 
     if rank == 0:
         detail = {"kernels": kernels, "layers": layers, "roofline": roofline, "e2e": e2e, "parity": parity,
-                  "config": workload_config(name, L, world, args.allreduce, args.reuse)}
+                  "config": workload_config(name, L, world, args.allreduce, args.reuse, exchange)}
         try:
             with open(args.detail_file, "w") as f:
                 json.dump(detail, f, indent=1)
@@ -581,7 +585,7 @@ def run_gpu_arm(args):
             "metric": METRIC, "value": sig(value, 5), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": sig(ms_per_step, 5), "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": workload_config(name, L, world, args.allreduce, args.reuse),
+            "config": workload_config(name, L, world, args.allreduce, args.reuse, exchange),
             "roofline": compact(roofline, ("bound", "kernel", "achieved", "peak", "unit", "frac", "traffic",
                                            "avg_launch_us", "peak_source")),
             "cpu_baseline": cpu,
