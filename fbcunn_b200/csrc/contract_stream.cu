@@ -182,7 +182,7 @@ cudaError_t launch_stream_expand(const float2* x, const float2* y, float2* z, in
   dim3 grid(bin_blocks, (U + TU - 1) / TU, (V + v_per_block - 1) / v_per_block);
   if (grid.y > 65535 || grid.z > 65535) return cudaErrorInvalidValue;
   const int smem = RING_STAGES * PMAX * THREADS * (int)sizeof(float4);
-  cudaError_t e = cudaFuncSetAttribute(stream_expand_kernel<TU>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(stream_expand_kernel<TU>), smem);
   if (e != cudaSuccess) return e;
   stream_expand_kernel<TU><<<grid, THREADS, smem, stream>>>(x, y, z, U, V, P, v_per_block, bins, alpha);
   count_launch();
@@ -211,7 +211,7 @@ cudaError_t launch_stream_reduce(const float2* x, const float2* y, float2* z, in
   if (grid.y > 65535) return cudaErrorInvalidValue;
   auto launch = [&](auto kernel) -> cudaError_t {
     const int smem = RING_STAGES * (PMAX + tu) * nt * (int)sizeof(float4);
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), smem);
     if (e != cudaSuccess) return e;
     kernel<<<grid, nt, smem, stream>>>(x, y, z, U, W, P, xs_u, xs_w, bins, alpha);
     return cudaSuccess;

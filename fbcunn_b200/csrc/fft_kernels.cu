@@ -9,10 +9,36 @@
 // single launch with no global scratch.
 #include <atomic>
 #include <cstdlib>
+#include <mutex>
+#include <vector>
 
 #include "kernels.h"
 
 namespace fbfft {
+
+// The opt-in to a kernel's dynamic shared memory is per device and function and only ever grows:
+// it is asked for when a launch needs more than any launch of that kernel on that device before.
+cudaError_t ensure_dynamic_smem(const void* kernel, int bytes) {
+  struct Entry {
+    const void* kernel;
+    int device, bytes;
+  };
+  static std::mutex mutex;
+  static std::vector<Entry> seen;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) dev = 0;
+  std::lock_guard<std::mutex> lock(mutex);
+  for (Entry& e : seen)
+    if (e.kernel == kernel && e.device == dev) {
+      if (e.bytes >= bytes) return cudaSuccess;
+      cudaError_t r = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+      if (r == cudaSuccess) e.bytes = bytes;
+      return r;
+    }
+  cudaError_t r = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (r == cudaSuccess) seen.push_back(Entry{kernel, dev, bytes});
+  return r;
+}
 
 namespace {
 
@@ -255,7 +281,7 @@ cudaError_t run_forward(const FftParams& p, cudaStream_t stream) {
       if (g.threads != block_threads<N, T>()) return cudaErrorInvalidConfiguration;
       kernel = fft2d_forward_kernel<N, T>;
     }
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, g.smem_bytes);
+    cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), g.smem_bytes);
     if (e != cudaSuccess) return e;
     dim3 grid((p.kc + T - 1) / T, p.n_rows);
     if constexpr (N > 32) grid = dim3(persistent_blocks((long long)grid.x * grid.y, g.smem_bytes), 1);
@@ -278,7 +304,7 @@ cudaError_t run_inverse(const FftParams& p, cudaStream_t stream) {
       if (g.threads != block_threads<N, T>()) return cudaErrorInvalidConfiguration;
       kernel = fft2d_inverse_kernel<N, T>;
     }
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, g.smem_bytes);
+    cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), g.smem_bytes);
     if (e != cudaSuccess) return e;
     dim3 grid((p.n_inner + T - 1) / T, p.n_rows);
     if constexpr (N > 32) grid = dim3(persistent_blocks((long long)grid.x * grid.y, g.smem_bytes), 1);
@@ -367,7 +393,7 @@ cudaError_t run_1d(bool inverse, const FftParams& p, cudaStream_t stream) {
   } else {
     const FftGeom g = inverse ? inverse_geom(N, T, p.h, p.w) : forward_geom(N, T, p.h, p.w, 0, p.off_x);
     void (*kernel)(FftParams, FftGeom) = inverse ? fft1d_inverse_kernel<N, T> : fft1d_forward_kernel<N, T>;
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, g.smem_bytes);
+    cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), g.smem_bytes);
     if (e != cudaSuccess) return e;
     kernel<<<(p.n_inner + T - 1) / T, g.threads, g.smem_bytes, stream>>>(p, g);
     count_launch();

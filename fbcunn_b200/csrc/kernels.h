@@ -15,6 +15,10 @@ uint64_t launch_count();
 // persistent kernels and the "does this launch fill the GPU" decisions are sized from it.
 int sm_count();
 
+// Opts `kernel` in to `bytes` of dynamic shared memory on the current device unless an earlier call
+// already did (the attribute is per device and function; asking on every launch costs a driver call).
+cudaError_t ensure_dynamic_smem(const void* kernel, int bytes);
+
 // Largest plane tile (planes per block) whose shared memory fits, preferring two
 // resident blocks per SM; 0 when even one plane does not fit.
 int pick_forward_tile(int N, int h, int w, int pad_u, int pad_l);
