@@ -87,6 +87,7 @@ _SIGNATURES = {
     "fbfftconv_tensor_core_wait_selftest": (c_int, [c_void_p]),
     "fbfftconv_peer_exchange_status": (c_int, [c_void_p, c_int]),
     "fbfftconv_peer_exchange_wait_selftest": (c_int, [c_void_p]),
+    "fbfftconv_exchange_plan": (c_int, [c_void_p, c_int, c_int, c_void_p]),
     "fbfftconv_update_output_bias": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "fbfftconv_acc_grad_parameters_bias": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p]),
     "fbfftconv_acc_grad_parameters_bias_noalloc": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p]),

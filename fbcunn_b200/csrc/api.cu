@@ -395,6 +395,8 @@ bool thin_contraction(int m, int n, int k) {
 // sizes of the stand-alone transforms (nn.FFTWrapper, test/test_FFTModule.lua:170-260); a convolution never
 // picks less than 8
 bool valid_fft_size(int n) { return n == 2 || n == 4 || n == 8 || n == 16 || n == 32 || n == 64 || n == 128; }
+// the 1-D stand-alone transforms also have the reference's largest 1-D size
+bool valid_fft1d_size(int n) { return valid_fft_size(n) || n == 256; }
 
 // What the reference's bindings check before they launch (THCudaTensor_checkGPU over all tensors,
 // src/fft/SpatialConvolutionCuFFTHost.cpp:33-66): every tensor lives in device memory of the
@@ -811,6 +813,67 @@ int fbfftconv_update_grad_input(fbfftconv_handle* h, const float* grad_output, c
   return FBFFTCONV_OK;
 }
 
+namespace {
+
+// How accGradParameters sums the weight gradient over `nranks` ranks, as `rank` sees it: arithmetic
+// on the handle's sizes only (no device), used by the pass and reported by fbfftconv_exchange_plan.
+struct ExchangePlan {
+  int mode;                          // FBFFTCONV_SUM_*
+  size_t spec_floats;                // the whole gradient spectrum
+  size_t chunk_floats, first_float;  // this rank's share of it (by filters / by bins)
+  size_t zero_before, zero_after;    // by bins: the other ranks' bins, cleared before the inverse transform
+  size_t n_weight;                   // gradWeight
+  size_t slice_floats, slice_first;  // by filters: this rank's filters inside gradWeight
+  size_t vec4;                       // float4s of [gradWeight | gradBias], the vector summed after the transform
+};
+
+ExchangePlan exchange_plan(const fbfftconv_handle* h, int rank, int nranks) {
+  const fbfftconv_desc& d = h->d;
+  const size_t F = d.n_output_plane, P = d.n_input_plane;
+  const bool pm = h->plane_major;
+  ExchangePlan x{};
+  x.spec_floats = (size_t)h->bins * F * (pm ? P : (size_t)pad4((int)P)) * 2;
+  x.n_weight = F * P * d.kernel_h * d.kernel_w;
+  x.vec4 = (x.n_weight + F + 3) / 4;
+  if (nranks < 1) {
+    x.mode = FBFFTCONV_SUM_NONE;
+  } else if (d.flags & FBFFTCONV_ALLREDUCE_SPATIAL) {
+    x.mode = FBFFTCONV_SUM_SPATIAL;
+  } else if (pm && F % nranks == 0) {
+    // plane-major spectra are contiguous per filter: every rank sums and inverts its own filters
+    x.mode = FBFFTCONV_SUM_SPECTRUM_BY_FILTERS;
+    x.chunk_floats = x.spec_floats / nranks;
+    x.first_float = (size_t)rank * x.chunk_floats;
+    x.slice_floats = x.n_weight / nranks;
+    x.slice_first = (size_t)rank * x.slice_floats;
+  } else if (!pm && nranks > 1 && h->bins % nranks == 0) {
+    // bin-major spectra are contiguous per bin: every rank sums a range of bins and inverts the
+    // spectrum that is zero outside it (the transform is linear in the bins)
+    x.mode = FBFFTCONV_SUM_SPECTRUM_BY_BINS;
+    x.chunk_floats = x.spec_floats / nranks;
+    x.first_float = (size_t)rank * x.chunk_floats;
+    x.zero_before = x.first_float;
+    x.zero_after = x.spec_floats - x.first_float - x.chunk_floats;
+  } else {
+    x.mode = FBFFTCONV_SUM_SPECTRUM_WHOLE;
+  }
+  return x;
+}
+
+}  // namespace
+
+int fbfftconv_exchange_plan(const fbfftconv_handle* h, int rank, int nranks, long long out[10]) {
+  if (!h || !out) return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "null argument");
+  if (nranks < 0 || (nranks > 0 && (rank < 0 || rank >= nranks)))
+    return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "rank %d of %d", rank, nranks);
+  const ExchangePlan x = exchange_plan(h, rank, nranks);
+  const long long v[10] = {x.mode, (long long)x.spec_floats, (long long)x.chunk_floats, (long long)x.first_float,
+                           (long long)x.zero_before, (long long)x.zero_after, (long long)x.n_weight,
+                           (long long)x.slice_floats, (long long)x.slice_first, (long long)x.vec4};
+  for (int i = 0; i < 10; ++i) out[i] = v[i];
+  return FBFFTCONV_OK;
+}
+
 int fbfftconv_acc_grad_parameters(fbfftconv_handle* h, const float* input, const float* grad_output,
                                   float* grad_weight, float* grad_bias, float scale,
                                   fbfftconv_stream stream) {
@@ -854,24 +917,20 @@ int fbfftconv_acc_grad_parameters(fbfftconv_handle* h, const float* input, const
   // Sums over peer memory replace the NCCL calls below wherever the exchange is a reduce-scatter plus a
   // small sum (and for the spatial sum); the same choice is made on every rank.
   const bool peer = h->comm && h->peer_ready;
-  const size_t vec4 = ((size_t)F * P * d.kernel_h * d.kernel_w + F + 3) / 4;  // float4s of [gradWeight | gradBias]
-  const bool spatial = h->comm && (d.flags & FBFFTCONV_ALLREDUCE_SPATIAL);
-  const size_t spec_floats = (size_t)h->bins * F * (pm ? P : pad4(P)) * 2;
-  const size_t n_weight = (size_t)F * P * d.kernel_h * d.kernel_w;
+  // The same arithmetic on every rank: which sum, and which share of it is this rank's.
+  ExchangePlan x = exchange_plan(h, h->comm ? h->rank : 0, h->comm ? h->nranks : 0);
+  // without peer memory the shares travel by NCCL calls this libnccl may not have
+  if (!peer && x.mode == FBFFTCONV_SUM_SPECTRUM_BY_FILTERS &&
+      !(api->ReduceScatter && api->AllGather && api->GroupStart && api->GroupEnd))
+    x.mode = FBFFTCONV_SUM_SPECTRUM_WHOLE;
+  if (!peer && x.mode == FBFFTCONV_SUM_SPECTRUM_BY_BINS && !api->ReduceScatter) x.mode = FBFFTCONV_SUM_SPECTRUM_WHOLE;
+  const size_t vec4 = x.vec4, spec_floats = x.spec_floats, n_weight = x.n_weight;
+  const bool spatial = x.mode == FBFFTCONV_SUM_SPATIAL;
+  const bool scatter = x.mode == FBFFTCONV_SUM_SPECTRUM_BY_FILTERS;
+  const bool scatter_bins = x.mode == FBFFTCONV_SUM_SPECTRUM_BY_BINS;
   // Across ranks the bias gradient travels behind whatever the weight gradient is summed
   // as: behind its spectrum, or behind the local spatial gradient.
   float* local_w = h->vec_in();
-  // Plane-major spectra are contiguous per filter, so the sum across ranks can be a reduce-scatter
-  // by filters (half the bytes of an all-reduce): every rank inverts its own filters and the
-  // spatial slices (a few hundred KB) are gathered.  Still the frequency-domain sum.
-  const bool scatter = h->comm && !spatial && pm && F % h->nranks == 0 && api->ReduceScatter && api->AllGather &&
-                       api->GroupStart && api->GroupEnd;
-  // Bin-major spectra are contiguous per bin: the sum across ranks is a reduce-scatter by bin
-  // range (half the bytes of an all-reduce), every rank inverts the spectrum that is zero outside
-  // its own bins (the transform is linear in the bins), and the spatial partial results -- a few
-  // MB -- are all-reduced.
-  const bool scatter_bins = h->comm && !spatial && !pm && h->nranks > 1 && h->bins % h->nranks == 0 &&
-                            api->ReduceScatter;
   float* bias_part =
       (spatial || scatter || scatter_bins) ? local_w + n_weight : reinterpret_cast<float*>(h->buf_w()) + spec_floats;
   // W'^[bin][f][p] = scale/N^2 sum_b conj(O'^[b][f]) I^[b][p]
@@ -899,12 +958,12 @@ int fbfftconv_acc_grad_parameters(fbfftconv_handle* h, const float* input, const
   }
   const size_t bias_floats = grad_bias ? (size_t)F : 0;
   if (scatter) {
-    const size_t chunk = spec_floats / h->nranks, slice = n_weight / h->nranks;
-    float* mine = reinterpret_cast<float*>(h->buf_w()) + (size_t)h->rank * chunk;
+    const size_t chunk = x.chunk_floats, slice = x.slice_floats;
+    float* mine = reinterpret_cast<float*>(h->buf_w()) + x.first_float;
     {
       StageTimer t(h, pass, FBFFTCONV_STAGE_ALLREDUCE, s);
       if (peer) {
-        FBF_CUDA(launch_peer_reduce(h->peers, h->peer_epoch, (size_t)h->rank * chunk / 4, chunk / 4, s));
+        FBF_CUDA(launch_peer_reduce(h->peers, h->peer_epoch, x.first_float / 4, chunk / 4, s));
         h->peer_epoch += 2;
         // this rank's filters will be the only non-zero part of the vector summed below
         FBF_CUDA(cudaMemsetAsync(local_w, 0, n_weight * sizeof(float), s));
@@ -915,7 +974,7 @@ int fbfftconv_acc_grad_parameters(fbfftconv_handle* h, const float* input, const
     }
     {
       StageTimer t(h, pass, FBFFTCONV_STAGE_IFFT, s);
-      FBF_CUDA(launch_inverse(inverse_params(reinterpret_cast<const float2*>(mine), local_w + (size_t)h->rank * slice,
+      FBF_CUDA(launch_inverse(inverse_params(reinterpret_cast<const float2*>(mine), local_w + x.slice_first,
                                              nullptr, F / h->nranks, P, d.kernel_h, d.kernel_w, 0, 0, 0, 2, h->N),
                               h->N, s));
     }
@@ -929,7 +988,7 @@ int fbfftconv_acc_grad_parameters(fbfftconv_handle* h, const float* input, const
       StageTimer t(h, pass, FBFFTCONV_STAGE_ALLREDUCE, s);
       ncclResult_t r = api->GroupStart();
       if (r == ncclSuccess)
-        r = api->AllGather(local_w + (size_t)h->rank * slice, local_w, slice, ncclFloat, h->comm, s);
+        r = api->AllGather(local_w + x.slice_first, local_w, slice, ncclFloat, h->comm, s);
       if (r == ncclSuccess && bias_floats)
         r = api->AllReduce(bias_part, bias_part, bias_floats, ncclFloat, ncclSum, h->comm, s);
       const ncclResult_t r2 = api->GroupEnd();
@@ -938,13 +997,13 @@ int fbfftconv_acc_grad_parameters(fbfftconv_handle* h, const float* input, const
       FBF_CUDA(launch_copy_or_add(local_w, grad_weight, (long long)n_weight, accumulate, s));
     }
   } else if (scatter_bins) {
-    const size_t chunk = spec_floats / h->nranks;
+    const size_t chunk = x.chunk_floats;
     float* all = reinterpret_cast<float*>(h->buf_w());
-    float* mine = all + (size_t)h->rank * chunk;
+    float* mine = all + x.first_float;
     {
       StageTimer t(h, pass, FBFFTCONV_STAGE_ALLREDUCE, s);
       if (peer) {
-        FBF_CUDA(launch_peer_reduce(h->peers, h->peer_epoch, (size_t)h->rank * chunk / 4, chunk / 4, s));
+        FBF_CUDA(launch_peer_reduce(h->peers, h->peer_epoch, x.first_float / 4, chunk / 4, s));
         h->peer_epoch += 2;
       } else {
         ncclResult_t r = api->ReduceScatter(all, mine, chunk, ncclFloat, ncclSum, h->comm, s);
@@ -952,9 +1011,8 @@ int fbfftconv_acc_grad_parameters(fbfftconv_handle* h, const float* input, const
       }
     }
     // the other ranks' bins still hold this rank's partial products
-    if (h->rank > 0) FBF_CUDA(cudaMemsetAsync(all, 0, (size_t)h->rank * chunk * sizeof(float), s));
-    if (h->rank + 1 < h->nranks)
-      FBF_CUDA(cudaMemsetAsync(mine + chunk, 0, (size_t)(h->nranks - 1 - h->rank) * chunk * sizeof(float), s));
+    if (x.zero_before) FBF_CUDA(cudaMemsetAsync(all, 0, x.zero_before * sizeof(float), s));
+    if (x.zero_after) FBF_CUDA(cudaMemsetAsync(mine + chunk, 0, x.zero_after * sizeof(float), s));
     {
       StageTimer t(h, pass, FBFFTCONV_STAGE_IFFT, s);
       FBF_CUDA(launch_inverse(inverse_params(h->buf_w(), local_w, nullptr, F, P, d.kernel_h, d.kernel_w, 0, 0, 0, 0,
@@ -973,7 +1031,7 @@ int fbfftconv_acc_grad_parameters(fbfftconv_handle* h, const float* input, const
         FBF_CUDA(launch_copy_or_add(local_w, grad_weight, (long long)n_weight, accumulate, s));
       }
     }
-  } else if (h->comm && !spatial) {
+  } else if (x.mode == FBFFTCONV_SUM_SPECTRUM_WHOLE) {
     StageTimer t(h, pass, FBFFTCONV_STAGE_ALLREDUCE, s);
     ncclResult_t r = api->AllReduce(h->buf_w(), h->buf_w(), spec_floats + bias_floats, ncclFloat, ncclSum, h->comm, s);
     if (r != ncclSuccess) return nccl_fail(api, r, "ncclAllReduce(gradWeight spectrum)");
@@ -1385,7 +1443,7 @@ int fbfftconv_ifft2d_reference_layout(const void* frequency, float* real, void* 
 int fbfftconv_fft1d(const float* real, void* spectrum, long long rows, int n, int fft_size,
                     int pad_left, fbfftconv_stream stream) {
   if (!real || !spectrum) return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "null argument");
-  if (!valid_fft_size(fft_size)) return fail(FBFFTCONV_ERR_UNSUPPORTED_SIZE, "transform size %d not in {2,4,8,16,32,64,128}", fft_size);
+  if (!valid_fft1d_size(fft_size)) return fail(FBFFTCONV_ERR_UNSUPPORTED_SIZE, "transform size %d not in {2,4,8,16,32,64,128,256}", fft_size);
   if (rows <= 0 || n <= 0 || pad_left < 0 || n + pad_left > fft_size)
     return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "row of %d floats at %d does not fit %d", n, pad_left, fft_size);
   FBF_CUDA(launch_fft1d(false, real, nullptr, static_cast<float2*>(spectrum), rows, n, fft_size, pad_left,
@@ -1396,7 +1454,7 @@ int fbfftconv_fft1d(const float* real, void* spectrum, long long rows, int n, in
 int fbfftconv_ifft1d(const void* spectrum, float* real, long long rows, int n, int fft_size,
                      int offset, fbfftconv_stream stream) {
   if (!real || !spectrum) return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "null argument");
-  if (!valid_fft_size(fft_size)) return fail(FBFFTCONV_ERR_UNSUPPORTED_SIZE, "transform size %d not in {2,4,8,16,32,64,128}", fft_size);
+  if (!valid_fft1d_size(fft_size)) return fail(FBFFTCONV_ERR_UNSUPPORTED_SIZE, "transform size %d not in {2,4,8,16,32,64,128,256}", fft_size);
   if (rows <= 0 || n <= 0 || offset < 0 || n + offset > fft_size)
     return fail(FBFFTCONV_ERR_INVALID_ARGUMENT, "window of %d floats at %d does not fit %d", n, offset, fft_size);
   FBF_CUDA(launch_fft1d(true, nullptr, real, static_cast<float2*>(const_cast<void*>(spectrum)), rows, n, fft_size,

@@ -418,6 +418,7 @@ cudaError_t dispatch_1d_tile(bool inverse, const FftParams& p, int T, cudaStream
 // Rows [0, rows) of `n` floats each, transform size N: full blocks of N rows, then the rest.
 cudaError_t launch_fft1d(bool inverse, const float* real_in, float* real_out, float2* spec, long long rows, int n,
                          int N, int offset, cudaStream_t stream) {
+  if (N == 256) return launch_fft1d_256(inverse, real_in, real_out, spec, rows, n, offset, stream);
   const int KX = N / 2 + 1;
   for (int part = 0; part < 2; ++part) {
     const long long first = part == 0 ? 0 : rows / N * N;

@@ -56,7 +56,8 @@ __device__ __forceinline__ bool peer_wait(const PeerTable& t, unsigned epoch) {
     unsigned spins = 0;
     // epochs only grow; the signed difference tolerates the 32-bit wrap
     while ((int)(ld_acquire_sys(slot) - epoch) < 0) {
-      __nanosleep(kPeerSleepNs);
+      // ranks of a running job arrive within microseconds of one another: poll fast at first
+      __nanosleep(spins < 256 ? 64 : kPeerSleepNs);
       if (++spins > (t.spin_limit ? t.spin_limit : kPeerSpinLimit)) {
         ok = false;
         atomicCAS(&g_peer_error, 0, 1 + (int)threadIdx.x);
@@ -86,52 +87,66 @@ __device__ __forceinline__ void peer_end_barrier(const PeerTable& t, unsigned ep
   if (ok) peer_wait(t, epoch);  // after a time-out the peers are told, not waited for again
 }
 
+// Sum over ranks, in rank order, of element i of every rank's block.  All NR loads are issued
+// before the first add: a load over NVLink takes microseconds, and what keeps the links busy is the
+// number of loads in flight, not the number of threads.
+template <int NR>
+__device__ __forceinline__ float4 peer_sum(char* const (&block)[kMaxPeers], size_t i) {
+  float4 v[NR];
+#pragma unroll
+  for (int r = 0; r < NR; ++r) v[r] = ld_peer(reinterpret_cast<const float4*>(block[r]) + i);
+  float4 acc = v[0];
+#pragma unroll
+  for (int r = 1; r < NR; ++r) {
+    acc.x += v[r].x;
+    acc.y += v[r].y;
+    acc.z += v[r].z;
+    acc.w += v[r].w;
+  }
+  return acc;
+}
+
 // In place, on this rank's share [first4, first4 + count4) (units of float4) of the spectrum
 // block every rank holds (t.spec): share = sum over ranks.  Barrier before (every rank has
 // produced its block) and after (every rank has read what it needs, so the blocks may be
-// overwritten).
+// overwritten).  NR = t.nranks.
+template <int NR>
 __global__ void __launch_bounds__(256)
 peer_reduce_kernel(const __grid_constant__ PeerTable t, unsigned epoch, size_t first4, size_t count4) {
   if (blockIdx.x == 0) peer_signal(t, epoch);
   const bool ok = peer_wait(t, epoch);
   if (ok) {
     float4* mine = reinterpret_cast<float4*>(t.spec[t.rank]) + first4;
-    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < count4; i += (size_t)gridDim.x * blockDim.x) {
-      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int r = 0; r < t.nranks; ++r) {
-        const float4 v = ld_peer(reinterpret_cast<const float4*>(t.spec[r]) + first4 + i);
-        acc.x += v.x;
-        acc.y += v.y;
-        acc.z += v.z;
-        acc.w += v.w;
-      }
-      mine[i] = acc;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+    // two elements per round while both exist: 2 * NR loads in flight per thread
+    for (; i + stride < count4; i += 2 * stride) {
+      const float4 a = peer_sum<NR>(t.spec, first4 + i);
+      const float4 b = peer_sum<NR>(t.spec, first4 + i + stride);
+      mine[i] = a;
+      mine[i + stride] = b;
     }
+    if (i < count4) mine[i] = peer_sum<NR>(t.spec, first4 + i);
   }
   peer_end_barrier(t, epoch + 1, t.counter, ok);
 }
 
 // out[i] = sum over ranks of in[i] for all i < n4 (float4 units), on every rank: this rank sums
 // its share of t.vec_in and stores it into every rank's t.vec_out.  Barrier before (inputs
-// complete, output blocks free) and after (all shares have landed here).
+// complete, output blocks free) and after (all shares have landed here).  NR = t.nranks.
+template <int NR>
 __global__ void __launch_bounds__(256)
 peer_allreduce_kernel(const __grid_constant__ PeerTable t, unsigned epoch, size_t n4) {
   if (blockIdx.x == 0) peer_signal(t, epoch);
   const bool ok = peer_wait(t, epoch);
   if (ok) {
-    const size_t per = (n4 + t.nranks - 1) / t.nranks;
+    const size_t per = (n4 + NR - 1) / NR;
     const size_t first = per * t.rank;
     const size_t last = first + per < n4 ? first + per : n4;
     for (size_t i = first + blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < last; i += (size_t)gridDim.x * blockDim.x) {
-      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int r = 0; r < t.nranks; ++r) {
-        const float4 v = ld_peer(reinterpret_cast<const float4*>(t.vec_in[r]) + i);
-        acc.x += v.x;
-        acc.y += v.y;
-        acc.z += v.z;
-        acc.w += v.w;
-      }
-      for (int r = 0; r < t.nranks; ++r) reinterpret_cast<float4*>(t.vec_out[r])[i] = acc;
+      const float4 acc = peer_sum<NR>(t.vec_in, i);
+#pragma unroll
+      for (int r = 0; r < NR; ++r) reinterpret_cast<float4*>(t.vec_out[r])[i] = acc;
     }
   }
   peer_end_barrier(t, epoch + 1, t.counter, ok);
@@ -175,7 +190,13 @@ cudaError_t launch_peer_reduce(const PeerTable& t, unsigned epoch, size_t first4
   const size_t want = (count4 + 255) / 256;
   const size_t cap = (size_t)sm_count() * 4;
   const int blocks = (int)(want < 1 ? 1 : want < cap ? want : cap);
-  peer_reduce_kernel<<<blocks, 256, 0, stream>>>(t, epoch, first4, count4);
+  switch (t.nranks) {
+#define FBF_PEER_CASE(NR) \
+  case NR: peer_reduce_kernel<NR><<<blocks, 256, 0, stream>>>(t, epoch, first4, count4); break;
+    FBF_PEER_CASE(1) FBF_PEER_CASE(2) FBF_PEER_CASE(3) FBF_PEER_CASE(4)
+    FBF_PEER_CASE(5) FBF_PEER_CASE(6) FBF_PEER_CASE(7) FBF_PEER_CASE(8)
+#undef FBF_PEER_CASE
+  }
   count_launch();
   return cudaGetLastError();
 }
@@ -186,7 +207,13 @@ cudaError_t launch_peer_allreduce(const PeerTable& t, unsigned epoch, size_t n4,
   const size_t want = (per + 255) / 256;
   const size_t cap = (size_t)sm_count() * 2;
   const int blocks = (int)(want < 1 ? 1 : want < cap ? want : cap);
-  peer_allreduce_kernel<<<blocks, 256, 0, stream>>>(t, epoch, n4);
+  switch (t.nranks) {
+#define FBF_PEER_CASE(NR) \
+  case NR: peer_allreduce_kernel<NR><<<blocks, 256, 0, stream>>>(t, epoch, n4); break;
+    FBF_PEER_CASE(1) FBF_PEER_CASE(2) FBF_PEER_CASE(3) FBF_PEER_CASE(4)
+    FBF_PEER_CASE(5) FBF_PEER_CASE(6) FBF_PEER_CASE(7) FBF_PEER_CASE(8)
+#undef FBF_PEER_CASE
+  }
   count_launch();
   return cudaGetLastError();
 }

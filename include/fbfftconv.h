@@ -236,8 +236,9 @@ int fbfftconv_ifft2d_reference_layout(const void* frequency, float* real, void* 
  * contiguous rows of n floats, each placed at `pad_left` of a zero line of fft_size, ->
  * spectrum[row][k], k in [0, fft_size/2], complex fp32: the reference's (batch, N/2+1, 2)
  * tensor.  The inverse is un-normalised and keeps columns [offset, offset + n).
- * fft_size in {2, 4, 8, 16, 32, 64, 128} (so are the 2-D stand-alone transforms; a convolution
- * handle never picks less than 8). */
+ * fft_size in {2, 4, 8, 16, 32, 64, 128, 256}: 256 is the reference's largest 1-D size
+ * (test/test_FFTModule.lua:170-260) and exists for these two calls only; the 2-D stand-alone
+ * transforms take 2 ... 128, and a convolution handle never picks less than 8. */
 int fbfftconv_fft1d(const float* real, void* spectrum, long long rows, int n, int fft_size,
                     int pad_left, fbfftconv_stream stream);
 int fbfftconv_ifft1d(const void* spectrum, float* real, long long rows, int n, int fft_size,
@@ -324,6 +325,24 @@ int fbfftconv_peer_exchange_status(fbfftconv_handle* h, int reset);
 /* Self-test of that give-up path without a second rank: one block waits for a flag nothing sets,
  * with a limit of a few polls.  FBFFTCONV_OK when the wait gave up as designed. */
 int fbfftconv_peer_exchange_wait_selftest(fbfftconv_stream stream);
+/* Which sum accGradParameters would use over `nranks` ranks and which share of it is `rank`'s:
+ * arithmetic on the handle's sizes only (no device, no communicator needed; nranks = 0: no
+ * communicator).  out[0] = one of the FBFFTCONV_SUM_* below; [1] floats of the whole gradient
+ * spectrum; [2], [3] floats and first float of this rank's share of it (BY_FILTERS, BY_BINS);
+ * [4], [5] floats before / after the share that are cleared before the inverse transform (BY_BINS);
+ * [6] floats of gradWeight; [7], [8] floats and first float of this rank's filters in gradWeight
+ * (BY_FILTERS); [9] 16-byte units of the vector [gradWeight | gradBias] that is summed after the
+ * transform.  The shares of all ranks tile the spectrum, and every share starts on and spans whole
+ * 16-byte units.  The layer falls back from a share-wise sum to SPECTRUM_WHOLE when the ranks do
+ * not divide the filters (plane-major layers) or the bins (bin-major layers). */
+enum {
+  FBFFTCONV_SUM_NONE = 0,                /* one process: nothing to sum */
+  FBFFTCONV_SUM_SPECTRUM_BY_FILTERS = 1, /* reduce-scatter of the spectrum by filters, inverse of the own filters, gather */
+  FBFFTCONV_SUM_SPECTRUM_BY_BINS = 2,    /* reduce-scatter by bin range, inverse of the own bins, sum of the partial results */
+  FBFFTCONV_SUM_SPECTRUM_WHOLE = 3,      /* one all-reduce of the whole spectrum */
+  FBFFTCONV_SUM_SPATIAL = 4              /* FBFFTCONV_ALLREDUCE_SPATIAL: all-reduce of gradWeight after the transform */
+};
+int fbfftconv_exchange_plan(const fbfftconv_handle* h, int rank, int nranks, long long out[10]);
 
 /* ---- per-kernel timing ---------------------------------------------------------
  * With profiling enabled every kernel (and collective) a pass enqueues is bracketed

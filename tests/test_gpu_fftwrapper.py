@@ -22,7 +22,8 @@ def _complex(t):
 SIZES = [2, 4, 8, 16, 32, 64, 128]
 
 
-@pytest.mark.parametrize("n", SIZES)
+# 256 points exist for the 1-D transform only, as in the reference's list
+@pytest.mark.parametrize("n", SIZES + [256])
 @pytest.mark.parametrize("batch", [(1,), (4,), (3, 5), (127,), (437,), (1000,)])
 def test_1d(n, batch):
     rng = np.random.default_rng(n + len(batch))
@@ -38,8 +39,8 @@ def test_1d(n, batch):
     assert np.abs(back.cpu().numpy() / n - x).max() <= TOL * n * np.abs(x).max()
 
 
-def test_1d_short_rows_are_zero_padded():
-    n, rows, width, pad = 32, 70, 20, 5
+@pytest.mark.parametrize("n,rows,width,pad", [(32, 70, 20, 5), (256, 33, 200, 17), (256, 64, 129, 127)])
+def test_1d_short_rows_are_zero_padded(n, rows, width, pad):
     rng = np.random.default_rng(1)
     x = rng.standard_normal((rows, width)).astype(np.float32)
     freq = torch.empty((rows, n // 2 + 1, 2), device="cuda")
