@@ -7,6 +7,7 @@ that it travels with the source tree; nothing is installed into site-packages.
 """
 from __future__ import annotations
 
+import fcntl
 import hashlib
 import os
 import subprocess
@@ -47,18 +48,41 @@ def _digest() -> str:
     return h.hexdigest()
 
 
+def _up_to_date(digest: str) -> bool:
+    stamp = LIB + ".stamp"
+    if not (os.path.exists(LIB) and os.path.exists(stamp)):
+        return False
+    with open(stamp) as f:
+        return f.read().strip() == digest
+
+
 def build(force: bool = False, verbose: bool = False) -> str:
     """Rebuilds when the sources' content hash differs from the one the library was
-    built from (file times do not survive a copy of the tree)."""
-    stamp = LIB + ".stamp"
+    built from (file times do not survive a copy of the tree).  Safe to call from
+    several processes at once (the ranks of a multi-GPU job): one of them builds
+    under a file lock, the others wait and find the library up to date; the library
+    appears under its name only when it is complete."""
     digest = _digest()
-    if not force and os.path.exists(LIB) and os.path.exists(stamp):
-        with open(stamp) as f:
-            if f.read().strip() == digest:
-                return LIB
+    if not force and _up_to_date(digest):
+        return LIB
     os.makedirs(OBJ, exist_ok=True)
+    with open(os.path.join(OBJ, ".lock"), "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not force and _up_to_date(digest):
+                return LIB  # another process built it while this one waited
+            _build_locked(digest, verbose)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+    return LIB
+
+
+def _build_locked(digest: str, verbose: bool) -> None:
+    stamp = LIB + ".stamp"
     nvcc = _nvcc()
     extra = ["-Xptxas", "-v"] if verbose else []
+    if os.path.exists(stamp):
+        os.remove(stamp)  # no stamp while objects and library are in flux
 
     def compile_one(src):
         obj = os.path.join(OBJ, src.replace(".cu", ".o"))
@@ -72,13 +96,15 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
     with ThreadPoolExecutor(max_workers=4) as ex:
         objs = list(ex.map(compile_one, SOURCES))
-    cmd = [nvcc, "-shared", "-o", LIB, *objs, "-gencode", "arch=compute_100a,code=sm_100a", "-ldl"]
+    tmp = os.path.join(OBJ, "libfbfftconv.so.tmp")
+    cmd = [nvcc, "-shared", "-o", tmp, *objs, "-gencode", "arch=compute_100a,code=sm_100a", "-ldl"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
-    with open(stamp, "w") as f:
+    os.replace(tmp, LIB)
+    with open(stamp + ".tmp", "w") as f:
         f.write(digest)
-    return LIB
+    os.replace(stamp + ".tmp", stamp)
 
 
 if __name__ == "__main__":
