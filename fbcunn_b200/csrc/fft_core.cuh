@@ -249,7 +249,7 @@ struct FftGeom {
 };
 
 static inline bool cooperative(int N) { return N > 32; }
-#define FBF_COOP_THREADS 256  // more threads per block (384, 512) measured slower
+#define FBF_COOP_THREADS 256  // measured slower: 288 (whole rounds in the column phases, but a 96-register cap), 384, 512
 static_assert(FBF_COOP_THREADS % 32 == 0, "whole warps, and a multiple of every N2");
 static inline int coop_threads() { return FBF_COOP_THREADS; }
 
