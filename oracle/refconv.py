@@ -50,7 +50,14 @@ class Shape:
         return _CShape(self.B, self.P, self.F, self.iH, self.iW, self.kH, self.kW, self.padH, self.padW)
 
 
-_REFERENCE_SRC = "/root/reference/test/ReferenceConvolutions.cpp"
+def _reference_root() -> str:
+    """Where the reference checkout lies: FBCUNN_REFERENCE_ROOT, else a directory `reference`
+    beside this repository; '' when there is none (the prebuilt _ref/ library is then used)."""
+    for cand in (os.environ.get("FBCUNN_REFERENCE_ROOT", ""),
+                 os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")):
+        if cand and os.path.exists(os.path.join(cand, "test", "ReferenceConvolutions.cpp")):
+            return cand
+    return ""
 
 
 def _stale(lib: str, sources) -> str:
@@ -78,13 +85,15 @@ def build(force: bool = False) -> None:
         subprocess.check_call(["make", "-s", "-B", "-C", _HERE, os.path.join(_HERE, "liboracle.so")])
         with open(_LIB + ".stamp", "w") as f:
             f.write(digest or _stale(_LIB + ".none", [os.path.join(_HERE, "refconv.c"), os.path.join(_HERE, "Makefile")]))
-    if os.path.exists(_REFERENCE_SRC):
+    root = _reference_root()
+    if root:
+        reference_src = os.path.join(root, "test", "ReferenceConvolutions.cpp")
         shim = [os.path.join(_HERE, "shim", d, f) for d, f in
                 (("thpp", "Tensor.h"), ("thpp", "Storage.h"), ("folly", "Optional.h"), ("glog", "logging.h"))]
-        srcs = [os.path.join(_HERE, "ref_bridge.cpp"), _REFERENCE_SRC] + shim
+        srcs = [os.path.join(_HERE, "ref_bridge.cpp"), reference_src] + shim
         digest = _stale(_REF, srcs)
         if force or digest:
-            subprocess.check_call(["make", "-s", "-C", _HERE, "ref"])
+            subprocess.check_call(["make", "-s", "-C", _HERE, "ref", "REFERENCE_ROOT=" + root])
             with open(_REF + ".stamp", "w") as f:
                 f.write(digest or _stale(_REF + ".none", srcs))
 
