@@ -301,7 +301,8 @@ int fbfftconv_acc_grad_parameters_bias_noalloc(const float* grad_output, float* 
  * fbfftconv_comm_init.  Handles that name the same id share one communicator; it stays
  * alive (an id cannot be used twice) until fbfftconv_comm_shutdown, which destroys every
  * communicator no handle is attached to.  fbfftconv_comm_destroy detaches one handle.
- * libnccl is loaded at run time on the first call.
+ * libnccl is loaded at run time on the first call: the copy the process already holds, else
+ * libnccl.so.2; FBFFTCONV_NCCL_LIB in the environment names another file.
  *
  * How the weight gradient is summed.  Up to 8 ranks (the GPUs of one NVSwitch box) whose scratch the
  * library allocated itself map one another's scratch (CUDA IPC) at the first accGradParameters -- a
