@@ -18,7 +18,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libfbfftconv.so")
-SOURCES = ["fft_kernels.cu", "contract_simt.cu", "contract_tc.cu", "contract_stream.cu", "bias.cu", "peer.cu", "tiled.cu", "fft1d_256.cu", "api.cu"]
+SOURCES = ["fft_kernels.cu", "contract_simt.cu", "contract_tc.cu", "contract_stream.cu", "bias.cu", "peer.cu", "tiled.cu", "fft1d_lines.cu", "api.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",

@@ -909,7 +909,7 @@ struct CoopInverse {
 };
 
 // ===========================================================================
-// Batched 1-D transforms: the row half of the 2-D kernels.  A "plane" is a block of up to N
+// Batched 1-D transforms up to 32 points: the row half of the 2-D kernels.  A "plane" is a block of up to N
 // consecutive rows (p.h of them, p.w floats each); after the row phases the column buffer holds
 // the half spectrum of every row, and it is written out / read in as it is:
 //     spectrum1d[global row][k],  k in [0, N/2],  global row = inner * p.h + y.
@@ -919,13 +919,10 @@ template <int N, int T>
 struct Rows1D {
   static constexpr int KX = N / 2 + 1;
 
-  // element (y, t, k) of the column buffer, in either kernel family's layout
+  // element (y, t, k) of the column buffer
   static FBF_HD int mid_index(int y, int t, int k) {
-    if constexpr (N <= 32) {
-      return y * TileLayout<N, T>::PITCH2 + k * T + t;
-    } else {
-      return y * CoopLayout<N, T>::PITCH2 + t * KX + k;
-    }
+    static_assert(N <= 32, "the 1-D transforms above 32 points have kernels of their own");
+    return y * TileLayout<N, T>::PITCH2 + k * T + t;
   }
 
   static FBF_HD void store_spectrum(const FftParams& p, const FftGeom& g, const char* smem, int tid,

@@ -177,68 +177,40 @@ fft2d_inverse_coop_kernel(const __grid_constant__ FftParams p, const __grid_cons
   }
 }
 
-// ---- batched 1-D transforms: the row phases only ------------------------------------------
+// ---- batched 1-D transforms up to 32 points: the row phases of the thread-per-line kernels (larger
+// ---- sizes have kernels of their own, fft1d_lines.cu)
 template <int N, int T>
-__global__ void __launch_bounds__(N <= 32 ? block_threads<N, T>() : FBF_COOP_THREADS)
+__global__ void __launch_bounds__(block_threads<N, T>())
 fft1d_forward_kernel(const __grid_constant__ FftParams p, const __grid_constant__ FftGeom g) {
+  static_assert(N <= 32, "thread-per-line sizes");
   extern __shared__ __align__(16) char smem[];
   const int tid = threadIdx.x, nth = blockDim.x;
   const int inner0 = blockIdx.x * T;
-  if constexpr (N <= 32) {
-    Forward<N, T>::load(p, g, smem, tid, nth, 0, inner0);
-    __syncthreads();
-    LineRegs<N> regs;
-    Forward<N, T>::row_fetch(p, g, smem, tid, 0, inner0, regs);
-    __syncthreads();
-    Forward<N, T>::row_pass(g, smem, tid, regs);
-  } else {
-    constexpr int N1 = CoopForward<N, T>::N1, N2 = CoopForward<N, T>::N2;
-    for (int line0 = 0; line0 < g.lines1; line0 += g.chunk) {
-      const int nl = min(g.chunk, g.lines1 - line0);
-      CoopForward<N, T>::row_step1(p, g, smem, tid, nth, 0, inner0, line0, nl);
-      __syncthreads();
-      const int items = nl * N1;
-      for (int base = 0; base < items; base += nth) {
-        float2 u[N2], mirror_odd[N2 / 2];
-        const bool active = CoopForward<N, T>::row_step2_fft(g, smem, base + tid, nl, u);
-#pragma unroll
-        for (int i = 0; i < N2 / 2; ++i) {
-          mirror_odd[i].x = __shfl_xor_sync(0xffffffffu, u[2 * i + 1].x, 1);
-          mirror_odd[i].y = __shfl_xor_sync(0xffffffffu, u[2 * i + 1].y, 1);
-        }
-        if (active) CoopForward<N, T>::row_step2_split(g, smem, base + tid, line0, u, mirror_odd);
-      }
-      __syncthreads();
-    }
-  }
+  Forward<N, T>::load(p, g, smem, tid, nth, 0, inner0);
+  __syncthreads();
+  LineRegs<N> regs;
+  Forward<N, T>::row_fetch(p, g, smem, tid, 0, inner0, regs);
+  __syncthreads();
+  Forward<N, T>::row_pass(g, smem, tid, regs);
   __syncthreads();
   Rows1D<N, T>::store_spectrum(p, g, smem, tid, nth, inner0);
 }
 
 template <int N, int T>
-__global__ void __launch_bounds__(N <= 32 ? block_threads<N, T>() : FBF_COOP_THREADS)
+__global__ void __launch_bounds__(block_threads<N, T>())
 fft1d_inverse_kernel(const __grid_constant__ FftParams p, const __grid_constant__ FftGeom g) {
+  static_assert(N <= 32, "thread-per-line sizes");
   extern __shared__ __align__(16) char smem[];
   const int tid = threadIdx.x, nth = blockDim.x;
   const int inner0 = blockIdx.x * T;
   Rows1D<N, T>::load_spectrum(p, g, smem, tid, nth, inner0);
   __syncthreads();
-  if constexpr (N <= 32) {
-    LineRegs<N> regs;
-    Inverse<N, T>::row_fetch(g, smem, tid, regs);
-    __syncthreads();
-    Inverse<N, T>::row_pass(p, g, smem, tid, 0, inner0, regs);
-    __syncthreads();
-    Inverse<N, T>::store(p, g, smem, tid, nth, 0, inner0);
-  } else {
-    for (int line0 = 0; line0 < g.lines1; line0 += g.chunk) {
-      const int nl = min(g.chunk, g.lines1 - line0);
-      CoopInverse<N, T>::row_step1(p, g, smem, tid, nth, line0, nl);
-      __syncthreads();
-      CoopInverse<N, T>::row_step2(p, g, smem, tid, nth, 0, inner0, line0, nl);
-      __syncthreads();
-    }
-  }
+  LineRegs<N> regs;
+  Inverse<N, T>::row_fetch(g, smem, tid, regs);
+  __syncthreads();
+  Inverse<N, T>::row_pass(p, g, smem, tid, 0, inner0, regs);
+  __syncthreads();
+  Inverse<N, T>::store(p, g, smem, tid, nth, 0, inner0);
 }
 
 constexpr int kSmemMax = 227 * 1024;
@@ -418,7 +390,7 @@ cudaError_t dispatch_1d_tile(bool inverse, const FftParams& p, int T, cudaStream
 // Rows [0, rows) of `n` floats each, transform size N: full blocks of N rows, then the rest.
 cudaError_t launch_fft1d(bool inverse, const float* real_in, float* real_out, float2* spec, long long rows, int n,
                          int N, int offset, cudaStream_t stream) {
-  if (N == 256) return launch_fft1d_256(inverse, real_in, real_out, spec, rows, n, offset, stream);
+  if (N >= 64) return launch_fft1d_lines(inverse, real_in, real_out, spec, rows, n, N, offset, stream);
   const int KX = N / 2 + 1;
   for (int part = 0; part < 2; ++part) {
     const long long first = part == 0 ? 0 : rows / N * N;
@@ -448,8 +420,6 @@ cudaError_t launch_fft1d(bool inverse, const float* real_in, float* real_out, fl
       case 8: e = dispatch_1d_tile<8>(inverse, p, T, stream); break;
       case 16: e = dispatch_1d_tile<16>(inverse, p, T, stream); break;
       case 32: e = dispatch_1d_tile<32>(inverse, p, T, stream); break;
-      case 64: e = dispatch_1d_tile<64>(inverse, p, T, stream); break;
-      case 128: e = dispatch_1d_tile<128>(inverse, p, T, stream); break;
       default: e = cudaErrorInvalidValue;
     }
     if (e != cudaSuccess) return e;

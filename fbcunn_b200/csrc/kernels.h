@@ -28,9 +28,9 @@ cudaError_t launch_forward(const FftParams& p, int N, cudaStream_t stream);
 // batched 1-D real <-> half-complex transforms of contiguous rows (the row phases of the 2-D kernels)
 cudaError_t launch_fft1d(bool inverse, const float* real_in, float* real_out, float2* spec, long long rows, int n,
                          int N, int offset, cudaStream_t stream);
-// The 256-point 1-D transform (stand-alone entry points only), same arguments without the size.
-cudaError_t launch_fft1d_256(bool inverse, const float* real_in, float* real_out, float2* spec, long long rows, int n,
-                             int offset, cudaStream_t stream);
+// The 1-D transforms of 64, 128 and 256 points (fft1d_lines.cu), same arguments.
+cudaError_t launch_fft1d_lines(bool inverse, const float* real_in, float* real_out, float2* spec, long long rows,
+                               int n, int N, int offset, cudaStream_t stream);
 cudaError_t launch_inverse(const FftParams& p, int N, cudaStream_t stream);
 // Between the library's half spectrum [bin][plane (padded to kc)] and the reference's 2-D frequency
 // tensor (planes, N/2+1, N, 2) (nn.FFTWrapper, test/test_FFTModule.lua:310-342).

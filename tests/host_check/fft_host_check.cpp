@@ -114,7 +114,7 @@ void run_inverse(const FftParams& p, int oh, int ow) {
   }
 }
 
-// The 1-D kernels: the row phases around Rows1D::store_spectrum / load_spectrum.
+// The 1-D kernels up to 32 points: the row phases around Rows1D::store_spectrum / load_spectrum.
 template <int N, int T>
 void run_1d(bool inverse, const FftParams& p) {
   const FftGeom g = inverse ? inverse_geom(N, T, p.h, p.w) : forward_geom(N, T, p.h, p.w, 0, p.off_x);
@@ -126,64 +126,29 @@ void run_1d(bool inverse, const FftParams& p) {
     const int inner0 = tile * T;
     std::memset(smem.data(), 0xFF, smem.size());
     if (!inverse) {
-      if constexpr (N <= 32) {
-        for (int tid = 0; tid < nth; ++tid) Forward<N, T>::load(p, g, smem.data(), tid, nth, 0, inner0);
-        for (int tid = 0; tid < nth; ++tid) Forward<N, T>::row_fetch(p, g, smem.data(), tid, 0, inner0, regs[tid]);
-        std::memset(smem.data(), 0xFF, smem.size());
-        for (int tid = 0; tid < nth; ++tid) Forward<N, T>::row_pass(g, smem.data(), tid, regs[tid]);
-      } else {
-        constexpr int N1 = CoopForward<N, T>::N1, N2 = CoopForward<N, T>::N2;
-        for (int line0 = 0; line0 < g.lines1; line0 += g.chunk) {
-          const int nl = std::min(g.chunk, g.lines1 - line0);
-          for (int tid = 0; tid < nth; ++tid)
-            CoopForward<N, T>::row_step1(p, g, smem.data(), tid, nth, 0, inner0, line0, nl);
-          const int items = nl * N1;
-          std::vector<float2> all(static_cast<size_t>(items) * N2);
-          for (int item = 0; item < items; ++item) {
-            float2 u[N2];
-            CoopForward<N, T>::row_step2_fft(g, smem.data(), item, nl, u);
-            std::copy(u, u + N2, all.begin() + static_cast<size_t>(item) * N2);
-          }
-          for (int item = 0; item < items; ++item) {
-            float2 u[N2], mirror_odd[N2 / 2];
-            std::copy(all.begin() + static_cast<size_t>(item) * N2, all.begin() + static_cast<size_t>(item + 1) * N2, u);
-            const int partner = item ^ 1;
-            for (int i = 0; i < N2 / 2; ++i)
-              mirror_odd[i] = partner < items ? all[static_cast<size_t>(partner) * N2 + 2 * i + 1] : make_float2(NAN, NAN);
-            CoopForward<N, T>::row_step2_split(g, smem.data(), item, line0, u, mirror_odd);
-          }
-        }
-      }
+      for (int tid = 0; tid < nth; ++tid) Forward<N, T>::load(p, g, smem.data(), tid, nth, 0, inner0);
+      for (int tid = 0; tid < nth; ++tid) Forward<N, T>::row_fetch(p, g, smem.data(), tid, 0, inner0, regs[tid]);
+      std::memset(smem.data(), 0xFF, smem.size());
+      for (int tid = 0; tid < nth; ++tid) Forward<N, T>::row_pass(g, smem.data(), tid, regs[tid]);
       for (int tid = 0; tid < nth; ++tid) Rows1D<N, T>::store_spectrum(p, g, smem.data(), tid, nth, inner0);
     } else {
       for (int tid = 0; tid < nth; ++tid) Rows1D<N, T>::load_spectrum(p, g, smem.data(), tid, nth, inner0);
-      if constexpr (N <= 32) {
-        for (int tid = 0; tid < nth; ++tid) Inverse<N, T>::row_fetch(g, smem.data(), tid, regs[tid]);
-        std::memset(smem.data(), 0xFF, smem.size());
-        for (int tid = 0; tid < nth; ++tid) Inverse<N, T>::row_pass(p, g, smem.data(), tid, 0, inner0, regs[tid]);
-        for (int tid = 0; tid < nth; ++tid) Inverse<N, T>::store(p, g, smem.data(), tid, nth, 0, inner0);
-      } else {
-        for (int line0 = 0; line0 < g.lines1; line0 += g.chunk) {
-          const int nl = std::min(g.chunk, g.lines1 - line0);
-          std::memset(smem.data() + g.off_a, 0xFF, g.off_b - g.off_a);
-          for (int tid = 0; tid < nth; ++tid) CoopInverse<N, T>::row_step1(p, g, smem.data(), tid, nth, line0, nl);
-          for (int tid = 0; tid < nth; ++tid)
-            CoopInverse<N, T>::row_step2(p, g, smem.data(), tid, nth, 0, inner0, line0, nl);
-        }
-      }
+      for (int tid = 0; tid < nth; ++tid) Inverse<N, T>::row_fetch(g, smem.data(), tid, regs[tid]);
+      std::memset(smem.data(), 0xFF, smem.size());
+      for (int tid = 0; tid < nth; ++tid) Inverse<N, T>::row_pass(p, g, smem.data(), tid, 0, inner0, regs[tid]);
+      for (int tid = 0; tid < nth; ++tid) Inverse<N, T>::store(p, g, smem.data(), tid, nth, 0, inner0);
     }
   }
 }
 
 template <int N>
 int dispatch_1d_t(bool inverse, const FftParams& p, int T) {
-  if (cooperative(N) && T > 8) return 2;
   switch (T) {
     case 1: run_1d<N, 1>(inverse, p); return 0;
     case 2: run_1d<N, 2>(inverse, p); return 0;
     case 4: run_1d<N, 4>(inverse, p); return 0;
     case 8: run_1d<N, 8>(inverse, p); return 0;
-    case 16: if constexpr (N <= 32) { run_1d<N, 16>(inverse, p); return 0; } else { return 2; }
+    case 16: run_1d<N, 16>(inverse, p); return 0;
   }
   return 2;
 }
@@ -250,8 +215,6 @@ int hostcheck_fft1d(int inverse, float* real, float* spec, int N, int T, int h, 
     case 8: return dispatch_1d_t<8>(inverse != 0, p, T);
     case 16: return dispatch_1d_t<16>(inverse != 0, p, T);
     case 32: return dispatch_1d_t<32>(inverse != 0, p, T);
-    case 64: return dispatch_1d_t<64>(inverse != 0, p, T);
-    case 128: return dispatch_1d_t<128>(inverse != 0, p, T);
   }
   return 1;
 }

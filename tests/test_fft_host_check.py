@@ -118,7 +118,8 @@ def test_plane_major_layout(hc, N, T):
     assert np.abs(out / (N * N) - x).max() <= 5e-6 * np.abs(x).max()
 
 
-@pytest.mark.parametrize("N,T", [(2, 16), (4, 16), (4, 2), (8, 16), (16, 4), (32, 16), (64, 2), (64, 8), (128, 1), (128, 2)])
+# (sizes above 32 have kernels of their own, which only the GPU tests reach)
+@pytest.mark.parametrize("N,T", [(2, 16), (4, 16), (4, 2), (8, 16), (16, 4), (32, 16), (32, 2)])
 def test_1d_transforms(hc, N, T):
     """The batched 1-D kernels (row phases + plain store / load of the column buffer) against numpy."""
     rng = np.random.default_rng(N + T)
