@@ -11,8 +11,8 @@
 // array and then polls its own, local array.
 //
 // Every wait is bounded.  A rank whose peers do not show up within the limit skips its part,
-// records a code (peer_error) and returns; nothing spins forever.  No multicast object, no
-// cluster multicast and no TMA is used here: plain loads and stores on peer pointers.
+// records a code (peer_error) and returns; nothing spins forever.  Peer memory is only ever touched
+// by plain loads and stores on peer pointers: no NVSwitch reduction object, no TMA.
 #include "kernels.h"
 
 namespace fbfft {
