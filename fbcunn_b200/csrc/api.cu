@@ -135,6 +135,9 @@ struct fbfftconv_handle {
   size_t bytes_in, bytes_out, bytes_w, bytes_small, bytes_gi, bytes_total;
   // spectrum reuse (plane-major layers only): which tensor's forward spectrum a buffer holds
   bool have_input_spec = false, have_grad_output_spec = false, have_weight_spec = false;
+  // set by a backward call between its two passes: the second one is handed the gradOutput whose spectrum
+  // the first has just left in buf_out
+  bool same_grad_output = false;
   char* ws = nullptr;
   bool ws_owned = false;
   // device copies for the host-buffer entry points
@@ -897,7 +900,7 @@ int fbfftconv_acc_grad_parameters(fbfftconv_handle* h, const float* input, const
   {
     Fork fork(h, s, forward_tiles(h->N, B, F, h->oH, h->oW, 0, 0, false),
               forward_tiles(h->N, B, P, d.input_h, d.input_w, d.pad_h, d.pad_w, false));
-    if (!((d.flags & FBFFTCONV_REUSE_OUTPUT) && h->have_grad_output_spec)) {
+    if (!(((d.flags & FBFFTCONV_REUSE_OUTPUT) || h->same_grad_output) && h->have_grad_output_spec)) {
       StageTimer t(h, pass, FBFFTCONV_STAGE_FFT_A, s);
       FBF_CUDA(launch_forward(forward_params(grad_output, h->buf_out(), B, F, h->oH, h->oW, 0, 0, pm ? 2 : 0, h->N), h->N, s));
       h->have_grad_output_spec = true;
@@ -1375,7 +1378,11 @@ int fbfftconv_backward_host_async(fbfftconv_handle* h, const float* input, const
   FBF_TRY(fbfftconv_update_grad_input(h, dgo, dw, dgi, stream));
   FBF_TRY(a1.begin_downloads());  // gradInput can leave while the weight gradient is computed
   FBF_CUDA(cudaMemcpyAsync(grad_input, dgi, n_in * 4, cudaMemcpyDeviceToHost, h->down));
-  FBF_TRY(fbfftconv_acc_grad_parameters(h, din, dgo, dgw, grad_bias ? dgb : nullptr, scale, stream));
+  // both passes of a backward call see the same gradOutput: its spectrum is transformed once
+  h->same_grad_output = true;
+  const int rc_acc = fbfftconv_acc_grad_parameters(h, din, dgo, dgw, grad_bias ? dgb : nullptr, scale, stream);
+  h->same_grad_output = false;
+  FBF_TRY(rc_acc);
   // gradOutput's staging belongs to pass 1 but is read until here: its 'kernels done' moves
   FBF_CUDA(cudaEventRecord(h->ev_kernels[1], s));
   FBF_TRY(a2.begin_downloads());

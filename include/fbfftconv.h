@@ -194,7 +194,7 @@ int fbfftconv_acc_grad_parameters_host_async(fbfftconv_handle* h, const float* i
                                              float* grad_bias, float scale, fbfftconv_stream stream);
 /* nn.Module:backward(input, gradOutput, scale) for host buffers: updateGradInput and
  * accGradParameters (fbcunn/SpatialConvolutionFFT.lua:405-416) with input, gradOutput and weight
- * uploaded once for both. */
+ * uploaded once for both, and gradOutput, which both passes see unchanged, transformed once. */
 int fbfftconv_backward_host_async(fbfftconv_handle* h, const float* input, const float* grad_output,
                                   const float* weight, float* grad_input, float* grad_weight,
                                   float* grad_bias, float scale, fbfftconv_stream stream);

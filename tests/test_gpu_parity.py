@@ -422,10 +422,15 @@ def test_host_buffer_entry_points():
     lib.fbfftconv_destroy(h)
 
 
-def test_asynchronous_host_buffer_entry_points():
+# bin-major on CUDA cores; plane-major (three input planes, 64-point transform); tensor cores with the
+# batch on the MMA's column side; tensor cores with the batch on its rows
+@pytest.mark.parametrize("s", [oracle.Shape(6, 4, 5, 30, 29, 3, 2, 1, 0), oracle.Shape(4, 3, 6, 60, 50, 5, 5, 0, 0),
+                               oracle.Shape(8, 16, 24, 20, 20, 5, 5, 0, 0), oracle.Shape(72, 16, 16, 12, 12, 3, 3, 1, 1)],
+                         ids=["simt", "plane_major", "tc_batch_on_columns", "tc"])
+def test_asynchronous_host_buffer_entry_points(s):
     """Three passes enqueued without waiting, results read after one fbfftconv_host_sync; repeated with
-    new data so that the staging buffers of a pass are reused while the previous step is in flight."""
-    s = oracle.Shape(6, 4, 5, 30, 29, 3, 2, 1, 0)
+    new data so that the staging buffers of a pass are reused while the previous step is in flight.
+    The middle step is one backward call, whose two passes share the spectrum of gradOutput."""
     lib = capi.lib()
     desc = capi.Desc(s.B, s.P, s.F, s.iH, s.iW, s.kH, s.kW, 1, 1, s.padH, s.padW, 0, 0)
     h = ctypes.c_void_p()
