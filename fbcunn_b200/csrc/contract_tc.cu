@@ -24,7 +24,6 @@
 // returns, and the host sees the error code.
 #include <cuda.h>
 
-#include <atomic>
 #include <cstdint>
 #include <cstdlib>
 #include <mutex>
@@ -309,17 +308,8 @@ cudaError_t launch_wide_as(const ContractParams& p, cudaStream_t stream) {
   t.s_b1_im = -sa * sb;
   t.s_b2_re = sb;
   t.s_b2_im = sa;
-  // the opt-in to large dynamic shared memory is per device and function: once is enough
-  constexpr int kMaxDevices = 64;
-  static std::atomic<bool> opted_in[kMaxDevices];
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) dev = 0;
-  if (!opted_in[dev].load(std::memory_order_acquire)) {
-    cudaError_t e = cudaFuncSetAttribute(contract_tc_wide_kernel<WBNC, A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         TL::SMEM_BYTES);
-    if (e != cudaSuccess) return e;
-    opted_in[dev].store(true, std::memory_order_release);
-  }
+  cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(contract_tc_wide_kernel<WBNC, A_MN, B_MN>), TL::SMEM_BYTES);
+  if (e != cudaSuccess) return e;
   const int sms = sm_count();
   const int grid = (int)(total < sms ? total : sms);
   contract_tc_wide_kernel<WBNC, A_MN, B_MN><<<grid, W_THREADS, TL::SMEM_BYTES, stream>>>(map_a, map_b, t);
