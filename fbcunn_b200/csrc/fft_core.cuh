@@ -269,6 +269,11 @@ static inline int stage_pitch(int n) {
   return p;
 }
 
+// Row pitch (float2) of the cooperative kernels' column buffer: at least `cols`, and 8 modulo 16, so that
+// the eight-element runs that the lanes of neighbouring row lines store in one instruction (row step 2)
+// fall into different halves of the banks.  The column phases walk along the rows and do not care.
+constexpr int coop_mid_pitch(int cols) { return (cols + 7) / 16 * 16 + 8; }
+
 // `plane_elems`: elements of one real plane as it lies in global memory.
 static inline FftGeom make_geom(int N, int T, int he, int we, int plane_elems, bool inverse) {
   FftGeom g;
@@ -293,7 +298,7 @@ static inline FftGeom make_geom(int N, int T, int he, int we, int plane_elems, b
   } else {
     const int n1 = N == 64 ? 8 : 8, n2 = N / n1;
     g.pitch1 = (n1 * (n2 + 1)) | 1;    // = CoopLayout::PITCH1 (odd: neighbouring lines, different banks)
-    g.pitch2 = g.lines2 | 1;           // = CoopLayout::PITCH2
+    g.pitch2 = coop_mid_pitch(g.lines2);  // = CoopLayout::PITCH2
     g.chunk = N == 64 ? 64 : 32;
     if (g.chunk > g.lines1) g.chunk = g.lines1;
     const int bytes_a = g.chunk * g.pitch1 * 8;
@@ -568,7 +573,7 @@ struct CoopLayout {
   static constexpr int N1 = Split<N>::N1, N2 = Split<N>::N2, KX = N / 2 + 1;
   static constexpr int COLS = T * KX;                 // columns of mid: (t, kx)
   static constexpr int PITCH1 = (N1 * (N2 + 1)) | 1;  // row buffer line pitch (float2), odd
-  static constexpr int PITCH2 = COLS | 1;             // mid row pitch (float2), odd
+  static constexpr int PITCH2 = coop_mid_pitch(COLS);  // mid row pitch (float2)
   static_assert(N1 == 8, "the residue pairing below is written for eight residues");
 };
 
