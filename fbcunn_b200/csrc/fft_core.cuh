@@ -297,7 +297,7 @@ static inline FftGeom make_geom(int N, int T, int he, int we, int plane_elems, b
     g.threads = round_up(g.lines2 < 64 ? 64 : g.lines2, 32);
   } else {
     const int n1 = N == 64 ? 8 : 8, n2 = N / n1;
-    g.pitch1 = (n1 * (n2 + 1)) | 1;    // = CoopLayout::PITCH1 (odd: neighbouring lines, different banks)
+    g.pitch1 = n1 * (n2 + 1);          // = CoopLayout::PITCH1
     g.pitch2 = coop_mid_pitch(g.lines2);  // = CoopLayout::PITCH2
     g.chunk = N == 64 ? 64 : 32;
     if (g.chunk > g.lines1) g.chunk = g.lines1;
@@ -572,7 +572,11 @@ template <int N, int T>
 struct CoopLayout {
   static constexpr int N1 = Split<N>::N1, N2 = Split<N>::N2, KX = N / 2 + 1;
   static constexpr int COLS = T * KX;                 // columns of mid: (t, kx)
-  static constexpr int PITCH1 = (N1 * (N2 + 1)) | 1;  // row buffer line pitch (float2), odd
+  // Row buffer line pitch (float2): 72 / 136, i.e. 8 modulo 16.  In the second row step the eight lanes of
+  // a line read at a stride of N2 + 1 and cover half of the banks; the next line's lanes, 16 banks on, the
+  // other half.  (The first row step stores 8 or 16 neighbouring values per line and does not care.)
+  static constexpr int PITCH1 = N1 * (N2 + 1);
+  static_assert(PITCH1 % 16 == 8, "neighbouring lines of the second row step: different halves of the banks");
   static constexpr int PITCH2 = coop_mid_pitch(COLS);  // mid row pitch (float2)
   static_assert(N1 == 8, "the residue pairing below is written for eight residues");
 };
