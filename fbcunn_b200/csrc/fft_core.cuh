@@ -273,6 +273,11 @@ static inline int stage_pitch(int n) {
 // the eight-element runs that the lanes of neighbouring row lines store in one instruction (row step 2)
 // fall into different halves of the banks.  The column phases walk along the rows and do not care.
 constexpr int coop_mid_pitch(int cols) { return (cols + 7) / 16 * 16 + 8; }
+// Distance (float2) between the planes of a tile inside a row of the column buffer: N/2 + 1 values per
+// plane, spaced 4 modulo 16 apart when a tile has several planes, so that the lanes that take the T
+// planes of neighbouring bins (column step 2 of the forward, column step 1 of the inverse) use
+// different banks.
+constexpr int coop_plane_stride(int kx, int T) { return T == 1 ? kx : (kx + 11) / 16 * 16 + 4; }
 
 // `plane_elems`: elements of one real plane as it lies in global memory.
 static inline FftGeom make_geom(int N, int T, int he, int we, int plane_elems, bool inverse) {
@@ -298,7 +303,7 @@ static inline FftGeom make_geom(int N, int T, int he, int we, int plane_elems, b
   } else {
     const int n1 = N == 64 ? 8 : 8, n2 = N / n1;
     g.pitch1 = n1 * (n2 + 1);          // = CoopLayout::PITCH1
-    g.pitch2 = coop_mid_pitch(g.lines2);  // = CoopLayout::PITCH2
+    g.pitch2 = coop_mid_pitch(T * coop_plane_stride(N / 2 + 1, T));  // = CoopLayout::PITCH2
     g.chunk = N == 64 ? 64 : 32;
     if (g.chunk > g.lines1) g.chunk = g.lines1;
     const int bytes_a = g.chunk * g.pitch1 * 8;
@@ -571,13 +576,22 @@ struct Inverse {
 template <int N, int T>
 struct CoopLayout {
   static constexpr int N1 = Split<N>::N1, N2 = Split<N>::N2, KX = N / 2 + 1;
-  static constexpr int COLS = T * KX;                 // columns of mid: (t, kx)
+  static constexpr int COLS = T * KX;                 // columns of a tile: (t, kx)
+  static constexpr int KXP = coop_plane_stride(KX, T); // column (t, kx) lies at t * KXP + kx of a mid row
+  static FBF_HD int col_address(int col) {             // column index t * KX + kx -> its place in a mid row
+    if constexpr (T == 1) {
+      return col;
+    } else {
+      const int t = col / KX;
+      return col + t * (KXP - KX);
+    }
+  }
   // Row buffer line pitch (float2): 72 / 136, i.e. 8 modulo 16.  In the second row step the eight lanes of
   // a line read at a stride of N2 + 1 and cover half of the banks; the next line's lanes, 16 banks on, the
   // other half.  (The first row step stores 8 or 16 neighbouring values per line and does not care.)
   static constexpr int PITCH1 = N1 * (N2 + 1);
   static_assert(PITCH1 % 16 == 8, "neighbouring lines of the second row step: different halves of the banks");
-  static constexpr int PITCH2 = coop_mid_pitch(COLS);  // mid row pitch (float2)
+  static constexpr int PITCH2 = coop_mid_pitch(T * KXP);  // mid row pitch (float2)
   static_assert(N1 == 8, "the residue pairing below is written for eight residues");
 };
 
@@ -691,8 +705,8 @@ struct CoopForward {
     int t, j;
     coop_split_line<T>(g, line, t, j);
     const bool has_b = (j + g.hh) < g.he;
-    float2* ma = mid + j * L::PITCH2 + t * KX;
-    float2* mb = mid + (j + g.hh) * L::PITCH2 + t * KX;
+    float2* ma = mid + j * L::PITCH2 + t * L::KXP;
+    float2* mb = mid + (j + g.hh) * L::PITCH2 + t * L::KXP;
     if (k1 == 0 || k1 == N1 / 2) {
 #pragma unroll
       for (int k2 = 0; k2 <= N2 / 2; ++k2) {
@@ -728,7 +742,7 @@ struct CoopForward {
     float2* mid = reinterpret_cast<float2*>(smem + g.off_b);
     for (int item = tid; item < L::COLS * N2; item += nthreads) {
       const int n2 = item / L::COLS, col = item - n2 * L::COLS;
-      float2* c = mid + col + n2 * L::PITCH2;
+      float2* c = mid + L::col_address(col) + n2 * L::PITCH2;
       float2 v[N1];
 #pragma unroll
       for (int n1 = 0; n1 < N1; ++n1)
@@ -755,7 +769,7 @@ struct CoopForward {
       // neighbouring lanes take the T planes of one bin, so that their 8-byte stores share a line
       const int k1 = item / L::COLS, ci = item - k1 * L::COLS;
       const int kx = ci / T, t = ci - kx * T;
-      const int col = t * KX + kx;
+      const int col = t * L::KXP + kx;
       const int inner = inner0 + t;
       if (inner >= p.kc) continue;
       const float2* c = mid + col + N2 * k1 * L::PITCH2;
@@ -789,7 +803,7 @@ struct CoopInverse {
     // neighbouring lanes take the T planes of one bin: their 8-byte loads share a line
     const int n2 = item / L::COLS, ci = item - n2 * L::COLS;
     const int kx = ci / T, t = ci - kx * T;
-    const int col = t * KX + kx;
+    const int col = t * L::KXP + kx;
     const bool live = inner0 + t < p.n_inner;
     const int bin_stride = PM ? 1 : (int)p.spec_bin;
     const int inner_stride = PM ? N * KX : (int)p.spec_inner;
@@ -835,7 +849,7 @@ struct CoopInverse {
     float2* mid = reinterpret_cast<float2*>(smem + g.off_b);
     for (int item = tid; item < L::COLS * N1; item += nthreads) {
       const int k1 = item / L::COLS, col = item - k1 * L::COLS;
-      float2* c = mid + col + k1 * L::PITCH2;
+      float2* c = mid + L::col_address(col) + k1 * L::PITCH2;
       float2 u[N2];
 #pragma unroll
       for (int n2 = 0; n2 < N2; ++n2) u[n2] = c[N1 * n2 * L::PITCH2];
@@ -861,7 +875,7 @@ struct CoopInverse {
       int t, j;
     coop_split_line<T>(g, line, t, j);
       const bool has_b = (j + g.hh) < g.he;
-      const float2* pa = mid + (p.off_y + j) * L::PITCH2 + t * KX;
+      const float2* pa = mid + (p.off_y + j) * L::PITCH2 + t * L::KXP;
       const float2* pb = pa + g.hh * L::PITCH2;
       float2 v[N1];
 #pragma unroll
