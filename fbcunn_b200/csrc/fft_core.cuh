@@ -43,22 +43,8 @@ namespace fbfft {
 // ---------------------------------------------------------------------------
 // complex helpers and twiddles
 // ---------------------------------------------------------------------------
-// Complex add / subtract as one packed f32x2 instruction on the device (sm_100 has two-wide fp32
-// add / mul / fma on register pairs; a float2 that came from an 8-byte load already is one).
-FBF_HD float2 cadd(float2 a, float2 b) {
-#if defined(__CUDA_ARCH__) && defined(FBF_PACKED)
-  return __fadd2_rn(a, b);
-#else
-  return make_float2(a.x + b.x, a.y + b.y);
-#endif
-}
-FBF_HD float2 csub(float2 a, float2 b) {
-#if defined(__CUDA_ARCH__) && defined(FBF_PACKED)
-  return __ffma2_rn(b, make_float2(-1.f, -1.f), a);
-#else
-  return make_float2(a.x - b.x, a.y - b.y);
-#endif
-}
+FBF_HD float2 cadd(float2 a, float2 b) { return make_float2(a.x + b.x, a.y + b.y); }
+FBF_HD float2 csub(float2 a, float2 b) { return make_float2(a.x - b.x, a.y - b.y); }
 FBF_HD float2 cmul(float2 a, float2 b) {
   return make_float2(a.x * b.x - a.y * b.y, a.x * b.y + a.y * b.x);
 }
@@ -419,6 +405,26 @@ struct Forward {
     const bool va = live && (unsigned)ya < (unsigned)p.h, vb = live && (unsigned)yb < (unsigned)p.h;
     const float* pa = sp + ya * p.w - p.off_x;
     const float* pb = pa + g.hh * p.w;
+    if constexpr (N >= 4) {
+      // Rows that start on 16-byte boundaries of the staged plane (width and offset multiples of four,
+      // plane staged without a shift) are read four floats at a time: a quarter of the loads, and the
+      // eight planes that neighbouring lanes read lie 16 bytes apart modulo the banks, where scalar
+      // loads of rows a multiple of four floats long collide four ways.
+      if (((p.w | p.off_x) & 3) == 0 && sp == stage + t * g.pitch1) {
+        const Quad zero = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int c = 0; c < N / 4; ++c) {
+          const bool px = (unsigned)(4 * c - p.off_x) < (unsigned)p.w;
+          const Quad a = va && px ? *reinterpret_cast<const Quad*>(pa + 4 * c) : zero;
+          const Quad b = vb && px ? *reinterpret_cast<const Quad*>(pb + 4 * c) : zero;
+          regs.v[4 * c + 0] = make_float2(a.a, b.a);
+          regs.v[4 * c + 1] = make_float2(a.b, b.b);
+          regs.v[4 * c + 2] = make_float2(a.c, b.c);
+          regs.v[4 * c + 3] = make_float2(a.d, b.d);
+        }
+        return;
+      }
+    }
 #pragma unroll
     for (int x = 0; x < N; ++x) {
       const bool px = (unsigned)(x - p.off_x) < (unsigned)p.w;
@@ -519,10 +525,28 @@ struct Inverse {
     float* stage = reinterpret_cast<float*>(smem + g.off_a);
     const int j = line / T, t = line - j * T;
     const bool has_b = (j + g.hh) < g.he;
-    float* sa = stage + t * g.pitch1 + phase16(plane_ptr(p, g, row, inner0 + t)) + j * g.we - p.off_x;
+    const int shift = phase16(plane_ptr(p, g, row, inner0 + t));
+    float* sa = stage + t * g.pitch1 + shift + j * g.we - p.off_x;
     float* sb = sa + g.hh * g.we;
     const unsigned we = (unsigned)g.we;
     fft_inreg<N, true>(regs.v);
+    if constexpr (N >= 4) {
+      // rows on 16-byte boundaries of the staged plane: four floats per store (see Forward::row_fetch)
+      if (((g.we | p.off_x) & 3) == 0 && shift == 0) {
+#pragma unroll
+        for (int c = 0; c < N / 4; ++c) {
+          if ((unsigned)(4 * c - p.off_x) < we) {
+            const Quad a = {regs.v[4 * c].x, regs.v[4 * c + 1].x, regs.v[4 * c + 2].x, regs.v[4 * c + 3].x};
+            *reinterpret_cast<Quad*>(sa + 4 * c) = a;
+            if (has_b) {
+              const Quad b = {regs.v[4 * c].y, regs.v[4 * c + 1].y, regs.v[4 * c + 2].y, regs.v[4 * c + 3].y};
+              *reinterpret_cast<Quad*>(sb + 4 * c) = b;
+            }
+          }
+        }
+        return;
+      }
+    }
 #pragma unroll
     for (int x = 0; x < N; ++x) {
       if ((unsigned)(x - p.off_x) < we) {
